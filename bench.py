@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Benchmark of the FlyVec train step (and, on request, of the hashers) on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference ...                      # the CPU arm
+
+A "step" is one global minibatch step: every GPU processes ``batch`` = 10 000
+windows of w = 11 tokens against K = 400 hidden units over a V = 20 000
+vocabulary.  The corpus is synthetic (bounded Zipf(1.0) token ids, geometric
+chunk lengths, seeds fixed); initial weights are N(0,1).  Rank 0 prints one JSON
+line.  Under ``torch.distributed.run`` every process is one rank; the data path
+uses the library's own NCCL communicator, ``torch.distributed`` (gloo) only
+carries the rendezvous, the barriers and the max-over-ranks of the timings.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG = dict(K=400, V=20000, W=11, batch=10000, lr=2e-4, zipf_s=1.0, chunk_mean=25.0, tokens_per_gpu=50_000_000)
+CORPUS_SEED, WEIGHT_SEED, PERM_SEED = 101, 1, 201
+
+
+# ----------------------------------------------------------------------------
+# helpers
+# ----------------------------------------------------------------------------
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    return rank, world, local
+
+
+class Dist:
+    """Rendezvous / barrier / max-reduce over gloo; a no-op for one rank."""
+
+    def __init__(self, world):
+        self.world = world
+        self.dist = None
+        if world > 1:
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("gloo")
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+
+    def bcast_obj(self, obj, src=0):
+        if not self.dist:
+            return obj
+        box = [obj]
+        self.dist.broadcast_object_list(box, src=src)
+        return box[0]
+
+    def max(self, x: float) -> float:
+        if not self.dist:
+            return x
+        import torch
+
+        t = torch.tensor([x], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def sum(self, x: float) -> float:
+        if not self.dist:
+            return x
+        import torch
+
+        t = torch.tensor([x], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t[0])
+
+    def close(self):
+        if self.dist:
+            self.dist.destroy_process_group()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+def make_or_load_corpus(ntok: int, rank: int, dist: Dist):
+    """Rank 0 draws the corpus once and shares it through /dev/shm."""
+    from flyvec_b200 import synth
+
+    if dist.world == 1:
+        return synth.make_corpus(ntok, CFG["V"], s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=CFG["W"],
+                                 seed=CORPUS_SEED)
+    tag = os.environ.get("MASTER_PORT", "0")
+    base = Path("/dev/shm" if Path("/dev/shm").exists() else tempfile.gettempdir()) / f"fvbench_{tag}_{ntok}"
+    if rank == 0:
+        base.mkdir(exist_ok=True)
+        enc, off = synth.make_corpus(ntok, CFG["V"], s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=CFG["W"],
+                                     seed=CORPUS_SEED)
+        np.save(base / "enc.npy", enc)
+        np.save(base / "off.npy", off)
+    dist.barrier()
+    enc = np.load(base / "enc.npy", mmap_mode="r")
+    off = np.load(base / "off.npy", mmap_mode="r")
+    return enc, off
+
+
+def build_idx_host(enc, starts, perm, W, V):
+    """Input ids of the given windows (token, centre token + V) as the streaming
+    entry point takes them."""
+    pos = starts[perm].astype(np.int64)[:, None] + np.arange(W, dtype=np.int64)[None, :]
+    idx = np.asarray(enc)[pos].astype(np.int32)
+    idx[:, W // 2] += V
+    return idx
+
+
+# ----------------------------------------------------------------------------
+# this library
+# ----------------------------------------------------------------------------
+def bench_train(args):
+    from flyvec_b200 import _lib, engine, synth
+
+    rank, world, local = dist_env()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    dist = Dist(world)
+    K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
+    steps, warmup = args.steps, args.warmup
+    need_windows = (steps + warmup + 8) * world * B
+    ntok = args.tokens or min(CFG["tokens_per_gpu"] * world, 400_000_000)
+    enc, off = make_or_load_corpus(ntok, rank, dist)
+
+    tr = engine.Trainer(hid=K, vocab=V, window=W, batch=B, lr0=CFG["lr"], device=local, rank=rank, world=world)
+    if world > 1:
+        uid = dist.bcast_obj(engine.Trainer.comm_unique_id() if rank == 0 else None)
+        tr.init_comm(uid)
+    ns = tr.set_corpus(np.asarray(enc), np.asarray(off))
+    assert ns >= need_windows, f"corpus has {ns} windows, {need_windows} needed: raise --tokens"
+    tr.set_weights(synth.make_weights(K, 2 * V, seed=WEIGHT_SEED))
+    tr.shuffle(PERM_SEED)
+    eps = np.float32(CFG["lr"])  # one epoch: eps = lr0 * (1 - 0/1)
+
+    # ---- device-resident loop ------------------------------------------------
+    tr.run_steps(0, warmup, eps)
+    sampler = ClockSampler(local)
+    dist.barrier()
+    if rank == 0:
+        sampler.start()
+    t0 = time.perf_counter()
+    st = tr.run_steps(warmup, steps, eps)  # returns after the stream is idle
+    wall = time.perf_counter() - t0
+    dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    sec = dist.max(st["seconds"])
+    wall = dist.max(wall)
+    fwd_s = dist.max(st["fwd_seconds"])
+    total_windows = steps * world * B
+    value = total_windows / sec
+
+    # ---- end to end: ids streamed from pinned host memory, normalisers read back ----
+    e2e_steps = min(steps, args.e2e_steps)
+    perm = tr.get_permutation()
+    starts = engine.enumerate_windows(np.asarray(off), W)
+    first = (warmup + steps) * world * B
+    if first + e2e_steps * world * B > ns:
+        first = 0
+    sel = perm[first:first + e2e_steps * world * B]
+    pinned = _lib.pinned_empty((e2e_steps, world * B, W), np.int32)
+    pinned[...] = build_idx_host(enc, starts, sel, W, V).reshape(e2e_steps, world * B, W)
+    nc_host = _lib.pinned_empty((e2e_steps,), np.float32)
+    tr.run_steps_host(pinned[:min(8, e2e_steps)], min(8, e2e_steps), eps)  # warm the staging buffers
+    dist.barrier()
+    t0 = time.perf_counter()
+    tr.run_steps_host(pinned, e2e_steps, eps, nc_out=nc_host)
+    e2e_wall = dist.max(time.perf_counter() - t0)
+    e2e_value = e2e_steps * world * B / e2e_wall
+
+    # ---- roofline of the dominant kernel ---------------------------------------
+    peak, peak_src = measured_peaks()
+    fwd_bytes = B * W * K * 4 + B * (8 + 4 * W) + B * 8  # gathered rows + order entry and ids + winner and activation out
+    fwd_avg = fwd_s / steps
+    achieved = fwd_bytes / fwd_avg / 1e9
+    step_bytes = B * W * K * 4 + 3 * K * 2 * V * 4 + B * (8 + 4 * W) + B * 2 + K * 4  # the reference schedule's figure
+
+    out = {
+        "metric": "train windows/sec (K=400,V=20k,w=11)", "value": value, "unit": "windows/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec / steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000/GPU lr=2e-4 W0~N(0,1)",
+                   "corpus_tokens": int(ntok), "windows": int(ns), "global_batch": world * B,
+                   "parallelism": f"dp{world}",
+                   "l2": "inputs larger than L2: corpus + window tables (>0.6 GB) stream through; the 64 MB synapse "
+                         "matrix is re-read every step by design"},
+        "wall_ms_per_step": wall / steps * 1e3,
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "windows/s", "h2d_bytes_per_step": world * B * W * 4,
+                "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                "what": "fv_trainer_run_steps_host: input ids uploaded from pinned host memory inside the call, "
+                        "per-step normaliser copied back"},
+        "gpu_launches": int(st["kernel_launches"]),
+        "roofline": {"kernel": "k_forward (fused gather-sum + arg-max)", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": fwd_bytes, "avg_launch_ms": fwd_avg * 1e3,
+                     "note": "rows are gathered from the L2-resident matrix, so achieved can exceed the HBM figure"},
+        "phases_ms_per_step": {"forward": fwd_avg * 1e3, "xx+exchange": dist.max(st["exch_seconds"]) / steps * 1e3,
+                               "update": dist.max(st["upd_seconds"]) / steps * 1e3},
+        "step_algorithmic_gbs": step_bytes / (sec / steps) / 1e9,
+        "last_nc": st["last_nc"],
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_train_baseline(enc, off, seconds_budget=args.cpu_seconds)
+    tr.close()
+    dist.close()
+    if rank == 0:
+        print(json.dumps(out))
+
+
+def bench_hash(args, windows: bool):
+    """Device-resident and end-to-end throughput of the token / window hasher."""
+    from flyvec_b200 import engine, synth
+
+    K, V, W = CFG["K"], CFG["V"], CFG["W"]
+    hl = args.hash_length
+    Wm = synth.make_weights(K, 2 * V, seed=WEIGHT_SEED)
+    h = engine.Hasher(Wm, normalize=True)
+    peak, peak_src = measured_peaks()
+    code_b = (K + 7) // 8
+    if windows:
+        n = args.items or 16_000_000
+        enc, off = synth.make_corpus(max(n // 2, 1_000_000), V, seed=104)
+        starts = engine.enumerate_windows(off, W)
+        rng = np.random.default_rng(204)
+        sel = rng.integers(0, len(starts), n)
+        ids = build_idx_host(enc, starts, sel, W, V)
+        h.set_inverse_frequency(engine.inverse_frequency(enc, V))
+        per_item = W * K * 4 + W * 4 + code_b
+    else:
+        n = args.items or 1_000_000
+        ids = synth.make_hash_ids(n, V, seed=100)
+        per_item = K * 4 + code_b
+    d_in = engine.DeviceBuffer(ids.nbytes)
+    d_in.upload(ids)
+    d_out = engine.DeviceBuffer(n * code_b)
+    run = (lambda: h.hash_windows_device(d_in.ptr, n, W, True, hl, d_out.ptr)) if windows else \
+          (lambda: h.hash_tokens_device(d_in.ptr, n, hl, d_out.ptr))
+    for _ in range(max(args.warmup, 3)):
+        run()
+    times = []
+    for _ in range(max(args.steps, 1)):
+        engine.flush_l2(0)
+        times.append(run())
+    t = float(np.mean(times))
+    t0 = time.perf_counter()
+    if windows:
+        h.hash_windows(ids, inv_freq=None, hash_length=hl, packed=True)
+    else:
+        h.hash_tokens(ids, hash_length=hl, packed=True)
+    e2e = time.perf_counter() - t0
+    out = {"metric": "hashed windows/sec" if windows else "hashed tokens/sec", "value": n / t,
+           "unit": "windows/s" if windows else "tokens/s", "n_gpus": 1, "steps": len(times), "warmup": max(args.warmup, 3),
+           "ms_per_step": t * 1e3, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": ("config 4: window hashing" if windows else "config 0 shapes: token hashing"),
+                      "items": n, "hash_length": hl, "l2": "L2 flushed between timed launches"},
+           "e2e": {"value": n / e2e, "unit": "items/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": n * code_b},
+           "roofline": {"kernel": "k_hash", "bound": "hbm", "achieved": per_item * n / t / 1e9, "peak": peak,
+                        "unit": "GB/s", "frac": per_item * n / t / 1e9 / peak, "traffic": None, "peak_source": peak_src}}
+    print(json.dumps(out))
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the oracle's C restatement of the reference step on the host cores
+# ----------------------------------------------------------------------------
+def cpu_train_baseline(enc, off, seconds_budget: float = 20.0, max_steps: int = 10 ** 9):
+    """Times oracle/oracle_train.c (a literal restatement of the reference's step;
+    the reference trainer itself is CUDA-only) on config-1 shapes."""
+    from flyvec_b200 import synth
+    from oracle import c_oracle
+    from oracle import flyvec_oracle as orc
+
+    K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
+    starts = orc.enumerate_windows(np.asarray(off[:200_000]), W)
+    f = orc.inverse_word_frequency(np.asarray(enc), V, saturate_fp32=False)
+    rng = np.random.default_rng(PERM_SEED)
+    perm = rng.permutation(len(starts))
+    Wm = synth.make_weights(K, 2 * V, seed=WEIGHT_SEED)
+    runner = c_oracle.StepRunner(K, 2 * V, V, W, B, 1)
+    nsteps, t_total = 0, 0.0
+    while nsteps < max_steps and (nsteps < 2 or t_total < seconds_budget):
+        idx = orc.build_idx(np.asarray(enc), starts, perm[(nsteps * B) % (len(perm) - B):][:B], W, V)
+        t0 = time.perf_counter()
+        runner.step(Wm, idx[None], [B], f, np.float32(CFG["lr"]))
+        dt = time.perf_counter() - t0
+        if nsteps > 0:  # the first call pages the scratch memory in
+            t_total += dt
+        nsteps += 1
+    timed = nsteps - 1
+    return {"value": timed * B / t_total, "unit": "windows/s", "cores": c_oracle.num_threads(), "kind": "port",
+            "sample": f"{timed} full minibatch steps of {B} windows (config 1 shapes), {t_total:.1f} s",
+            "seconds_per_step": t_total / timed}
+
+
+def bench_reference(args):
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    from flyvec_b200 import synth
+
+    K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
+    enc, off = synth.make_corpus(5_000_000, V, s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=W, seed=CORPUS_SEED)
+    budget = args.cpu_seconds_reference
+    base = cpu_train_baseline(enc, off, seconds_budget=budget, max_steps=args.steps + 1)
+    timed = int(base["sample"].split()[0])
+    out = {"impl": "reference", "metric": "train windows/sec (K=400,V=20k,w=11)", "value": base["value"],
+           "unit": "windows/s", "n_gpus": args.gpus, "steps": timed, "warmup": 1,
+           "ms_per_step": base["seconds_per_step"] * 1e3, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000 lr=2e-4 W0~N(0,1)",
+                      "note": "the reference trainer is CUDA-only; this arm times the C/OpenMP restatement of its "
+                              "step (oracle/oracle_train.c) on the host cores, a bounded number of full steps"},
+           "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+           "e2e": {"value": base["value"], "unit": "windows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=["train", "hash_tokens", "hash_windows"], default="train")
+    ap.add_argument("--tokens", type=int, default=0, help="corpus size (default 50M per GPU, at most 400M)")
+    ap.add_argument("--items", type=int, default=0, help="hash workloads: number of tokens / windows")
+    ap.add_argument("--hash-length", type=int, default=50)
+    ap.add_argument("--e2e-steps", type=int, default=400)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--cpu-seconds-reference", type=float, default=90.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return bench_reference(args)
+    if args.workload == "train":
+        return bench_train(args)
+    return bench_hash(args, windows=(args.workload == "hash_windows"))
+
+
+if __name__ == "__main__":
+    main()

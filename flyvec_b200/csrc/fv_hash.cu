@@ -1,0 +1,518 @@
+// FlyVec hasher for sm_100a.
+//
+// The synapse matrix is held transposed, wt[N][Kp] (row = one input id, Kp = K
+// padded to a multiple of 4), optionally row-normalised exactly as the
+// reference does it (flyvec/core.py:22-36).  A code is computed by one warp:
+// activations of the K units -> the hash_length-th and the next largest value
+// by a bitwise search on order-preserving integer keys -> threshold at their
+// float midpoint with a strict '>' (flyvec/core.py:155-158) -> bits.
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "fv_common.h"
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+struct HDev {
+  int K, Kp, Kq, N, V;
+  const float* wt;
+  const float* f;  // 1/count per vocabulary id, may be null
+  uint32_t* error;
+};
+
+// ---- normalisation ---------------------------------------------------------
+// numpy sums a contiguous float32 row pairwise: blocks of at most 128 elements
+// are summed with eight interleaved accumulators combined as
+// ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)) plus a sequential tail; longer ranges are
+// split at n/2 rounded down to a multiple of 8.  np.sum(syn**2, axis=1) in
+// flyvec/core.py:35 therefore has a fixed association order, reproduced here so
+// that the normalised weights -- and every code derived from them -- are
+// bit-identical to the reference's.
+__device__ float leaf_sumsq(const float* __restrict__ a, long long n) {
+  if (n < 8) {
+    float r = 0.f;
+    for (long long i = 0; i < n; ++i) r = __fadd_rn(r, __fmul_rn(a[i], a[i]));
+    return r;
+  }
+  float r[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) r[j] = __fmul_rn(a[j], a[j]);
+  long long i = 8;
+  const long long m = n - (n % 8);
+  for (; i < m; i += 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = __fadd_rn(r[j], __fmul_rn(a[i + j], a[i + j]));
+  }
+  float res = __fadd_rn(__fadd_rn(__fadd_rn(r[0], r[1]), __fadd_rn(r[2], r[3])),
+                        __fadd_rn(__fadd_rn(r[4], r[5]), __fadd_rn(r[6], r[7])));
+  for (; i < n; ++i) res = __fadd_rn(res, __fmul_rn(a[i], a[i]));
+  return res;
+}
+
+// Post-order walk of the split tree with an explicit stack (depth <= log2(n/64)).
+__device__ float pairwise_sumsq(const float* __restrict__ a, long long n) {
+  struct Frame {
+    long long off, n;
+    float lo;
+    int stage;
+  };
+  Frame st[40];
+  int sp = 0;
+  st[0] = Frame{0, n, 0.f, 0};
+  float ret = 0.f;
+  while (sp >= 0) {
+    Frame& fr = st[sp];
+    if (fr.stage == 0) {
+      if (fr.n <= 128) {
+        ret = leaf_sumsq(a + fr.off, fr.n);
+        --sp;
+        continue;
+      }
+      long long n2 = fr.n / 2;
+      n2 -= n2 % 8;
+      fr.stage = 1;
+      st[sp + 1] = Frame{fr.off, n2, 0.f, 0};
+      ++sp;
+    } else if (fr.stage == 1) {
+      long long n2 = fr.n / 2;
+      n2 -= n2 % 8;
+      fr.lo = ret;
+      fr.stage = 2;
+      st[sp + 1] = Frame{fr.off + n2, fr.n - n2, 0.f, 0};
+      ++sp;
+    } else {
+      ret = __fadd_rn(fr.lo, ret);
+      --sp;
+    }
+  }
+  return ret;
+}
+
+// One thread per unit: norm[mu] = sqrt(sum_i w[mu][i]^2) + prec, all in float.
+__global__ void k_row_norms(const float* __restrict__ w_kn, int K, long long N, float prec, float* __restrict__ norm) {
+  const int mu = blockIdx.x * blockDim.x + threadIdx.x;
+  if (mu >= K) return;
+  const float ss = pairwise_sumsq(w_kn + (size_t)mu * N, N);
+  norm[mu] = __fadd_rn(__fsqrt_rn(ss), prec);
+}
+
+// [K][N] -> [N][Kp], dividing by the unit's norm when norm != nullptr.
+__global__ void k_load_transposed(const float* __restrict__ w_kn, const float* __restrict__ norm,
+                                  float* __restrict__ wt, int K, int Kp, int N) {
+  __shared__ float tile[32][33];
+  const int i0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int mu = m0 + r, i = i0 + threadIdx.x;
+    float v = 0.f;
+    if (mu < K && i < N) {
+      v = w_kn[(size_t)mu * N + i];
+      if (norm) v = __fdiv_rn(v, norm[mu]);
+    }
+    tile[r][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int i = i0 + r, mu = m0 + threadIdx.x;
+    if (i < N && mu < Kp) wt[(size_t)i * Kp + mu] = tile[threadIdx.x][r];
+  }
+}
+__global__ void k_store_untransposed(const float* __restrict__ wt, float* __restrict__ w_kn, int K, int Kp, int N) {
+  __shared__ float tile[32][33];
+  const int i0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int i = i0 + r, mu = m0 + threadIdx.x;
+    tile[r][threadIdx.x] = (i < N && mu < K) ? wt[(size_t)i * Kp + mu] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int mu = m0 + r, i = i0 + threadIdx.x;
+    if (mu < K && i < N) w_kn[(size_t)mu * N + i] = tile[threadIdx.x][r];
+  }
+}
+
+// ---- selection -------------------------------------------------------------
+// Monotone map float -> uint32 (larger float = larger key); 0 is below every
+// non-NaN value and marks the padding columns.
+__device__ __forceinline__ uint32_t f2key(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// MODE 0: token ids (activation = row V+id); MODE 1: windows, weighted by f;
+// MODE 2: windows, raw.
+template <int NT, int MODE>
+__global__ void __launch_bounds__(256) k_hash(HDev h, const int32_t* __restrict__ in, unsigned long long n, int W,
+                                              int hash_len, uint32_t flags, uint8_t* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned long long nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;
+  const int Kq = h.Kq;
+  const bool bytes_out = (flags & FV_HASH_BYTES) != 0;
+  const size_t out_stride = bytes_out ? (size_t)h.K : (size_t)((h.K + 7) / 8);
+
+  for (unsigned long long item = warp; item < n; item += nwarps) {
+    float a[NT][4];
+    bool zero_code = false;
+    if (MODE == 0) {
+      const int id = in[item];
+      if (id < 0 || id >= h.V) {
+        if (lane == 0) atomicOr(h.error, FV_DEVERR_TOKEN_RANGE);
+        zero_code = true;
+      } else if (id == 0 && !(flags & FV_HASH_NO_UNK)) {
+        zero_code = true;  // the unknown token hashes to all zeros (flyvec/core.py:120-125, 151)
+      }
+      const float4* __restrict__ row =
+          reinterpret_cast<const float4*>(h.wt + (size_t)(h.V + (zero_code ? 0 : id)) * h.Kp);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int q = lane + 32 * t;
+        const float4 v = (q < Kq) ? __ldg(row + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        a[t][0] = v.x; a[t][1] = v.y; a[t][2] = v.z; a[t][3] = v.w;
+      }
+    } else {
+      // double sum over the window positions of the (float) weighted term, float store
+      // (flyvec/src/cuda_funcs.cu:289-305; 248-263 for the raw form)
+      const int my = (lane < W) ? in[item * (unsigned long long)W + lane] : -1;
+      if (my >= h.N) {
+        atomicOr(h.error, FV_DEVERR_TOKEN_RANGE);
+      }
+      double acc[NT][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0;
+      for (int c = 0; c < W; ++c) {
+        const int id = __shfl_sync(FULL, my, c);
+        if (id < 0 || id >= h.N) continue;
+        const float sc = (MODE == 1) ? __ldg(h.f + (id % h.V)) : 1.f;
+        const float4* __restrict__ row = reinterpret_cast<const float4*>(h.wt + (size_t)id * h.Kp);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const int q = lane + 32 * t;
+          if (q < Kq) {
+            const float4 v = __ldg(row + q);
+            if (MODE == 1) {
+              acc[t][0] += (double)__fmul_rn(v.x, sc);
+              acc[t][1] += (double)__fmul_rn(v.y, sc);
+              acc[t][2] += (double)__fmul_rn(v.z, sc);
+              acc[t][3] += (double)__fmul_rn(v.w, sc);
+            } else {
+              acc[t][0] += (double)v.x;
+              acc[t][1] += (double)v.y;
+              acc[t][2] += (double)v.z;
+              acc[t][3] += (double)v.w;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a[t][k] = (float)acc[t][k];
+    }
+
+    uint32_t key[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) key[t][k] = (4 * (lane + 32 * t) + k < h.K) ? f2key(a[t][k]) : 0u;
+
+    // hash_len-th largest key: the largest v with #{key >= v} >= hash_len
+    uint32_t kh = 0u;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = kh | (1u << bit);
+      int c = 0;
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) c += (key[t][k] >= cand);
+      c = __reduce_add_sync(FULL, c);
+      if (c >= hash_len) kh = cand;
+    }
+    // the next one in sorted order: kh again if it occurs beyond rank hash_len, else the largest key below it
+    int cge = 0;
+    uint32_t below = 0u;
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        cge += (key[t][k] >= kh);
+        if (key[t][k] < kh) below = max(below, key[t][k]);
+      }
+    cge = __reduce_add_sync(FULL, cge);
+    below = __reduce_max_sync(FULL, below);
+    const uint32_t kn = (cge > hash_len) ? kh : below;
+    const float thr = __fmul_rn(__fadd_rn(key2f(kh), key2f(kn)), 0.5f);
+
+    uint8_t* __restrict__ dst = out + (size_t)item * out_stride;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int q = lane + 32 * t;
+      uint32_t nib = 0u;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (!zero_code && 4 * q + k < h.K && a[t][k] > thr) nib |= 1u << k;
+      if (bytes_out) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (4 * q + k < h.K) dst[4 * q + k] = (uint8_t)((nib >> k) & 1u);
+      } else {
+        const uint32_t hi = __shfl_down_sync(FULL, nib, 1);
+        if (!(lane & 1) && 4 * q < h.K) dst[q >> 1] = (uint8_t)(nib | (hi << 4));
+      }
+    }
+  }
+}
+
+}  // namespace
+
+struct fv_hasher {
+  int device = 0;
+  int num_sms = 0;
+  int NT = 1;
+  HDev h;
+  float* d_wt = nullptr;
+  float* d_f = nullptr;
+  uint32_t* d_err = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+namespace {
+
+#define FV_TRY(expr)                    \
+  do {                                  \
+    int fv_rc_ = (expr);                \
+    if (fv_rc_ != FV_OK) return fv_rc_; \
+  } while (0)
+
+template <int NT>
+void launch_hash(fv_hasher* hs, int mode, int grid, const int32_t* in, unsigned long long n, int W, int hl,
+                 uint32_t flags, uint8_t* out) {
+  if (mode == 0)
+    k_hash<NT, 0><<<grid, 256, 0, hs->stream>>>(hs->h, in, n, W, hl, flags, out);
+  else if (mode == 1)
+    k_hash<NT, 1><<<grid, 256, 0, hs->stream>>>(hs->h, in, n, W, hl, flags, out);
+  else
+    k_hash<NT, 2><<<grid, 256, 0, hs->stream>>>(hs->h, in, n, W, hl, flags, out);
+}
+
+int run_hash(fv_hasher* hs, int mode, const int32_t* d_in, unsigned long long n, int W, uint32_t hash_len,
+             uint32_t flags, uint8_t* d_out, double* seconds) {
+  FV_REQUIRE(hash_len >= 1 && (int)hash_len < hs->h.K, FV_ERR_INVALID,
+             "hash_length must be in [1, K-1] (K = %d), got %u", hs->h.K, hash_len);
+  if (seconds) *seconds = 0.0;
+  if (n == 0) return FV_OK;
+  unsigned long long blocks = (n + 7) / 8;
+  const unsigned long long cap = (unsigned long long)hs->num_sms * 8;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  FV_CUDA(cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream));
+  FV_CUDA(cudaEventRecord(hs->ev0, hs->stream));
+  switch (hs->NT) {
+    case 1: launch_hash<1>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 2: launch_hash<2>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 3: launch_hash<3>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 4: launch_hash<4>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 5: launch_hash<5>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 6: launch_hash<6>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 7: launch_hash<7>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    default: launch_hash<8>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+  }
+  FV_CUDA(cudaGetLastError());
+  FV_CUDA(cudaEventRecord(hs->ev1, hs->stream));
+  uint32_t err = 0;
+  FV_CUDA(cudaMemcpyAsync(&err, hs->d_err, sizeof(err), cudaMemcpyDeviceToHost, hs->stream));
+  FV_CUDA(cudaStreamSynchronize(hs->stream));
+  if (seconds) {
+    float ms = 0.f;
+    FV_CUDA(cudaEventElapsedTime(&ms, hs->ev0, hs->ev1));
+    *seconds = ms * 1e-3;
+  }
+  if (err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "an input id was out of range (device check)");
+  return FV_OK;
+}
+
+void free_hasher(fv_hasher* hs) {
+  cudaSetDevice(hs->device);
+  if (hs->d_wt) cudaFree(hs->d_wt);
+  if (hs->d_f) cudaFree(hs->d_f);
+  if (hs->d_err) cudaFree(hs->d_err);
+  if (hs->ev0) cudaEventDestroy(hs->ev0);
+  if (hs->ev1) cudaEventDestroy(hs->ev1);
+  if (hs->stream) cudaStreamDestroy(hs->stream);
+  delete hs;
+}
+
+int create_hasher(fv_hasher* hs, const float* w_kn, int K, int N, int normalize, float prec, int device) {
+  hs->device = device;
+  FV_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  FV_CUDA(cudaGetDeviceProperties(&prop, device));
+  hs->num_sms = prop.multiProcessorCount;
+  FV_CUDA(cudaStreamCreateWithFlags(&hs->stream, cudaStreamNonBlocking));
+  FV_CUDA(cudaEventCreate(&hs->ev0));
+  FV_CUDA(cudaEventCreate(&hs->ev1));
+  HDev& h = hs->h;
+  h.K = K;
+  h.Kp = (K + 3) & ~3;
+  h.Kq = h.Kp / 4;
+  h.N = N;
+  h.V = N / 2;
+  h.f = nullptr;
+  hs->NT = (h.Kq + 31) / 32;
+  FV_CUDA(cudaMalloc((void**)&hs->d_wt, (size_t)N * h.Kp * sizeof(float)));
+  FV_CUDA(cudaMalloc((void**)&hs->d_err, sizeof(uint32_t)));
+  h.wt = hs->d_wt;
+  h.error = hs->d_err;
+  float* tmp = nullptr;
+  float* norm = nullptr;
+  FV_CUDA(cudaMalloc((void**)&tmp, (size_t)K * N * sizeof(float)));
+  cudaError_t e = cudaMemcpyAsync(tmp, w_kn, (size_t)K * N * sizeof(float), cudaMemcpyHostToDevice, hs->stream);
+  if (e == cudaSuccess && normalize) {
+    e = cudaMalloc((void**)&norm, (size_t)K * sizeof(float));
+    if (e == cudaSuccess) {
+      k_row_norms<<<(K + 31) / 32, 32, 0, hs->stream>>>(tmp, K, (long long)N, prec, norm);
+      e = cudaGetLastError();
+    }
+  }
+  if (e == cudaSuccess) {
+    dim3 grid((N + 31) / 32, (h.Kp + 31) / 32), block(32, 8);
+    k_load_transposed<<<grid, block, 0, hs->stream>>>(tmp, norm, hs->d_wt, K, h.Kp, N);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(hs->stream);
+  cudaFree(tmp);
+  if (norm) cudaFree(norm);
+  FV_CUDA(e);
+  return FV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fv_hasher_create(const float* w_kn, uint32_t hid, uint32_t n_cols, int normalize, float prec, int device,
+                     fv_hasher** out) {
+  FV_REQUIRE(w_kn && out, FV_ERR_INVALID, "fv_hasher_create: NULL argument");
+  *out = nullptr;
+  FV_REQUIRE(hid >= 2 && hid <= 1024, FV_ERR_INVALID, "hid must be in [2, 1024], got %u", hid);
+  FV_REQUIRE(n_cols >= 2 && n_cols % 2 == 0 && n_cols <= (1u << 30), FV_ERR_INVALID,
+             "the synapse matrix needs an even number of columns (context half, target half), got %u", n_cols);
+  int ndev = 0;
+  FV_CUDA(cudaGetDeviceCount(&ndev));
+  FV_REQUIRE(device >= 0 && device < ndev, FV_ERR_INVALID, "device %d not present (%d devices)", device, ndev);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  fv_hasher* hs = new fv_hasher();
+  const int rc = create_hasher(hs, w_kn, (int)hid, (int)n_cols, normalize, prec, device);
+  if (rc != FV_OK) {
+    free_hasher(hs);
+    cudaSetDevice(prev);
+    return rc;
+  }
+  cudaSetDevice(prev);
+  *out = hs;
+  return FV_OK;
+}
+
+int fv_hasher_destroy(fv_hasher* h) {
+  if (!h) return FV_OK;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(h->device);
+  cudaDeviceSynchronize();
+  free_hasher(h);
+  cudaSetDevice(prev);
+  return FV_OK;
+}
+
+int fv_hasher_get_weights(fv_hasher* hs, float* w_kn) {
+  FV_REQUIRE(hs && w_kn, FV_ERR_INVALID, "fv_hasher_get_weights: NULL argument");
+  fv::DeviceGuard guard(hs->device);
+  const HDev& h = hs->h;
+  float* tmp = nullptr;
+  FV_CUDA(cudaMalloc((void**)&tmp, (size_t)h.K * h.N * sizeof(float)));
+  dim3 grid((h.N + 31) / 32, (h.Kp + 31) / 32), block(32, 8);
+  k_store_untransposed<<<grid, block, 0, hs->stream>>>(h.wt, tmp, h.K, h.Kp, h.N);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(w_kn, tmp, (size_t)h.K * h.N * sizeof(float), cudaMemcpyDeviceToHost, hs->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(hs->stream);
+  cudaFree(tmp);
+  FV_CUDA(e);
+  return FV_OK;
+}
+
+int fv_hasher_set_inverse_frequency(fv_hasher* hs, const float* inv_freq, uint32_t vocab) {
+  FV_REQUIRE(hs && inv_freq, FV_ERR_INVALID, "fv_hasher_set_inverse_frequency: NULL argument");
+  FV_REQUIRE((int)vocab == hs->h.V, FV_ERR_INVALID, "inverse frequency table has %u entries, vocabulary is %d", vocab,
+             hs->h.V);
+  fv::DeviceGuard guard(hs->device);
+  if (!hs->d_f) FV_CUDA(cudaMalloc((void**)&hs->d_f, (size_t)vocab * sizeof(float)));
+  FV_CUDA(cudaMemcpy(hs->d_f, inv_freq, (size_t)vocab * sizeof(float), cudaMemcpyHostToDevice));
+  hs->h.f = hs->d_f;
+  return FV_OK;
+}
+
+int fv_hash_tokens_device(fv_hasher* hs, const int32_t* d_ids, uint64_t n, uint32_t hash_length, uint32_t flags,
+                          uint8_t* d_out, double* kernel_seconds) {
+  FV_REQUIRE(hs && (n == 0 || (d_ids && d_out)), FV_ERR_INVALID, "fv_hash_tokens_device: NULL argument");
+  fv::DeviceGuard guard(hs->device);
+  return run_hash(hs, 0, d_ids, n, 0, hash_length, flags, d_out, kernel_seconds);
+}
+
+int fv_hash_windows_device(fv_hasher* hs, const int32_t* d_idx, uint64_t nwin, uint32_t window, int weighted,
+                           uint32_t hash_length, uint32_t flags, uint8_t* d_out, double* kernel_seconds) {
+  FV_REQUIRE(hs && (nwin == 0 || (d_idx && d_out)), FV_ERR_INVALID, "fv_hash_windows_device: NULL argument");
+  FV_REQUIRE(window >= 1 && window <= 32, FV_ERR_INVALID, "window must be in [1, 32], got %u", window);
+  if (weighted) FV_REQUIRE(hs->h.f != nullptr, FV_ERR_STATE, "weighted window hashing needs an inverse frequency table");
+  fv::DeviceGuard guard(hs->device);
+  return run_hash(hs, weighted ? 1 : 2, d_idx, nwin, (int)window, hash_length, flags, d_out, kernel_seconds);
+}
+
+// Host-buffer forms: upload, hash, download.
+static int hash_host(fv_hasher* hs, int mode, const int32_t* in, uint64_t n, size_t in_per_item, uint32_t window,
+                     uint32_t hash_length, uint32_t flags, uint8_t* out) {
+  if (n == 0) return FV_OK;
+  fv::DeviceGuard guard(hs->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", hs->device);
+  const size_t out_per = (flags & FV_HASH_BYTES) ? (size_t)hs->h.K : (size_t)((hs->h.K + 7) / 8);
+  int32_t* d_in = nullptr;
+  uint8_t* d_out = nullptr;
+  FV_CUDA(cudaMalloc((void**)&d_in, n * in_per_item * sizeof(int32_t)));
+  cudaError_t e = cudaMalloc((void**)&d_out, n * out_per);
+  int rc = FV_OK;
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(d_in, in, n * in_per_item * sizeof(int32_t), cudaMemcpyHostToDevice, hs->stream);
+  if (e == cudaSuccess) rc = run_hash(hs, mode, d_in, n, (int)window, hash_length, flags, d_out, nullptr);
+  if (e == cudaSuccess && rc == FV_OK) e = cudaMemcpy(out, d_out, n * out_per, cudaMemcpyDeviceToHost);
+  cudaFree(d_in);
+  if (d_out) cudaFree(d_out);
+  if (rc != FV_OK) return rc;
+  FV_CUDA(e);
+  return FV_OK;
+}
+
+int fv_hash_tokens(fv_hasher* hs, const int32_t* ids, uint64_t n, uint32_t hash_length, uint32_t flags, uint8_t* out) {
+  FV_REQUIRE(hs && (n == 0 || (ids && out)), FV_ERR_INVALID, "fv_hash_tokens: NULL argument");
+  FV_REQUIRE(hash_length >= 1 && (int)hash_length < hs->h.K, FV_ERR_INVALID,
+             "hash_length must be in [1, K-1] (K = %d), got %u", hs->h.K, hash_length);
+  return hash_host(hs, 0, ids, n, 1, 0, hash_length, flags, out);
+}
+
+int fv_hash_windows(fv_hasher* hs, const int32_t* idx, uint64_t nwin, uint32_t window, const float* inv_freq,
+                    uint32_t hash_length, uint32_t flags, uint8_t* out) {
+  FV_REQUIRE(hs && (nwin == 0 || (idx && out)), FV_ERR_INVALID, "fv_hash_windows: NULL argument");
+  FV_REQUIRE(window >= 1 && window <= 32, FV_ERR_INVALID, "window must be in [1, 32], got %u", window);
+  FV_REQUIRE(hash_length >= 1 && (int)hash_length < hs->h.K, FV_ERR_INVALID,
+             "hash_length must be in [1, K-1] (K = %d), got %u", hs->h.K, hash_length);
+  const bool raw = (flags & FV_HASH_RAW) || inv_freq == nullptr;
+  if (!raw) FV_TRY(fv_hasher_set_inverse_frequency(hs, inv_freq, (uint32_t)hs->h.V));
+  return hash_host(hs, raw ? 2 : 1, idx, nwin, window, window, hash_length, flags, out);
+}
+
+}  // extern "C"

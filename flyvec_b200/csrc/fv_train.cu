@@ -1,0 +1,1357 @@
+// FlyVec trainer for sm_100a: one handle = one GPU = one data-parallel rank.
+//
+// Data layout in HBM
+//   wt      float [N][Kp]   transposed synapses: row i holds the Kp (K padded to a
+//                           multiple of 4) weights of input i, so the activation of
+//                           a window is a sum of w contiguous rows.
+//   alpha   double[2][Kp]   per-unit scale; the synapse matrix is alpha[mu]*wt[i][mu].
+//                           The dense part of the Hebbian update, W_mu *= (1 - s*X_mu),
+//                           only touches alpha; wt changes at the scattered positions.
+//   tokens, wstart, perm    corpus, window starts, window order.
+//   idx     int  [G*B][w]   input ids of the current global step (all ranks' windows).
+//   pkt     u32  [G][B+Kp]  per rank: B winners then Kp floats of xx; all-gathered.
+//   cnt/saved   [G*B*w]     scatter bookkeeping, one slot per (window, position).
+//
+// One global step (reference: run_epoch, flyvec/src/cuda_funcs.cu:1662-1812):
+//   k_build_idx  T4   window -> input ids                    (cuda_funcs.cu:915-936)
+//   k_forward    T6-8 gather-sum, arg-max, weighted winner    (cuda_funcs.cu:248-305, 488-561, 722-744)
+//   k_xx         T8   xx[mu] = sum of weighted winning activations, fixed order
+//   all-gather        winners + xx of every rank (NCCL)
+//   k_tag        T10  each touched (mu,i) gets one owner slot; its weight is parked in
+//                     `saved` and replaced by a tagged NaN     (cuda_funcs.cu:657-672)
+//   k_scan       T11  nc = max|D|: exact D at touched positions, column max of |wt|
+//                     over untouched ones (tags read as 0)     (cu_special_reduction.cu:26-99)
+//   k_apply      T12-13 s = eps/max(prec,nc); alpha *= 1 - s*X; touched weights restored
+//                     plus their scatter term                  (cuda_funcs.cu:1797-1799,
+//                                                               cu_special_reduction.cu:316-354)
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "fv_common.h"
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+constexpr uint32_t TAG_BASE = 0x7f800000u;  // exponent all ones: tag = TAG_BASE | (slot+1)
+constexpr uint32_t ABS_MASK = 0x7fffffffu;
+constexpr int MAX_K = 1024;
+
+struct StepCtl {
+  unsigned long long base;  // schedule index of the step launched with local == 0
+  unsigned long long tick;  // steps executed since the weights were last folded (selects the alpha buffer)
+  float eps;
+  uint32_t error;
+};
+
+// Everything a kernel needs, passed by value.
+struct Dev {
+  int K, Kp, Kq, V, N, W, B, G, rank, P;
+  unsigned long long Ns, ntok;
+  float prec;
+  uint32_t flags;
+  float* wt;
+  double* alpha;
+  const int32_t* tokens;
+  const unsigned long long* wstart;
+  const unsigned long long* perm;
+  const float* f;
+  uint32_t* pkt_send;
+  uint32_t* pkt_recv;
+  float* aw;
+  int32_t* cnt;
+  float* saved;
+  uint32_t* colmax;
+  uint32_t* ncb;
+  StepCtl* ctl;
+  float* nc_log;
+  float* s_log;
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
+  return v;
+}
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) { return __reduce_max_sync(FULL, v); }
+
+// ---------------------------------------------------------------------------
+// control word
+// ---------------------------------------------------------------------------
+__global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps) {
+  ctl->base = base;
+  ctl->eps = eps;
+}
+__global__ void k_advance(StepCtl* ctl, unsigned long long n) {
+  ctl->base += n;
+  ctl->tick += n;
+}
+
+// ---------------------------------------------------------------------------
+// T4: input ids of every window of the global step (all ranks' blocks).
+// Absent windows (past the end of the order) are marked -2 in every position.
+// ---------------------------------------------------------------------------
+__global__ void k_build_idx(Dev d, int local, int32_t* __restrict__ idx) {
+  const unsigned long long step = d.ctl->base + local;
+  const int total = d.G * d.B * d.W;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+    const int q = e / d.W, c = e - q * d.W;
+    const unsigned long long pos = step * (unsigned long long)d.G * d.B + q;
+    int val = -2;
+    if (pos < d.Ns) {
+      const unsigned long long p = d.perm[pos];
+      if (p >= d.Ns) {
+        atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
+      } else {
+        const unsigned long long s = d.wstart[p];
+        if (s + d.W > d.ntok) {
+          atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
+        } else {
+          const int tok = d.tokens[s + c];
+          if (tok < 0) {
+            val = -1;
+          } else if (tok >= d.V) {
+            atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
+            val = -1;
+          } else {
+            val = tok + (c == d.W / 2 ? d.V : 0);
+          }
+        }
+      }
+    }
+    idx[e] = val;
+  }
+}
+
+// Checks host-supplied input ids (streaming mode) against [ -2, N ).
+__global__ void k_check_idx(Dev d, const int32_t* __restrict__ idx, size_t total) {
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const int v = idx[e];
+    if (v >= d.N || v < -2) atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Forward pass.  One warp per window; lane l owns the float4 column groups
+// l, l+32, ... of a row.  The winner is selected on the raw (unweighted)
+// activation, the Hebbian coefficient uses the 1/count-weighted one
+// (cuda_funcs.cu:1716-1721).
+//
+// Arithmetic.  The reference sums each unit in double over c = 0..w-1 and rounds
+// to float (cuda_funcs.cu:252-260).  The fast path sums in float and also tracks
+// the largest |term| it saw; sequential float summation of w terms bounded by
+// xmax is off by at most w*w*2^-24*xmax, so when the gap between the two largest
+// activations exceeds four times that bound (plus the rounding of the scale
+// product) the arg-max of the float sums is the arg-max of the exact sums.
+// Otherwise -- about one window in 10^4 -- the warp redoes the window in double
+// with the reference's tie order (smallest (index % 64, index) among equal
+// maxima, cuda_funcs.cu:507-540).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool better(float a, int ia, float b, int ib) {
+  // true when (a, ia) beats (b, ib) under the reference's tie order
+  if (a > b) return true;
+  if (a < b) return false;
+  const int ka = ((ia & 63) << 20) | ia, kb = ((ib & 63) << 20) | ib;
+  return ka < kb;
+}
+
+template <int NT>
+__device__ __noinline__ int exact_winner(const Dev& d, const double* __restrict__ alpha, int my, int lane, int skip) {
+  float best = -INFINITY;
+  int bi = 0x000fffff;
+  const int Kq = d.Kq;
+  for (int t = 0; t < NT; ++t) {
+    const int q = lane + 32 * t;
+    double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    for (int c = 0; c < d.W; ++c) {
+      const int id = __shfl_sync(FULL, my, c);
+      if (id < 0 || q >= Kq) continue;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(d.wt + (size_t)id * d.Kp) + q);
+      s0 += (double)v.x;
+      s1 += (double)v.y;
+      s2 += (double)v.z;
+      s3 += (double)v.w;
+    }
+    if (q < Kq) {
+      const int mu = 4 * q;
+      const double s[4] = {s0, s1, s2, s3};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (mu + k < d.K && mu + k != skip) {
+          const float a = (float)(s[k] * alpha[mu + k]);
+          if (better(a, mu + k, best, bi)) {
+            best = a;
+            bi = mu + k;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const float ob = __shfl_xor_sync(FULL, best, o);
+    const int oi = __shfl_xor_sync(FULL, bi, o);
+    if (better(ob, oi, best, bi)) {
+      best = ob;
+      bi = oi;
+    }
+  }
+  return bi;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(256) k_forward(Dev d, int local, const int32_t* __restrict__ idx) {
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
+  const int Kq = d.Kq;
+
+  float af[NT][4];
+  float amax = 0.f;
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int q = lane + 32 * t;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      af[t][k] = (q < Kq) ? (float)alpha[4 * q + k] : 0.f;
+      amax = fmaxf(amax, fabsf(af[t][k]));
+    }
+  }
+  amax = warp_max(amax);
+  // theta = tol * xmax; 2^-24 = 5.9604645e-8
+  const float tol = 4.0f * (float)(d.W * d.W + 2 * d.W + 4) * 5.9604645e-8f * amax;
+  const bool force64 = (d.flags & FV_FLAG_ACC_FP64) != 0;
+
+  const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.B * d.W;
+  int32_t* __restrict__ win_out = reinterpret_cast<int32_t*>(d.pkt_send);
+
+  for (int j = warp; j < d.B; j += nwarps) {
+    const int my = (lane < d.W) ? idx_own[(size_t)j * d.W + lane] : -1;
+    if (__shfl_sync(FULL, my, 0) == -2) {  // absent window
+      if (lane == 0) {
+        win_out[j] = -1;
+        d.aw[j] = 0.f;
+      }
+      continue;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+    float xmax = 0.f;
+#pragma unroll 2
+    for (int c = 0; c < d.W; ++c) {
+      const int id = __shfl_sync(FULL, my, c);
+      if (id < 0) continue;
+      const float4* __restrict__ row = reinterpret_cast<const float4*>(d.wt + (size_t)id * d.Kp);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int q = lane + 32 * t;
+        if (q < Kq) {
+          const float4 v = __ldg(row + q);
+          acc[t][0] += v.x;
+          acc[t][1] += v.y;
+          acc[t][2] += v.z;
+          acc[t][3] += v.w;
+          xmax = fmaxf(xmax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+      }
+    }
+    // two largest scaled activations of this lane, then of the warp
+    float b1 = -INFINITY, b2 = -INFINITY;
+    int i1 = 0;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int q = lane + 32 * t;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int mu = 4 * q + k;
+        if (mu < d.K) {
+          const float a = acc[t][k] * af[t][k];
+          if (a > b1) {
+            b2 = b1;
+            b1 = a;
+            i1 = mu;
+          } else if (a > b2) {
+            b2 = a;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+      const float ob1 = __shfl_xor_sync(FULL, b1, o);
+      const float ob2 = __shfl_xor_sync(FULL, b2, o);
+      const int oi1 = __shfl_xor_sync(FULL, i1, o);
+      if (ob1 > b1) {
+        b2 = fmaxf(b1, ob2);
+        b1 = ob1;
+        i1 = oi1;
+      } else {
+        b2 = fmaxf(b2, ob1);
+      }
+    }
+    xmax = warp_max(xmax);
+    int winner = i1;
+    if (force64 || !((b1 - b2) > tol * xmax)) winner = exact_winner<NT>(d, alpha, my, lane, -1);
+
+    // weighted activation of the winner: float product with 1/count, double sum over c
+    float x = 0.f;
+    if (lane < d.W && my >= 0) {
+      const float wv = (float)((double)d.wt[(size_t)my * d.Kp + winner] * alpha[winner]);
+      x = wv * __ldg(d.f + (my % d.V));
+    }
+    double s = 0.0;
+    for (int c = 0; c < d.W; ++c) {
+      const float xc = __shfl_sync(FULL, x, c);
+      const int idc = __shfl_sync(FULL, my, c);
+      if (idc >= 0) s += (double)xc;
+    }
+    if (lane == 0) {
+      win_out[j] = winner;
+      d.aw[j] = (float)s;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// xx[mu] = sum over this rank's windows won by mu of the weighted activation
+// (cuda_funcs.cu:722-744 does this with float atomics in arbitrary order; here
+// the order is fixed: lane-strided partial sums, then a butterfly).
+// One warp per unit; written behind the winners in the outgoing packet.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_xx(Dev d) {
+  const int lane = threadIdx.x & 31;
+  const int mu = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (mu >= d.Kp) return;
+  const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(d.pkt_send);
+  float acc = 0.f;
+  if (mu < d.K)
+    for (int j = lane; j < d.B; j += 32)
+      if (win[j] == mu) acc += d.aw[j];
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(FULL, acc, o);
+  if (lane == 0) reinterpret_cast<float*>(d.pkt_send)[d.B + mu] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// T10 bookkeeping.  Every (window, position) of every rank is a slot e.  The
+// first slot to reach a matrix position (i, mu) becomes its owner: it parks the
+// weight in saved[e] and leaves TAG_BASE|(e+1) -- a NaN bit pattern no weight
+// can have -- in its place; later slots for the same position find the tag and
+// bump the owner's count.  A slot is skipped when its rank's xx[mu] is zero: the
+// reference drops a replica's whole row from the combine in that case
+// (cu_special_reduction.cu:42-66).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_tag(Dev d, const int32_t* __restrict__ idx) {
+  const int E = d.G * d.B * d.W;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
+    const int i = idx[e];
+    if (i < 0) continue;
+    const int q = e / d.W;
+    const int r = q / d.B, j = q - r * d.B;
+    const uint32_t* __restrict__ pkt = d.pkt_recv + (size_t)r * d.P;
+    const int mu = (int)pkt[j];
+    if (mu < 0) continue;
+    if (__uint_as_float(pkt[d.B + mu]) == 0.f) continue;
+    uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt + (size_t)i * d.Kp + mu);
+    uint32_t cur = __ldcg(addr);
+    const uint32_t tag = TAG_BASE | (uint32_t)(e + 1);
+    for (;;) {
+      if ((cur & ABS_MASK) > TAG_BASE) {
+        const uint32_t owner = (cur & 0x007fffffu) - 1u;
+        if ((cur >> 31) || owner >= (uint32_t)E) {
+          atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+        } else {
+          atomicAdd(&d.cnt[owner], 1);
+        }
+        break;
+      }
+      const uint32_t prev = atomicCAS(addr, cur, tag);
+      if (prev == cur) {
+        d.saved[e] = __uint_as_float(cur);
+        atomicAdd(&d.cnt[e], 1);
+        break;
+      }
+      cur = prev;
+    }
+  }
+}
+
+// Per-unit combine over ranks: n = number of ranks with xx != 0, X = mean of xx
+// over those ranks (the closed form of cu_special_reduction.cu:42-67 applied to
+// the -xx*W term).
+__device__ __forceinline__ void unit_stats(const Dev& d, int mu, double* X, int* n) {
+  double sum = 0.0;
+  int cnt = 0;
+  for (int r = 0; r < d.G; ++r) {
+    const float x = __uint_as_float(d.pkt_recv[(size_t)r * d.P + d.B + mu]);
+    if (x != 0.f) {
+      sum += (double)x;
+      ++cnt;
+    }
+  }
+  *n = cnt;
+  *X = cnt ? sum / (double)cnt : 0.0;
+}
+
+// ---------------------------------------------------------------------------
+// T11.  nc = max |D| with D = -X*W + S.
+//   part 1: owners evaluate D at their (touched) position -> ncb (scalar max);
+//   part 2: column maxima of |wt| over the untouched positions (tags read as 0)
+//           -> colmax; the dense term's maximum is |X*alpha| * colmax.
+// Non-negative floats order like their bit patterns, so maxima are integer.
+// ---------------------------------------------------------------------------
+template <int NT>
+__global__ void __launch_bounds__(256) k_scan(Dev d, int local, const int32_t* __restrict__ idx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* sC = reinterpret_cast<double*>(smem_raw);          // X*alpha
+  int* sN = reinterpret_cast<int*>(sC + d.Kp);               // active ranks
+  uint32_t* sMax = reinterpret_cast<uint32_t*>(sN + d.Kp);   // CTA column maxima
+  const int p = (int)((d.ctl->tick + local) & 1);
+  const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    double X = 0.0;
+    int n = 0;
+    if (mu < d.K) unit_stats(d, mu, &X, &n);
+    sC[mu] = X * alpha[mu];
+    sN[mu] = n;
+    sMax[mu] = 0u;
+  }
+  __syncthreads();
+
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nthreads = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+
+  // part 1
+  {
+    const int E = d.G * d.B * d.W;
+    uint32_t tmax = 0u;
+    for (int e = tid; e < E; e += nthreads) {
+      const int c = d.cnt[e];
+      if (c <= 0) continue;
+      const int i = idx[e];
+      const int q = e / d.W;
+      const int r = q / d.B, j = q - r * d.B;
+      const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
+      const double D = -sC[mu] * (double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) / (double)sN[mu];
+      tmax = max(tmax, __float_as_uint(fabsf((float)D)));
+    }
+    tmax = warp_max_u32(tmax);
+    if (lane == 0 && tmax) atomicMax(&d.ncb[p], tmax);
+  }
+
+  // part 2
+  {
+    const int warp = tid >> 5, nwarps = nthreads >> 5;
+    const int Kq = d.Kq;
+    uint32_t m[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) m[t][0] = m[t][1] = m[t][2] = m[t][3] = 0u;
+    auto fold_in = [&](int t, const uint4& v) {
+      uint32_t u;
+      u = v.x & ABS_MASK; m[t][0] = max(m[t][0], u > TAG_BASE ? 0u : u);
+      u = v.y & ABS_MASK; m[t][1] = max(m[t][1], u > TAG_BASE ? 0u : u);
+      u = v.z & ABS_MASK; m[t][2] = max(m[t][2], u > TAG_BASE ? 0u : u);
+      u = v.w & ABS_MASK; m[t][3] = max(m[t][3], u > TAG_BASE ? 0u : u);
+    };
+    int row = warp;
+    for (; row + nwarps < d.N; row += 2 * nwarps) {
+      const uint4* __restrict__ r0 = reinterpret_cast<const uint4*>(d.wt + (size_t)row * d.Kp);
+      const uint4* __restrict__ r1 = reinterpret_cast<const uint4*>(d.wt + (size_t)(row + nwarps) * d.Kp);
+      uint4 v0[NT], v1[NT];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int q = lane + 32 * t;
+        if (q < Kq) {
+          v0[t] = __ldcg(r0 + q);
+          v1[t] = __ldcg(r1 + q);
+        } else {
+          v0[t] = make_uint4(0, 0, 0, 0);
+          v1[t] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        fold_in(t, v0[t]);
+        fold_in(t, v1[t]);
+      }
+    }
+    for (; row < d.N; row += nwarps) {
+      const uint4* __restrict__ r0 = reinterpret_cast<const uint4*>(d.wt + (size_t)row * d.Kp);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int q = lane + 32 * t;
+        if (q < Kq) fold_in(t, __ldcg(r0 + q));
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int q = lane + 32 * t;
+      if (q < Kq) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (m[t][k]) atomicMax(&sMax[4 * q + k], m[t][k]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x)
+    if (sMax[mu]) atomicMax(&d.colmax[p * d.Kp + mu], sMax[mu]);
+}
+
+// ---------------------------------------------------------------------------
+// T12 + T13.  Every CTA derives nc and the step size from the K column maxima
+// (cheap) and then walks its share of the slots: owners write
+//   wt = saved + cnt * f_i * s / (n * alpha')      with alpha' = alpha * (1 - s*X)
+// and clear their count.  CTA 0 publishes alpha' and the step's nc and s, and
+// clears the maxima the next step will accumulate into.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* sCoef = reinterpret_cast<double*>(smem_raw);  // s / (n * alpha')
+  __shared__ float sRed[8];
+  __shared__ float sScale;
+  const int p = (int)((d.ctl->tick + local) & 1);
+  const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  double* __restrict__ alpha_next = d.alpha + (p ^ 1) * d.Kp;
+
+  float dense = 0.f;
+  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x) {
+    double X;
+    int n;
+    unit_stats(d, mu, &X, &n);
+    if (n > 0) dense = fmaxf(dense, (float)(fabs(X * alpha[mu]) * (double)__uint_as_float(d.colmax[p * d.Kp + mu])));
+  }
+  dense = warp_max(dense);
+  if ((threadIdx.x & 31) == 0) sRed[threadIdx.x >> 5] = dense;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float nc = __uint_as_float(d.ncb[p]);
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) nc = fmaxf(nc, sRed[w]);
+    const float eps = d.ctl->eps;
+    const float s = (d.prec > nc) ? eps / d.prec : eps / nc;  // cuda_funcs.cu:1797-1799
+    sScale = s;
+    if (blockIdx.x == 0) {
+      d.nc_log[local] = nc;
+      d.s_log[local] = s;
+    }
+  }
+  __syncthreads();
+  const float s = sScale;
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    double X = 0.0;
+    int n = 0;
+    if (mu < d.K) unit_stats(d, mu, &X, &n);
+    double a = alpha[mu];
+    double coef = 0.0;
+    if (n > 0) {
+      a = a * (1.0 - (double)s * X);
+      if (a != 0.0)
+        coef = (double)s / ((double)n * a);
+      else
+        atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+    }
+    sCoef[mu] = coef;
+    if (blockIdx.x == 0) {
+      alpha_next[mu] = a;
+      d.colmax[(p ^ 1) * d.Kp + mu] = 0u;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.ncb[p ^ 1] = 0u;
+  __syncthreads();
+
+  const int E = d.G * d.B * d.W;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
+    const int c = d.cnt[e];
+    if (c <= 0) continue;
+    const int i = idx[e];
+    const int q = e / d.W;
+    const int r = q / d.B, j = q - r * d.B;
+    const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
+    d.wt[(size_t)i * d.Kp + mu] = (float)((double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) * sCoef[mu]);
+    d.cnt[e] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Folding the scale into the weights: wt[i][mu] *= alpha[mu]; then alpha = 1.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
+  // `local` = steps already launched in this call: the buffer the next step would read
+  const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
+  const size_t total = (size_t)d.N * d.Kq;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (size_t)gridDim.x * blockDim.x) {
+    const int q = (int)(v % d.Kq);
+    float4* ptr = reinterpret_cast<float4*>(d.wt) + v;
+    float4 x = *ptr;
+    x.x = (float)((double)x.x * alpha[4 * q + 0]);
+    x.y = (float)((double)x.y * alpha[4 * q + 1]);
+    x.z = (float)((double)x.z * alpha[4 * q + 2]);
+    x.w = (float)((double)x.w * alpha[4 * q + 3]);
+    *ptr = x;
+  }
+}
+__global__ void k_reset_alpha(Dev d) {
+  // both buffers become 1, so the parity of the next step does not matter
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 2 * d.Kp; i += gridDim.x * blockDim.x) d.alpha[i] = 1.0;
+}
+
+// ---------------------------------------------------------------------------
+// Layout changes between the checkpoint layout [K][N] and wt [N][Kp].
+// ---------------------------------------------------------------------------
+__global__ void k_to_device_layout(const float* __restrict__ w_kn, float* __restrict__ wt, int K, int Kp, int N) {
+  __shared__ float tile[32][33];
+  const int i0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int mu = m0 + r, i = i0 + threadIdx.x;
+    tile[r][threadIdx.x] = (mu < K && i < N) ? w_kn[(size_t)mu * N + i] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int i = i0 + r, mu = m0 + threadIdx.x;
+    if (i < N && mu < Kp) wt[(size_t)i * Kp + mu] = tile[threadIdx.x][r];
+  }
+}
+__global__ void k_to_host_layout(const float* __restrict__ wt, float* __restrict__ w_kn, int K, int Kp, int N) {
+  __shared__ float tile[32][33];
+  const int i0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int i = i0 + r, mu = m0 + threadIdx.x;
+    tile[r][threadIdx.x] = (i < N && mu < K) ? wt[(size_t)i * Kp + mu] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int mu = m0 + r, i = i0 + threadIdx.x;
+    if (mu < K && i < N) w_kn[(size_t)mu * N + i] = tile[threadIdx.x][r];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Seeded window order: a keyed bijection of [0, n) (balanced Feistel network on
+// 2*half bits, cycle-walked into range), evaluated independently per index.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mix32(uint32_t x, uint32_t k) {
+  x ^= k;
+  x *= 0x85ebca6bu;
+  x ^= x >> 13;
+  x *= 0xc2b2ae35u;
+  x ^= x >> 16;
+  return x;
+}
+__global__ void k_feistel_perm(unsigned long long* __restrict__ perm, unsigned long long n, int half,
+                               unsigned long long seed) {
+  const unsigned long long mask = (1ull << half) - 1ull;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (unsigned long long)gridDim.x * blockDim.x) {
+    unsigned long long x = i;
+    do {
+      uint32_t L = (uint32_t)(x >> half), R = (uint32_t)(x & mask);
+#pragma unroll
+      for (int r = 0; r < 6; ++r) {
+        const uint32_t k = (uint32_t)(seed >> ((r & 1) * 32)) + 0x9e3779b9u * (uint32_t)(r + 1);
+        const uint32_t F = mix32(R, k) & (uint32_t)mask;
+        const uint32_t nl = R;
+        R = L ^ F;
+        L = nl;
+      }
+      x = ((unsigned long long)L << half) | R;
+    } while (x >= n);
+    perm[i] = x;
+  }
+}
+__global__ void k_iota(unsigned long long* __restrict__ perm, unsigned long long n) {
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (unsigned long long)gridDim.x * blockDim.x)
+    perm[i] = i;
+}
+
+// ---------------------------------------------------------------------------
+// NCCL, bound at run time so that a single-GPU process never needs it.
+// ---------------------------------------------------------------------------
+struct Id128 {
+  char bytes[128];
+};
+struct NcclApi {
+  void* lib = nullptr;
+  int (*GetUniqueId)(Id128*) = nullptr;
+  int (*CommInitRank)(void**, int, Id128, int) = nullptr;  // the id travels by value
+  int (*CommDestroy)(void*) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+};
+NcclApi g_nccl;
+
+int load_nccl() {
+  if (g_nccl.lib) return FV_OK;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  void* lib = nullptr;
+  for (const char* n : names) {
+    lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (lib) break;
+  }
+  if (!lib) return fv::fail(FV_ERR_COMM, "NCCL not found: %s", dlerror());
+  NcclApi api;
+  api.lib = lib;
+  api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+  api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+  api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+  api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(lib, "ncclAllGather"));
+  api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+  if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.GetErrorString)
+    return fv::fail(FV_ERR_COMM, "NCCL library lacks a required symbol");
+  g_nccl = api;
+  return FV_OK;
+}
+constexpr int NCCL_UINT32 = 3;  // ncclUint32 in ncclDataType_t
+
+}  // namespace
+
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+struct fv_trainer {
+  fv_config cfg;
+  Dev d;
+  int device = 0;
+  int num_sms = 0;
+  int NT = 0;
+  cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+  cudaEvent_t ev_copy[2] = {nullptr, nullptr}, ev_used[2] = {nullptr, nullptr};
+  std::vector<cudaEvent_t> phase_events;
+  bool have_corpus = false, have_weights = false;
+  void* comm = nullptr;
+  // owned device buffers
+  float* d_wt = nullptr;
+  double* d_alpha = nullptr;
+  int32_t* d_tokens = nullptr;
+  unsigned long long* d_wstart = nullptr;
+  unsigned long long* d_perm = nullptr;
+  float* d_f = nullptr;
+  int32_t* d_idx = nullptr;
+  int32_t* d_idx_stage[2] = {nullptr, nullptr};
+  uint32_t* d_pkt = nullptr;
+  float* d_aw = nullptr;
+  int32_t* d_cnt = nullptr;
+  float* d_saved = nullptr;
+  uint32_t* d_colmax = nullptr;
+  uint32_t* d_ncb = nullptr;
+  StepCtl* d_ctl = nullptr;
+  float* d_log = nullptr;
+  size_t log_cap = 0;
+  unsigned long long steps_since_fold = 0;
+  int fwd_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
+  size_t scan_smem = 0, apply_smem = 0;
+};
+
+namespace {
+
+constexpr unsigned long long FOLD_EVERY = 32;  // steps between folds of alpha into wt
+constexpr int PHASE_SAMPLE = 16;               // every 16th step carries phase events
+constexpr int STAGE_STEPS = 32;                // steps per upload chunk in streaming mode
+
+#define FV_TRY(expr)                    \
+  do {                                  \
+    int fv_rc_ = (expr);                \
+    if (fv_rc_ != FV_OK) return fv_rc_; \
+  } while (0)
+
+template <typename T>
+int dev_alloc(T** p, size_t count) {
+  *p = nullptr;
+  FV_CUDA(cudaMalloc(reinterpret_cast<void**>(p), (count ? count : 1) * sizeof(T)));
+  return FV_OK;
+}
+
+int grid_for(size_t work, int block, int cap) {
+  size_t g = (work + block - 1) / block;
+  if (g < 1) g = 1;
+  if (g > (size_t)cap) g = cap;
+  return (int)g;
+}
+
+template <int NT>
+void launch_forward(fv_trainer* tr, int local, const int32_t* idx) {
+  k_forward<NT><<<tr->fwd_grid, 256, 0, tr->stream>>>(tr->d, local, idx);
+}
+template <int NT>
+void launch_scan(fv_trainer* tr, int local, const int32_t* idx) {
+  k_scan<NT><<<tr->scan_grid, 256, tr->scan_smem, tr->stream>>>(tr->d, local, idx);
+}
+template <int NT>
+void occupancy(int* fwd, int* scan, size_t scan_smem, cudaError_t* err) {
+  *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(fwd, k_forward<NT>, 256, 0);
+  if (*err == cudaSuccess) *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(scan, k_scan<NT>, 256, scan_smem);
+}
+
+#define FV_DISPATCH_NT(nt, fn, ...)     \
+  switch (nt) {                         \
+    case 1: fn<1>(__VA_ARGS__); break;  \
+    case 2: fn<2>(__VA_ARGS__); break;  \
+    case 3: fn<3>(__VA_ARGS__); break;  \
+    case 4: fn<4>(__VA_ARGS__); break;  \
+    case 5: fn<5>(__VA_ARGS__); break;  \
+    case 6: fn<6>(__VA_ARGS__); break;  \
+    case 7: fn<7>(__VA_ARGS__); break;  \
+    default: fn<8>(__VA_ARGS__); break; \
+  }
+
+// Multiplies alpha into wt and resets alpha.  `local` = steps already launched
+// since ctl->tick was last advanced.
+int fold_weights(fv_trainer* tr, int local) {
+  if (tr->steps_since_fold == 0) return FV_OK;
+  k_fold<<<tr->num_sms * 4, 256, 0, tr->stream>>>(tr->d, local);
+  k_reset_alpha<<<4, 256, 0, tr->stream>>>(tr->d);
+  FV_CUDA(cudaGetLastError());
+  tr->steps_since_fold = 0;
+  return FV_OK;
+}
+
+// One global step on tr->stream; `idx` = device array of this step's input ids.
+// Returns the number of kernels launched through *launches.
+int enqueue_step(fv_trainer* tr, int local, int32_t* idx, bool build_idx, cudaEvent_t* marks, uint64_t* launches) {
+  const Dev& d = tr->d;
+  if (build_idx) {
+    k_build_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, local, idx);
+    *launches += 1;
+  }
+  if (marks) FV_CUDA(cudaEventRecord(marks[0], tr->stream));
+  if (d.flags & FV_FLAG_EMULATE_RANKS) {
+    // every rank's block in turn, each into its own packet slot
+    const Dev own = tr->d;
+    for (int r = 0; r < own.G; ++r) {
+      tr->d.rank = r;
+      tr->d.pkt_send = own.pkt_recv + (size_t)r * own.P;
+      FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
+      k_xx<<<(own.Kp * 32 + 127) / 128, 128, 0, tr->stream>>>(tr->d);
+      *launches += 2;
+    }
+    tr->d = own;
+    *launches -= 2;
+    if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
+  } else {
+    FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
+    if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
+    k_xx<<<(d.Kp * 32 + 127) / 128, 128, 0, tr->stream>>>(d);
+  }
+  if (d.G > 1 && !(d.flags & FV_FLAG_EMULATE_RANKS)) {
+    const int rc = g_nccl.AllGather(d.pkt_send, d.pkt_recv, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
+    if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+  }
+  if (marks) FV_CUDA(cudaEventRecord(marks[2], tr->stream));
+  k_tag<<<tr->entry_grid, 256, 0, tr->stream>>>(d, idx);
+  FV_DISPATCH_NT(tr->NT, launch_scan, tr, local, idx);
+  k_apply<<<tr->apply_grid, 256, tr->apply_smem, tr->stream>>>(d, local, idx);
+  if (marks) FV_CUDA(cudaEventRecord(marks[3], tr->stream));
+  FV_CUDA(cudaGetLastError());
+  *launches += 5;
+  tr->steps_since_fold += 1;
+  return FV_OK;
+}
+
+int ensure_log(fv_trainer* tr, size_t nsteps) {
+  if (tr->log_cap >= nsteps) return FV_OK;
+  if (tr->d_log) FV_CUDA(cudaFree(tr->d_log));
+  tr->d_log = nullptr;
+  tr->log_cap = 0;
+  FV_TRY(dev_alloc(&tr->d_log, 2 * nsteps));
+  tr->log_cap = nsteps;
+  tr->d.nc_log = tr->d_log;
+  tr->d.s_log = tr->d_log + nsteps;
+  return FV_OK;
+}
+
+int read_device_error(fv_trainer* tr, uint32_t* out) {
+  StepCtl h;
+  FV_CUDA(cudaMemcpyAsync(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost, tr->stream));
+  FV_CUDA(cudaStreamSynchronize(tr->stream));
+  *out = h.error;
+  return FV_OK;
+}
+
+// The step loop.  idx_host == nullptr: ids are built on the GPU from the corpus
+// and the current order.  Otherwise they are uploaded in chunks of STAGE_STEPS
+// steps on a second stream, two chunks in flight.
+int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long long nsteps, float eps,
+                   const int32_t* idx_host, float* nc_out, float* scale_out, fv_run_stats* stats) {
+  FV_REQUIRE(tr->have_weights, FV_ERR_STATE, "trainer has no weights: call fv_trainer_set_weights first");
+  if (!idx_host) FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus: call fv_trainer_set_corpus first");
+  if (tr->d.G > 1 && !(tr->d.flags & FV_FLAG_EMULATE_RANKS))
+    FV_REQUIRE(tr->comm != nullptr, FV_ERR_STATE, "world > 1 but fv_trainer_init_comm was not called");
+  if (stats) memset(stats, 0, sizeof(*stats));
+  if (nsteps == 0) return FV_OK;
+  FV_REQUIRE(nsteps <= (1ull << 30), FV_ERR_INVALID, "too many steps in one call");
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  FV_TRY(ensure_log(tr, nsteps));
+  const Dev& d = tr->d;
+  const unsigned long long fold_every = (d.flags & FV_FLAG_FOLD_EVERY_STEP) ? 1 : FOLD_EVERY;
+  const size_t step_ids = (size_t)d.G * d.B * d.W;
+
+  const size_t nsamples = (size_t)((nsteps + PHASE_SAMPLE - 1) / PHASE_SAMPLE);
+  while (tr->phase_events.size() < nsamples * 4) {
+    cudaEvent_t e;
+    FV_CUDA(cudaEventCreate(&e));
+    tr->phase_events.push_back(e);
+  }
+  if (idx_host) {
+    for (int b = 0; b < 2; ++b)
+      if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
+  }
+
+  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps);
+  FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
+  uint64_t launches = 1;
+  unsigned long long chunk_id = 0;
+  for (unsigned long long k = 0; k < nsteps; ++k) {
+    int32_t* idx = tr->d_idx;
+    if (idx_host) {
+      const int b = (int)(chunk_id & 1);
+      if (k % STAGE_STEPS == 0) {
+        const unsigned long long n = (nsteps - k < STAGE_STEPS) ? nsteps - k : STAGE_STEPS;
+        // the buffer must no longer be read by the chunk that used it two chunks ago
+        if (chunk_id >= 2) FV_CUDA(cudaStreamWaitEvent(tr->copy_stream, tr->ev_used[b], 0));
+        FV_CUDA(cudaMemcpyAsync(tr->d_idx_stage[b], idx_host + k * step_ids, n * step_ids * sizeof(int32_t),
+                                cudaMemcpyHostToDevice, tr->copy_stream));
+        FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
+        FV_CUDA(cudaStreamWaitEvent(tr->stream, tr->ev_copy[b], 0));
+        k_check_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, tr->d_idx_stage[b], n * step_ids);
+        launches += 1;
+      }
+      idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * step_ids;
+    }
+    cudaEvent_t* marks = (k % PHASE_SAMPLE == 0) ? &tr->phase_events[(k / PHASE_SAMPLE) * 4] : nullptr;
+    FV_TRY(enqueue_step(tr, (int)k, idx, idx_host == nullptr, marks, &launches));
+    if (idx_host && ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps)) {
+      FV_CUDA(cudaEventRecord(tr->ev_used[chunk_id & 1], tr->stream));
+      ++chunk_id;
+    }
+    if (tr->steps_since_fold >= fold_every) {
+      FV_TRY(fold_weights(tr, (int)(k + 1)));
+      launches += 2;
+    }
+  }
+  k_advance<<<1, 1, 0, tr->stream>>>(tr->d_ctl, nsteps);
+  launches += 1;
+  FV_CUDA(cudaEventRecord(tr->ev_end, tr->stream));
+  std::vector<float> log(2 * nsteps);
+  FV_CUDA(cudaMemcpyAsync(log.data(), tr->d.nc_log, nsteps * sizeof(float), cudaMemcpyDeviceToHost, tr->stream));
+  FV_CUDA(cudaMemcpyAsync(log.data() + nsteps, tr->d.s_log, nsteps * sizeof(float), cudaMemcpyDeviceToHost,
+                          tr->stream));
+  FV_CUDA(cudaStreamSynchronize(tr->stream));
+  if (nc_out) memcpy(nc_out, log.data(), nsteps * sizeof(float));
+  if (scale_out) memcpy(scale_out, log.data() + nsteps, nsteps * sizeof(float));
+
+  uint32_t dev_err = 0;
+  FV_TRY(read_device_error(tr, &dev_err));
+  if (stats) {
+    float ms = 0.f;
+    FV_CUDA(cudaEventElapsedTime(&ms, tr->ev_begin, tr->ev_end));
+    stats->steps = nsteps;
+    unsigned long long mine = 0;
+    for (unsigned long long k = 0; k < nsteps; ++k) {
+      if (idx_host) {
+        mine += d.B;
+      } else {
+        uint64_t first, cnt;
+        fv_shard_range(d.Ns, d.B, d.G, d.rank, first_step + k, &first, &cnt);
+        mine += cnt;
+      }
+    }
+    stats->windows = mine;
+    stats->seconds = ms * 1e-3;
+    double ph[3] = {0, 0, 0};
+    for (size_t smp = 0; smp < nsamples; ++smp) {
+      cudaEvent_t* m = &tr->phase_events[smp * 4];
+      for (int i = 0; i < 3; ++i) {
+        float t = 0.f;
+        FV_CUDA(cudaEventElapsedTime(&t, m[i], m[i + 1]));
+        ph[i] += t * 1e-3;
+      }
+    }
+    const double scale = (double)nsteps / (double)nsamples;
+    stats->fwd_seconds = ph[0] * scale;
+    stats->exch_seconds = ph[1] * scale;
+    stats->upd_seconds = ph[2] * scale;
+    stats->kernel_launches = launches;
+    stats->last_nc = log[nsteps - 1];
+    stats->last_scale = log[2 * nsteps - 1];
+    stats->device_error = dev_err;
+  }
+  if (dev_err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "a token id was outside [0, V) (device check)");
+  if (dev_err & FV_DEVERR_WINDOW_RANGE)
+    return fv::fail(FV_ERR_DATA, "a window order entry or window start was out of range (device check)");
+  if (dev_err & FV_DEVERR_NAN_WEIGHT)
+    return fv::fail(FV_ERR_DATA, "a weight was NaN or a unit's scale collapsed to zero (device check)");
+  return FV_OK;
+}
+
+void free_all(fv_trainer* tr) {
+  cudaSetDevice(tr->device);
+  if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
+  void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,   tr->d_idx,
+                  tr->d_pkt, tr->d_aw,    tr->d_cnt,    tr->d_saved,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+                  tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
+  for (void* b : bufs)
+    if (b) cudaFree(b);
+  for (cudaEvent_t e : tr->phase_events) cudaEventDestroy(e);
+  cudaEvent_t evs[] = {tr->ev_begin, tr->ev_end, tr->ev_copy[0], tr->ev_copy[1], tr->ev_used[0], tr->ev_used[1]};
+  for (cudaEvent_t e : evs)
+    if (e) cudaEventDestroy(e);
+  if (tr->stream) cudaStreamDestroy(tr->stream);
+  if (tr->copy_stream) cudaStreamDestroy(tr->copy_stream);
+  delete tr;
+}
+
+int create_impl(const fv_config* cfg, fv_trainer* tr) {
+  tr->cfg = *cfg;
+  tr->device = cfg->device;
+  FV_CUDA(cudaSetDevice(cfg->device));
+  cudaDeviceProp prop;
+  FV_CUDA(cudaGetDeviceProperties(&prop, cfg->device));
+  tr->num_sms = prop.multiProcessorCount;
+  FV_CUDA(cudaStreamCreateWithFlags(&tr->stream, cudaStreamNonBlocking));
+  FV_CUDA(cudaStreamCreateWithFlags(&tr->copy_stream, cudaStreamNonBlocking));
+  FV_CUDA(cudaEventCreate(&tr->ev_begin));
+  FV_CUDA(cudaEventCreate(&tr->ev_end));
+  for (int b = 0; b < 2; ++b) {
+    FV_CUDA(cudaEventCreateWithFlags(&tr->ev_copy[b], cudaEventDisableTiming));
+    FV_CUDA(cudaEventCreateWithFlags(&tr->ev_used[b], cudaEventDisableTiming));
+  }
+
+  Dev& d = tr->d;
+  memset(&d, 0, sizeof(d));
+  d.K = (int)cfg->hid;
+  d.Kp = (d.K + 3) & ~3;
+  d.Kq = d.Kp / 4;
+  d.V = (int)cfg->vocab;
+  d.N = 2 * d.V;
+  d.W = (int)cfg->window;
+  d.B = (int)cfg->batch;
+  d.G = cfg->world;
+  d.rank = cfg->rank;
+  d.P = d.B + d.Kp;
+  d.prec = cfg->prec;
+  d.flags = cfg->flags;
+  tr->NT = (d.Kq + 31) / 32;
+
+  const size_t E = (size_t)d.G * d.B * d.W;
+  FV_TRY(dev_alloc(&tr->d_wt, (size_t)d.N * d.Kp));
+  FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
+  FV_TRY(dev_alloc(&tr->d_idx, E));
+  FV_TRY(dev_alloc(&tr->d_pkt, (size_t)d.G * d.P));
+  FV_TRY(dev_alloc(&tr->d_aw, (size_t)d.B));
+  FV_TRY(dev_alloc(&tr->d_cnt, E));
+  FV_TRY(dev_alloc(&tr->d_saved, E));
+  FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_ncb, 2));
+  FV_TRY(dev_alloc(&tr->d_ctl, 1));
+  FV_CUDA(cudaMemsetAsync(tr->d_cnt, 0, E * sizeof(int32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_colmax, 0, 2 * (size_t)d.Kp * sizeof(uint32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_ncb, 0, 2 * sizeof(uint32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_ctl, 0, sizeof(StepCtl), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_pkt, 0, (size_t)d.G * d.P * sizeof(uint32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_f, 0, (size_t)d.V * sizeof(float), tr->stream));
+  d.wt = tr->d_wt;
+  d.alpha = tr->d_alpha;
+  d.f = tr->d_f;
+  d.pkt_recv = tr->d_pkt;
+  d.pkt_send = tr->d_pkt + (size_t)d.rank * d.P;  // in-place all-gather
+  d.aw = tr->d_aw;
+  d.cnt = tr->d_cnt;
+  d.saved = tr->d_saved;
+  d.colmax = tr->d_colmax;
+  d.ncb = tr->d_ncb;
+  d.ctl = tr->d_ctl;
+  k_reset_alpha<<<4, 256, 0, tr->stream>>>(d);
+  FV_CUDA(cudaGetLastError());
+
+  // launch geometry: whole multiples of the SM count
+  tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + sizeof(uint32_t));
+  tr->apply_smem = (size_t)d.Kp * sizeof(double);
+  int fwd_bps = 0, scan_bps = 0;
+  cudaError_t oerr = cudaSuccess;
+  FV_DISPATCH_NT(tr->NT, occupancy, &fwd_bps, &scan_bps, tr->scan_smem, &oerr);
+  FV_CUDA(oerr);
+  if (fwd_bps < 1) fwd_bps = 1;
+  if (scan_bps < 1) scan_bps = 1;
+  if (scan_bps > 2) scan_bps = 2;
+  tr->fwd_grid = grid_for((size_t)d.B * 32, 256, tr->num_sms * fwd_bps);
+  tr->scan_grid = tr->num_sms * scan_bps;
+  tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
+  tr->apply_grid = grid_for(E, 256, tr->num_sms * 4);
+  FV_CUDA(cudaStreamSynchronize(tr->stream));
+  return FV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fv_trainer_create(const fv_config* cfg, fv_trainer** out) {
+  FV_REQUIRE(cfg && out, FV_ERR_INVALID, "fv_trainer_create: NULL argument");
+  *out = nullptr;
+  FV_REQUIRE(cfg->struct_size == sizeof(fv_config), FV_ERR_INVALID,
+             "fv_trainer_create: struct_size %u != %zu (ABI mismatch)", cfg->struct_size, sizeof(fv_config));
+  FV_REQUIRE(cfg->hid >= 1 && cfg->hid <= MAX_K, FV_ERR_INVALID, "hid must be in [1, %d], got %u", MAX_K, cfg->hid);
+  FV_REQUIRE(cfg->vocab >= 1 && cfg->vocab <= (1u << 29), FV_ERR_INVALID, "vocab out of range: %u", cfg->vocab);
+  FV_REQUIRE(cfg->window >= 1 && cfg->window <= 32, FV_ERR_INVALID, "window must be in [1, 32], got %u", cfg->window);
+  FV_REQUIRE(cfg->batch >= 1, FV_ERR_INVALID, "batch must be >= 1");
+  FV_REQUIRE(cfg->world >= 1 && cfg->rank >= 0 && cfg->rank < cfg->world, FV_ERR_INVALID,
+             "need world >= 1 and 0 <= rank < world (rank %d, world %d)", cfg->rank, cfg->world);
+  FV_REQUIRE((uint64_t)cfg->world * cfg->batch * cfg->window < 0x7ffffeull, FV_ERR_INVALID,
+             "world*batch*window = %llu does not fit the 23-bit scatter slot id",
+             (unsigned long long)cfg->world * cfg->batch * cfg->window);
+  FV_REQUIRE(cfg->delta == 0.0f, FV_ERR_INVALID, "delta != 0 (anti-Hebbian term) is not implemented");
+  FV_REQUIRE(cfg->prec > 0.0f, FV_ERR_INVALID, "prec must be > 0");
+  int ndev = 0;
+  FV_CUDA(cudaGetDeviceCount(&ndev));
+  FV_REQUIRE(cfg->device >= 0 && cfg->device < ndev, FV_ERR_INVALID, "device %d not present (%d devices)",
+             cfg->device, ndev);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  fv_trainer* tr = new fv_trainer();
+  const int rc = create_impl(cfg, tr);
+  if (rc != FV_OK) {
+    free_all(tr);
+    cudaSetDevice(prev);
+    return rc;
+  }
+  cudaSetDevice(prev);
+  *out = tr;
+  return FV_OK;
+}
+
+int fv_trainer_destroy(fv_trainer* tr) {
+  if (!tr) return FV_OK;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(tr->device);
+  cudaDeviceSynchronize();
+  free_all(tr);
+  cudaSetDevice(prev);
+  return FV_OK;
+}
+
+int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
+                          uint64_t noffsets) {
+  FV_REQUIRE(tr && enc && offsets, FV_ERR_INVALID, "fv_trainer_set_corpus: NULL argument");
+  FV_REQUIRE(noffsets >= 2, FV_ERR_DATA, "offsets needs at least two entries");
+  FV_REQUIRE(offsets[0] == 0, FV_ERR_DATA, "offsets[0] must be 0, got %llu", (unsigned long long)offsets[0]);
+  FV_REQUIRE(offsets[noffsets - 1] <= ntok, FV_ERR_DATA, "last offset %llu exceeds the number of tokens %llu",
+             (unsigned long long)offsets[noffsets - 1], (unsigned long long)ntok);
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  Dev& d = tr->d;
+  uint64_t ns = 0;
+  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, d.W, tr->cfg.maxlen, &ns, nullptr));
+  std::vector<uint64_t> starts(ns);
+  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, d.W, tr->cfg.maxlen, &ns, starts.data()));
+  std::vector<float> f(d.V);
+  FV_TRY(fv_inverse_frequency(enc, ntok, d.V, (d.flags & FV_FLAG_COUNT_FP32) != 0, f.data()));
+
+  tr->have_corpus = false;
+  if (tr->d_tokens) FV_CUDA(cudaFree(tr->d_tokens));
+  if (tr->d_wstart) FV_CUDA(cudaFree(tr->d_wstart));
+  if (tr->d_perm) FV_CUDA(cudaFree(tr->d_perm));
+  tr->d_tokens = nullptr;
+  tr->d_wstart = nullptr;
+  tr->d_perm = nullptr;
+  FV_TRY(dev_alloc(&tr->d_tokens, ntok));
+  FV_TRY(dev_alloc(&tr->d_wstart, ns));
+  FV_TRY(dev_alloc(&tr->d_perm, ns));
+  FV_CUDA(cudaMemcpyAsync(tr->d_tokens, enc, ntok * sizeof(int32_t), cudaMemcpyHostToDevice, tr->stream));
+  FV_CUDA(cudaMemcpyAsync(tr->d_wstart, starts.data(), ns * sizeof(uint64_t), cudaMemcpyHostToDevice, tr->stream));
+  FV_CUDA(cudaMemcpyAsync(tr->d_f, f.data(), (size_t)d.V * sizeof(float), cudaMemcpyHostToDevice, tr->stream));
+  k_iota<<<tr->num_sms * 4, 256, 0, tr->stream>>>(tr->d_perm, ns);
+  FV_CUDA(cudaGetLastError());
+  FV_CUDA(cudaStreamSynchronize(tr->stream));
+  d.tokens = tr->d_tokens;
+  d.wstart = tr->d_wstart;
+  d.perm = tr->d_perm;
+  d.Ns = ns;
+  d.ntok = ntok;
+  tr->have_corpus = true;
+  return FV_OK;
+}
+
+int fv_trainer_num_windows(fv_trainer* tr, uint64_t* count) {
+  FV_REQUIRE(tr && count, FV_ERR_INVALID, "fv_trainer_num_windows: NULL argument");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  *count = tr->d.Ns;
+  return FV_OK;
+}
+
+int fv_trainer_get_inverse_frequency(fv_trainer* tr, float* inv_freq) {
+  FV_REQUIRE(tr && inv_freq, FV_ERR_INVALID, "fv_trainer_get_inverse_frequency: NULL argument");
+  fv::DeviceGuard guard(tr->device);
+  FV_CUDA(cudaMemcpy(inv_freq, tr->d_f, (size_t)tr->d.V * sizeof(float), cudaMemcpyDeviceToHost));
+  return FV_OK;
+}
+
+int fv_trainer_set_inverse_frequency(fv_trainer* tr, const float* inv_freq) {
+  FV_REQUIRE(tr && inv_freq, FV_ERR_INVALID, "fv_trainer_set_inverse_frequency: NULL argument");
+  fv::DeviceGuard guard(tr->device);
+  FV_CUDA(cudaMemcpy(tr->d_f, inv_freq, (size_t)tr->d.V * sizeof(float), cudaMemcpyHostToDevice));
+  return FV_OK;
+}
+
+int fv_trainer_set_weights(fv_trainer* tr, const float* w_kn) {
+  FV_REQUIRE(tr && w_kn, FV_ERR_INVALID, "fv_trainer_set_weights: NULL argument");
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  const Dev& d = tr->d;
+  float* tmp = nullptr;
+  FV_TRY(dev_alloc(&tmp, (size_t)d.K * d.N));
+  cudaError_t e = cudaMemcpyAsync(tmp, w_kn, (size_t)d.K * d.N * sizeof(float), cudaMemcpyHostToDevice, tr->stream);
+  if (e == cudaSuccess) {
+    dim3 grid((d.N + 31) / 32, (d.Kp + 31) / 32), block(32, 8);
+    k_to_device_layout<<<grid, block, 0, tr->stream>>>(tmp, tr->d_wt, d.K, d.Kp, d.N);
+    k_reset_alpha<<<4, 256, 0, tr->stream>>>(d);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(tr->stream);
+  cudaFree(tmp);
+  FV_CUDA(e);
+  tr->steps_since_fold = 0;
+  tr->have_weights = true;
+  return FV_OK;
+}
+
+int fv_trainer_get_weights(fv_trainer* tr, float* w_kn) {
+  FV_REQUIRE(tr && w_kn, FV_ERR_INVALID, "fv_trainer_get_weights: NULL argument");
+  FV_REQUIRE(tr->have_weights, FV_ERR_STATE, "trainer has no weights");
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  const Dev& d = tr->d;
+  FV_TRY(fold_weights(tr, 0));
+  float* tmp = nullptr;
+  FV_TRY(dev_alloc(&tmp, (size_t)d.K * d.N));
+  dim3 grid((d.N + 31) / 32, (d.Kp + 31) / 32), block(32, 8);
+  k_to_host_layout<<<grid, block, 0, tr->stream>>>(tr->d_wt, tmp, d.K, d.Kp, d.N);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(w_kn, tmp, (size_t)d.K * d.N * sizeof(float), cudaMemcpyDeviceToHost, tr->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(tr->stream);
+  cudaFree(tmp);
+  FV_CUDA(e);
+  return FV_OK;
+}
+
+int fv_trainer_set_permutation(fv_trainer* tr, const uint64_t* perm, uint64_t n) {
+  FV_REQUIRE(tr && perm, FV_ERR_INVALID, "fv_trainer_set_permutation: NULL argument");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  FV_REQUIRE(n == tr->d.Ns, FV_ERR_INVALID, "permutation has %llu entries, the corpus has %llu windows",
+             (unsigned long long)n, (unsigned long long)tr->d.Ns);
+  fv::DeviceGuard guard(tr->device);
+  FV_CUDA(cudaMemcpy(tr->d_perm, perm, n * sizeof(uint64_t), cudaMemcpyHostToDevice));
+  return FV_OK;
+}
+
+int fv_trainer_shuffle(fv_trainer* tr, uint64_t seed) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_shuffle: NULL trainer");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  fv::DeviceGuard guard(tr->device);
+  const unsigned long long n = tr->d.Ns;
+  if (n == 0) return FV_OK;
+  int bits = 1;
+  while ((1ull << bits) < n) ++bits;
+  int half = (bits + 1) / 2;
+  if (half < 1) half = 1;
+  // scramble the seed once so that nearby seeds give unrelated keys
+  unsigned long long k = seed + 0x9e3779b97f4a7c15ull;
+  k = (k ^ (k >> 30)) * 0xbf58476d1ce4e5b9ull;
+  k = (k ^ (k >> 27)) * 0x94d049bb133111ebull;
+  k ^= k >> 31;
+  k_feistel_perm<<<tr->num_sms * 4, 256, 0, tr->stream>>>(tr->d_perm, n, half, k);
+  FV_CUDA(cudaGetLastError());
+  FV_CUDA(cudaStreamSynchronize(tr->stream));
+  return FV_OK;
+}
+
+int fv_trainer_get_permutation(fv_trainer* tr, uint64_t* perm) {
+  FV_REQUIRE(tr && perm, FV_ERR_INVALID, "fv_trainer_get_permutation: NULL argument");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  fv::DeviceGuard guard(tr->device);
+  FV_CUDA(cudaMemcpy(perm, tr->d_perm, tr->d.Ns * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  return FV_OK;
+}
+
+int fv_trainer_run_steps(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, float eps, float* nc_out,
+                         float* scale_out, fv_run_stats* stats) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_run_steps: NULL trainer");
+  return run_steps_impl(tr, first_step, nsteps, eps, nullptr, nc_out, scale_out, stats);
+}
+
+int fv_trainer_run_steps_host(fv_trainer* tr, const int32_t* idx_host, uint64_t nsteps, float eps, float* nc_out,
+                              float* scale_out, fv_run_stats* stats) {
+  FV_REQUIRE(tr && idx_host, FV_ERR_INVALID, "fv_trainer_run_steps_host: NULL argument");
+  return run_steps_impl(tr, 0, nsteps, eps, idx_host, nc_out, scale_out, stats);
+}
+
+int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_stats* stats) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_run_epoch: NULL trainer");
+  FV_REQUIRE(nep >= 1, FV_ERR_INVALID, "nep must be >= 1");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  // eps = lr0 * (1 - epoch/Nep): float quotient, double product, float store
+  const float q = (float)epoch / (float)nep;
+  const float eps = (float)((double)tr->cfg.lr0 * (1.0 - (double)q));
+  const unsigned long long per_step = (unsigned long long)tr->d.G * tr->d.B;
+  const unsigned long long nsteps = (tr->d.Ns + per_step - 1) / per_step;
+  return run_steps_impl(tr, 0, nsteps, eps, nullptr, nullptr, nullptr, stats);
+}
+
+int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* winners, float* xx, float* nc,
+                          float* scale) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_step_debug: NULL trainer");
+  float nc1 = 0.f, s1 = 0.f;
+  FV_TRY(run_steps_impl(tr, step, 1, eps, nullptr, &nc1, &s1, nullptr));
+  fv::DeviceGuard guard(tr->device);
+  const Dev& d = tr->d;
+  std::vector<uint32_t> pkt((size_t)d.G * d.P);
+  FV_CUDA(cudaMemcpy(pkt.data(), tr->d_pkt, pkt.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  for (int r = 0; r < d.G; ++r) {
+    if (winners) memcpy(winners + (size_t)r * d.B, pkt.data() + (size_t)r * d.P, (size_t)d.B * sizeof(int32_t));
+    if (xx) memcpy(xx + (size_t)r * d.K, pkt.data() + (size_t)r * d.P + d.B, (size_t)d.K * sizeof(float));
+  }
+  if (nc) *nc = nc1;
+  if (scale) *scale = s1;
+  return FV_OK;
+}
+
+int fv_comm_unique_id(uint8_t id[128]) {
+  FV_REQUIRE(id, FV_ERR_INVALID, "fv_comm_unique_id: NULL id");
+  FV_TRY(load_nccl());
+  Id128 uid;
+  memset(&uid, 0, sizeof(uid));
+  const int rc = g_nccl.GetUniqueId(&uid);
+  if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclGetUniqueId failed: %s", g_nccl.GetErrorString(rc));
+  memcpy(id, uid.bytes, 128);
+  return FV_OK;
+}
+
+int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
+  FV_REQUIRE(tr && id, FV_ERR_INVALID, "fv_trainer_init_comm: NULL argument");
+  if (tr->d.G == 1) return FV_OK;
+  FV_REQUIRE(tr->comm == nullptr, FV_ERR_STATE, "communicator already initialised");
+  FV_TRY(load_nccl());
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  Id128 uid;
+  memcpy(uid.bytes, id, 128);
+  void* comm = nullptr;
+  const int rc = g_nccl.CommInitRank(&comm, tr->d.G, uid, tr->d.rank);
+  if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(rc));
+  tr->comm = comm;
+  return FV_OK;
+}
+
+}  // extern "C"

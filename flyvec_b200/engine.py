@@ -1,0 +1,276 @@
+"""Thin Python objects over the C ABI: one :class:`Trainer` per GPU (rank) and a
+:class:`Hasher`.  They only marshal numpy arrays; all arithmetic runs in the
+CUDA library."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import FvConfig, FvRunStats, as_c, check, ptr
+
+
+class Trainer:
+    """One data-parallel rank of the FlyVec trainer (the role of the reference's
+    ``model_descriptor`` + ``model_arrays`` pair, flyvec/train_flyvec.py:141-229)."""
+
+    def __init__(self, hid: int, vocab: int, window: int = 11, batch: int = 10000, lr0: float = 0.002,
+                 delta: float = 0.0, prec: float = 1e-30, device: int = 0, rank: int = 0, world: int = 1,
+                 flags: int = 0, maxlen: int = 0, m: int = 2):
+        self._h = C.c_void_p()
+        self.cfg = FvConfig(C.sizeof(FvConfig), device, rank, world, hid, vocab, window, batch, lr0, delta, prec, m,
+                            maxlen, flags)
+        self.K, self.V, self.N, self.W, self.B, self.G, self.rank = hid, vocab, 2 * vocab, window, batch, world, rank
+        check(_lib.lib().fv_trainer_create(C.byref(self.cfg), C.byref(self._h)))
+
+    # -- lifetime -----------------------------------------------------------
+    def close(self):
+        if self._h:
+            _lib.lib().fv_trainer_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # -- data ---------------------------------------------------------------
+    def set_corpus(self, encodings: np.ndarray, offsets: np.ndarray) -> int:
+        enc = as_c(encodings, np.int32)
+        off = as_c(offsets, np.uint64)
+        check(_lib.lib().fv_trainer_set_corpus(self._h, ptr(enc), enc.size, ptr(off), off.size))
+        return self.num_windows
+
+    @property
+    def num_windows(self) -> int:
+        n = C.c_uint64(0)
+        check(_lib.lib().fv_trainer_num_windows(self._h, C.byref(n)))
+        return n.value
+
+    @property
+    def steps_per_epoch(self) -> int:
+        per = self.G * self.B
+        return (self.num_windows + per - 1) // per
+
+    def inverse_frequency(self) -> np.ndarray:
+        f = np.empty(self.V, np.float32)
+        check(_lib.lib().fv_trainer_get_inverse_frequency(self._h, ptr(f)))
+        return f
+
+    def set_inverse_frequency(self, f: np.ndarray):
+        f = as_c(f, np.float32)
+        assert f.size == self.V
+        check(_lib.lib().fv_trainer_set_inverse_frequency(self._h, ptr(f)))
+
+    def set_weights(self, w: np.ndarray):
+        w = as_c(w, np.float32)
+        if w.shape != (self.K, self.N):
+            raise ValueError(f"weights must have shape ({self.K}, {self.N}), got {w.shape}")
+        check(_lib.lib().fv_trainer_set_weights(self._h, ptr(w)))
+
+    def get_weights(self) -> np.ndarray:
+        w = np.empty((self.K, self.N), np.float32)
+        check(_lib.lib().fv_trainer_get_weights(self._h, ptr(w)))
+        return w
+
+    def set_permutation(self, perm: np.ndarray):
+        perm = as_c(perm, np.uint64)
+        check(_lib.lib().fv_trainer_set_permutation(self._h, ptr(perm), perm.size))
+
+    def shuffle(self, seed: int):
+        check(_lib.lib().fv_trainer_shuffle(self._h, C.c_uint64(seed & (2 ** 64 - 1))))
+
+    def get_permutation(self) -> np.ndarray:
+        perm = np.empty(self.num_windows, np.uint64)
+        check(_lib.lib().fv_trainer_get_permutation(self._h, ptr(perm)))
+        return perm
+
+    # -- running ------------------------------------------------------------
+    def run_epoch(self, epoch: int, nep: int) -> dict:
+        st = FvRunStats()
+        check(_lib.lib().fv_trainer_run_epoch(self._h, epoch, nep, C.byref(st)))
+        return st.as_dict()
+
+    def run_steps(self, first_step: int, nsteps: int, eps: float, want_log: bool = False):
+        st = FvRunStats()
+        nc = np.empty(nsteps, np.float32) if want_log else None
+        sc = np.empty(nsteps, np.float32) if want_log else None
+        check(_lib.lib().fv_trainer_run_steps(self._h, first_step, nsteps, eps, ptr(nc) if want_log else None,
+                                              ptr(sc) if want_log else None, C.byref(st)))
+        d = st.as_dict()
+        if want_log:
+            d["nc"], d["scale"] = nc, sc
+        return d
+
+    def run_steps_host(self, idx_host: np.ndarray, nsteps: int, eps: float, nc_out: np.ndarray | None = None):
+        """``idx_host``: int32 ``[nsteps, world*batch, window]`` input ids in host
+        (ideally pinned) memory; uploaded inside the call."""
+        assert idx_host.dtype == np.int32 and idx_host.flags.c_contiguous
+        assert idx_host.size == nsteps * self.G * self.B * self.W
+        st = FvRunStats()
+        check(_lib.lib().fv_trainer_run_steps_host(self._h, ptr(idx_host), nsteps, eps,
+                                                   ptr(nc_out) if nc_out is not None else None, None, C.byref(st)))
+        return st.as_dict()
+
+    def step_debug(self, step: int, eps: float):
+        win = np.empty(self.G * self.B, np.int32)
+        xx = np.empty((self.G, self.K), np.float32)
+        nc, sc = C.c_float(0), C.c_float(0)
+        check(_lib.lib().fv_trainer_step_debug(self._h, step, eps, ptr(win), ptr(xx), C.byref(nc), C.byref(sc)))
+        return win.reshape(self.G, self.B), xx, np.float32(nc.value), np.float32(sc.value)
+
+    # -- multi-GPU ----------------------------------------------------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        buf = (C.c_uint8 * 128)()
+        check(_lib.lib().fv_comm_unique_id(buf))
+        return bytes(buf)
+
+    def init_comm(self, uid: bytes):
+        assert len(uid) == 128
+        buf = (C.c_uint8 * 128).from_buffer_copy(uid)
+        check(_lib.lib().fv_trainer_init_comm(self._h, buf))
+
+
+def shard_range(num_windows: int, batch: int, world: int, rank: int, step: int):
+    """Windows ``[first, first+count)`` of the current order that ``rank`` owns in
+    global step ``step`` (flyvec/src/cuda_funcs.cu:1667-1670)."""
+    a, b = C.c_uint64(0), C.c_uint64(0)
+    check(_lib.lib().fv_shard_range(num_windows, batch, world, rank, step, C.byref(a), C.byref(b)))
+    return a.value, b.value
+
+
+def enumerate_windows(offsets: np.ndarray, window: int, maxlen: int = 0) -> np.ndarray:
+    off = as_c(offsets, np.uint64)
+    n = C.c_uint64(0)
+    nch = max(off.size - 1, 0)
+    check(_lib.lib().fv_enumerate_windows(ptr(off), nch, window, maxlen, C.byref(n), None))
+    starts = np.empty(n.value, np.uint64)
+    check(_lib.lib().fv_enumerate_windows(ptr(off), nch, window, maxlen, C.byref(n), ptr(starts)))
+    return starts
+
+
+def inverse_frequency(encodings: np.ndarray, vocab: int, saturate: bool = False) -> np.ndarray:
+    enc = as_c(encodings, np.int32)
+    f = np.empty(vocab, np.float32)
+    check(_lib.lib().fv_inverse_frequency(ptr(enc), enc.size, vocab, int(saturate), ptr(f)))
+    return f
+
+
+class Hasher:
+    """Synapses resident on one GPU plus the two hashing entry points."""
+
+    def __init__(self, synapses: np.ndarray, normalize: bool = False, prec: float = 1.0e-32, device: int = 0):
+        w = as_c(synapses, np.float32)
+        if w.ndim != 2 or w.shape[1] % 2:
+            raise ValueError("synapses must be float32 [K][2V]")
+        self.K, self.N = w.shape
+        self.V = self.N // 2
+        self.device = device
+        self._h = C.c_void_p()
+        check(_lib.lib().fv_hasher_create(ptr(w), self.K, self.N, int(normalize), prec, device, C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            _lib.lib().fv_hasher_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def weights(self) -> np.ndarray:
+        w = np.empty((self.K, self.N), np.float32)
+        check(_lib.lib().fv_hasher_get_weights(self._h, ptr(w)))
+        return w
+
+    def code_bytes(self, packed: bool) -> int:
+        return (self.K + 7) // 8 if packed else self.K
+
+    def hash_tokens(self, ids, hash_length: int = 50, packed: bool = False, zero_unknown: bool = True) -> np.ndarray:
+        ids = as_c(ids, np.int32).reshape(-1)
+        flags = (_lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES) | (0 if zero_unknown else _lib.FV_HASH_NO_UNK)
+        out = np.empty((ids.size, self.code_bytes(packed)), np.uint8)
+        check(_lib.lib().fv_hash_tokens(self._h, ptr(ids), ids.size, hash_length, flags, ptr(out)))
+        return out if packed else out.view(np.int8)
+
+    def hash_windows(self, idx, inv_freq=None, hash_length: int = 50, packed: bool = False) -> np.ndarray:
+        idx = as_c(idx, np.int32)
+        assert idx.ndim == 2
+        flags = _lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES
+        f = None
+        if inv_freq is None:
+            flags |= _lib.FV_HASH_RAW
+        else:
+            f = as_c(inv_freq, np.float32)
+            assert f.size == self.V
+        out = np.empty((idx.shape[0], self.code_bytes(packed)), np.uint8)
+        check(_lib.lib().fv_hash_windows(self._h, ptr(idx), idx.shape[0], idx.shape[1], ptr(f) if f is not None else None,
+                                         hash_length, flags, ptr(out)))
+        return out if packed else out.view(np.int8)
+
+    def set_inverse_frequency(self, f):
+        f = as_c(f, np.float32)
+        check(_lib.lib().fv_hasher_set_inverse_frequency(self._h, ptr(f), f.size))
+
+    # device-resident forms, used by the benchmark
+    def hash_tokens_device(self, d_ids: int, n: int, hash_length: int, d_out: int, packed: bool = True) -> float:
+        sec = C.c_double(0)
+        flags = _lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES
+        check(_lib.lib().fv_hash_tokens_device(self._h, C.c_void_p(d_ids), n, hash_length, flags, C.c_void_p(d_out),
+                                               C.byref(sec)))
+        return sec.value
+
+    def hash_windows_device(self, d_idx: int, nwin: int, window: int, weighted: bool, hash_length: int, d_out: int,
+                            packed: bool = True) -> float:
+        sec = C.c_double(0)
+        flags = _lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES
+        check(_lib.lib().fv_hash_windows_device(self._h, C.c_void_p(d_idx), nwin, window, int(weighted), hash_length,
+                                                flags, C.c_void_p(d_out), C.byref(sec)))
+        return sec.value
+
+
+class DeviceBuffer:
+    """Raw device allocation through the C ABI (benchmark helper)."""
+
+    def __init__(self, nbytes: int, device: int = 0):
+        self.device, self.nbytes = device, nbytes
+        p = C.c_void_p()
+        check(_lib.lib().fv_device_alloc(device, nbytes, C.byref(p)))
+        self.ptr = p.value
+
+    def upload(self, a: np.ndarray):
+        a = np.ascontiguousarray(a)
+        assert a.nbytes <= self.nbytes
+        check(_lib.lib().fv_copy_to_device(self.device, C.c_void_p(self.ptr), ptr(a), a.nbytes))
+
+    def download(self, shape, dtype) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        assert out.nbytes <= self.nbytes
+        check(_lib.lib().fv_copy_to_host(self.device, ptr(out), C.c_void_p(self.ptr), out.nbytes))
+        return out
+
+    def free(self):
+        if self.ptr:
+            _lib.lib().fv_device_free(self.device, C.c_void_p(self.ptr))
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def flush_l2(device: int = 0, nbytes: int = 256 << 20):
+    check(_lib.lib().fv_flush_l2(device, nbytes))

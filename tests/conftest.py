@@ -1,0 +1,23 @@
+import os
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def built_lib():
+    """The in-tree CUDA library; built on demand (nvcc cross-compiles without a GPU)."""
+    from flyvec_b200 import _lib
+
+    if not _lib.LIB_PATH.exists():
+        _lib.build()
+    return _lib.lib()
