@@ -13,9 +13,11 @@
 //   cnt/saved   [G*B*w]     scatter bookkeeping, one slot per (window, position).
 //
 // One global step (reference: run_epoch, flyvec/src/cuda_funcs.cu:1662-1812):
-//   k_build_idx  T4   window -> input ids                    (cuda_funcs.cu:915-936)
-//   k_forward    T6-8 gather-sum, arg-max, weighted winner    (cuda_funcs.cu:248-305, 488-561, 722-744)
-//   k_xx         T8   xx[mu] = sum of weighted winning activations, fixed order
+//   k_forward    T4   window -> input ids                    (cuda_funcs.cu:915-936)
+//                T6-8 gather-sum, arg-max, weighted winner    (cuda_funcs.cu:248-305, 488-561)
+//                T8   xx[mu] = sum of weighted winning activations, in a fixed order
+//                     (cuda_funcs.cu:722-744)
+//   (k_build_idx      only when world > 1: ids of the other ranks' windows)
 //   all-gather        winners + xx of every rank (NCCL)
 //   k_tag        T10  each touched (mu,i) gets one owner slot; its weight is parked in
 //                     `saved` and replaced by a tagged NaN     (cuda_funcs.cu:657-672)
@@ -45,6 +47,10 @@ struct StepCtl {
   unsigned long long tick;  // steps executed since the weights were last folded (selects the alpha buffer)
   float eps;
   uint32_t error;
+  uint32_t wabsmax;       // bit pattern of an upper bound of max |wt|
+  uint32_t wabsmax_fold;  // the same, collected while folding
+  uint32_t xx_ticket;     // CTAs of the running k_xx that have finished
+  uint32_t fwd_next;      // next window index k_forward hands out beyond the first round
 };
 
 // Everything a kernel needs, passed by value.
@@ -61,7 +67,8 @@ struct Dev {
   const float* f;
   uint32_t* pkt_send;
   uint32_t* pkt_recv;
-  float* aw;
+  float* aw;       // [B] weighted activation of each window's winner
+  float* xx_part;  // [k_xx CTAs][Kp] partial sums of xx
   int32_t* cnt;
   float* saved;
   uint32_t* colmax;
@@ -84,6 +91,8 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) { return __reduce_m
 __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps) {
   ctl->base = base;
   ctl->eps = eps;
+  ctl->fwd_next = 0u;
+  ctl->xx_ticket = 0u;
 }
 __global__ void k_advance(StepCtl* ctl, unsigned long long n) {
   ctl->base += n;
@@ -94,36 +103,38 @@ __global__ void k_advance(StepCtl* ctl, unsigned long long n) {
 // T4: input ids of every window of the global step (all ranks' blocks).
 // Absent windows (past the end of the order) are marked -2 in every position.
 // ---------------------------------------------------------------------------
-__global__ void k_build_idx(Dev d, int local, int32_t* __restrict__ idx) {
-  const unsigned long long step = d.ctl->base + local;
-  const int total = d.G * d.B * d.W;
-  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
-    const int q = e / d.W, c = e - q * d.W;
-    const unsigned long long pos = step * (unsigned long long)d.G * d.B + q;
-    int val = -2;
-    if (pos < d.Ns) {
-      const unsigned long long p = d.perm[pos];
-      if (p >= d.Ns) {
+__device__ __forceinline__ int input_id(const Dev& d, unsigned long long step, int e) {
+  const int q = e / d.W, c = e - q * d.W;
+  const unsigned long long pos = step * (unsigned long long)d.G * d.B + q;
+  int val = -2;
+  if (pos < d.Ns) {
+    const unsigned long long p = d.perm[pos];
+    if (p >= d.Ns) {
+      atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
+    } else {
+      const unsigned long long s = d.wstart[p];
+      if (s + d.W > d.ntok) {
         atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
       } else {
-        const unsigned long long s = d.wstart[p];
-        if (s + d.W > d.ntok) {
-          atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
+        const int tok = d.tokens[s + c];
+        if (tok < 0) {
+          val = -1;
+        } else if (tok >= d.V) {
+          atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
+          val = -1;
         } else {
-          const int tok = d.tokens[s + c];
-          if (tok < 0) {
-            val = -1;
-          } else if (tok >= d.V) {
-            atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
-            val = -1;
-          } else {
-            val = tok + (c == d.W / 2 ? d.V : 0);
-          }
+          val = tok + (c == d.W / 2 ? d.V : 0);
         }
       }
     }
-    idx[e] = val;
   }
+  return val;
+}
+__global__ void k_build_idx(Dev d, int local, int32_t* __restrict__ idx) {
+  const unsigned long long step = d.ctl->base + local;
+  const int total = d.G * d.B * d.W;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x)
+    idx[e] = input_id(d, step, e);
 }
 
 // Checks host-supplied input ids (streaming mode) against [ -2, N ).
@@ -141,11 +152,12 @@ __global__ void k_check_idx(Dev d, const int32_t* __restrict__ idx, size_t total
 // (cuda_funcs.cu:1716-1721).
 //
 // Arithmetic.  The reference sums each unit in double over c = 0..w-1 and rounds
-// to float (cuda_funcs.cu:252-260).  The fast path sums in float and also tracks
-// the largest |term| it saw; sequential float summation of w terms bounded by
-// xmax is off by at most w*w*2^-24*xmax, so when the gap between the two largest
-// activations exceeds four times that bound (plus the rounding of the scale
-// product) the arg-max of the float sums is the arg-max of the exact sums.
+// to float (cuda_funcs.cu:252-260).  The fast path sums in float; sequential float
+// summation of w terms bounded by xmax is off by at most w*w*2^-24*xmax, and the
+// control word carries an upper bound of max |wt| (set when weights are loaded or
+// folded, raised by k_apply), so when the gap between the two largest activations
+// exceeds four times that bound (plus the rounding of the scale product) the
+// arg-max of the float sums is the arg-max of the exact sums.
 // Otherwise -- about one window in 10^4 -- the warp redoes the window in double
 // with the reference's tie order (smallest (index % 64, index) among equal
 // maxima, cuda_funcs.cu:507-540).
@@ -158,29 +170,40 @@ __device__ __forceinline__ bool better(float a, int ia, float b, int ib) {
   return ka < kb;
 }
 
-template <int NT>
-__device__ __noinline__ int exact_winner(const Dev& d, const double* __restrict__ alpha, int my, int lane, int skip) {
+// The double-precision path for one window: per column group all w rows are fetched
+// together (they were just read, so they come from L1/L2), summed in position order
+// in double, scaled, rounded to float and compared with the reference's tie order.
+// `skip` excludes one unit (used for the m-th winner).
+__device__ __noinline__ int exact_winner(const float* __restrict__ wt, const double* __restrict__ alpha, int Kp, int Kq,
+                                         int K, int W, int zrow, int my, int lane, int skip) {
   float best = -INFINITY;
   int bi = 0x000fffff;
-  const int Kq = d.Kq;
-  for (int t = 0; t < NT; ++t) {
-    const int q = lane + 32 * t;
+  const int row_id = (my < 0) ? zrow : my;
+  const int groups = (Kq + 31) >> 5;
+  for (int t = 0; t < groups; ++t) {
+    const int q = min(lane + 32 * t, Kq - 1);
     double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-    for (int c = 0; c < d.W; ++c) {
-      const int id = __shfl_sync(FULL, my, c);
-      if (id < 0 || q >= Kq) continue;
-      const float4 v = __ldg(reinterpret_cast<const float4*>(d.wt + (size_t)id * d.Kp) + q);
-      s0 += (double)v.x;
-      s1 += (double)v.y;
-      s2 += (double)v.z;
-      s3 += (double)v.w;
+    for (int c0 = 0; c0 < W; c0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int id = __shfl_sync(FULL, row_id, (c0 + u) & 31);
+        v[u] = __ldg(reinterpret_cast<const float4*>(wt + (size_t)((c0 + u < W) ? id : zrow) * Kp) + q);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        s0 += (double)v[u].x;
+        s1 += (double)v[u].y;
+        s2 += (double)v[u].z;
+        s3 += (double)v[u].w;
+      }
     }
-    if (q < Kq) {
+    if (lane + 32 * t < Kq) {
       const int mu = 4 * q;
       const double s[4] = {s0, s1, s2, s3};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        if (mu + k < d.K && mu + k != skip) {
+        if (mu + k < K && mu + k != skip) {
           const float a = (float)(s[k] * alpha[mu + k]);
           if (better(a, mu + k, best, bi)) {
             best = a;
@@ -202,139 +225,232 @@ __device__ __noinline__ int exact_winner(const Dev& d, const double* __restrict_
   return bi;
 }
 
+constexpr int FWD_THREADS = 128;
+constexpr int FWD_WARPS = FWD_THREADS / 32;
+
+// Two floats per 64-bit register; Blackwell adds both halves in one instruction.
+__device__ __forceinline__ void add2(unsigned long long& a, const unsigned long long b) {
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(a) : "l"(b));
+}
+__device__ __forceinline__ float lo_f(unsigned long long v) { return __uint_as_float((unsigned)(v & 0xffffffffull)); }
+__device__ __forceinline__ float hi_f(unsigned long long v) { return __uint_as_float((unsigned)(v >> 32)); }
+
+// Weighted activation of the winner: float product with 1/count, double running sum
+// over c = 0..w-1, float store (cuda_funcs.cu:289-305 restricted to one unit).
+__device__ __forceinline__ float weighted_activation(const Dev& d, const double* __restrict__ alpha, int my, int winner,
+                                                     int lane) {
+  float x = 0.f;  // padding positions contribute +0, which leaves the double sum unchanged
+  if (lane < d.W && my >= 0) {
+    const float wv = (float)((double)d.wt[(size_t)my * d.Kp + winner] * alpha[winner]);
+    x = wv * __ldg(d.f + (my % d.V));
+  }
+  double s = 0.0;
+  for (int c = 0; c < d.W; ++c) s += (double)__shfl_sync(FULL, x, c);
+  return (float)s;
+}
+
+// One warp per window.  The first nwarps windows are dealt statically, the rest is
+// handed out through a counter in the control word, one window per request, so no
+// warp idles while others still have a queue; outputs are keyed by window index, so
+// the schedule does not influence any result.
+//   * rows are gathered four at a time (16 independent 128-bit loads per lane) and
+//     added in position order with packed float adds; padding positions gather an
+//     all-zero row behind the matrix; lanes past the end of a row re-read its last
+//     16 bytes instead of being predicated off.
+//   * the float arg-max is certified when no other unit comes within theta of the
+//     maximum; otherwise the window is redone in double on the spot.
 template <int NT>
-__global__ void __launch_bounds__(256) k_forward(Dev d, int local, const int32_t* __restrict__ idx) {
+__global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const int32_t* __restrict__ idx) {
+  extern __shared__ __align__(16) unsigned char fwd_smem[];
+  float* s_alpha = reinterpret_cast<float*>(fwd_smem);  // [Kp] the units' scales as floats
+
   const int lane = threadIdx.x & 31;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int warp = blockIdx.x * FWD_WARPS + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * FWD_WARPS;
   const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
   const int Kq = d.Kq;
+  const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.B * d.W;
 
-  float af[NT][4];
+  int j = warp;
+  int my = (j < d.B && lane < d.W) ? idx_own[(size_t)j * d.W + lane] : -1;
+
   float amax = 0.f;
-#pragma unroll
-  for (int t = 0; t < NT; ++t) {
-    const int q = lane + 32 * t;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      af[t][k] = (q < Kq) ? (float)alpha[4 * q + k] : 0.f;
-      amax = fmaxf(amax, fabsf(af[t][k]));
-    }
-  }
+  for (int mu = threadIdx.x; mu < d.Kp; mu += FWD_THREADS) s_alpha[mu] = (mu < d.K) ? (float)alpha[mu] : 0.f;
+  for (int mu = lane; mu < d.K; mu += 32) amax = fmaxf(amax, fabsf((float)alpha[mu]));
+  __syncthreads();
   amax = warp_max(amax);
-  // theta = tol * xmax; 2^-24 = 5.9604645e-8
-  const float tol = 4.0f * (float)(d.W * d.W + 2 * d.W + 4) * 5.9604645e-8f * amax;
+  // Gap that certifies the float arg-max: 4 x (summation error w*w*u*xmax + scale rounding), u = 2^-24,
+  // with xmax replaced by the bound on |alpha * wt| kept in the control word.
+  const float theta = 4.0f * (float)(d.W * d.W + 2 * d.W + 4) * 5.9604645e-8f * amax * __uint_as_float(d.ctl->wabsmax);
   const bool force64 = (d.flags & FV_FLAG_ACC_FP64) != 0;
 
-  const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.B * d.W;
   int32_t* __restrict__ win_out = reinterpret_cast<int32_t*>(d.pkt_send);
-
-  for (int j = warp; j < d.B; j += nwarps) {
-    const int my = (lane < d.W) ? idx_own[(size_t)j * d.W + lane] : -1;
-    if (__shfl_sync(FULL, my, 0) == -2) {  // absent window
-      if (lane == 0) {
-        win_out[j] = -1;
-        d.aw[j] = 0.f;
-      }
-      continue;
-    }
-    float acc[NT][4];
+  const int zrow = d.N;  // the all-zero row
+  const int nbatch = (d.W + 3) >> 2;
+  int qc[NT];
+  bool live[NT];  // does this lane own real columns in group t?
 #pragma unroll
-    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-    float xmax = 0.f;
-#pragma unroll 2
-    for (int c = 0; c < d.W; ++c) {
-      const int id = __shfl_sync(FULL, my, c);
-      if (id < 0) continue;
-      const float4* __restrict__ row = reinterpret_cast<const float4*>(d.wt + (size_t)id * d.Kp);
+  for (int t = 0; t < NT; ++t) {
+    live[t] = lane + 32 * t < Kq;
+    qc[t] = min(lane + 32 * t, Kq - 1);
+  }
+
+  while (j < d.B) {
+    // ask for the next window now; its ids are fetched while this one is summed
+    int jn = 0;
+    if (lane == 0) jn = nwarps + (int)atomicAdd(&d.ctl->fwd_next, 1u);
+    int winner = -1;
+    float awv = 0.f;
+    int n_my = -1;
+    if (__shfl_sync(FULL, my, 0) != -2) {  // -2 marks a window past the end of the order
+      const int row_id = (my < 0) ? zrow : my;  // lanes >= W hold -1
+      unsigned long long acc[NT][2];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = 0ull;
+      for (int b = 0; b < nbatch; ++b) {
+        const ulonglong2* __restrict__ r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int id = __shfl_sync(FULL, row_id, (4 * b + u) & 31);
+          r[u] = reinterpret_cast<const ulonglong2*>(d.wt + (size_t)id * d.Kp);
+        }
+        ulonglong2 v[4][NT];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int t = 0; t < NT; ++t) v[u][t] = __ldg(r[u] + qc[t]);
+        if (b == 0) {
+          jn = __shfl_sync(FULL, jn, 0);
+          if (jn < d.B && lane < d.W) n_my = idx_own[(size_t)jn * d.W + lane];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)  // position order, as the reference adds
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            add2(acc[t][0], v[u][t].x);
+            add2(acc[t][1], v[u][t].y);
+          }
+      }
+      // scaled activations; padding columns and clamped lanes are pushed to -inf
+      float a[NT][4];
+      float lmax = -INFINITY;
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const int q = lane + 32 * t;
-        if (q < Kq) {
-          const float4 v = __ldg(row + q);
-          acc[t][0] += v.x;
-          acc[t][1] += v.y;
-          acc[t][2] += v.z;
-          acc[t][3] += v.w;
-          xmax = fmaxf(xmax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        const float4 al = *reinterpret_cast<const float4*>(s_alpha + 4 * qc[t]);
+        a[t][0] = lo_f(acc[t][0]) * al.x;
+        a[t][1] = hi_f(acc[t][0]) * al.y;
+        a[t][2] = lo_f(acc[t][1]) * al.z;
+        a[t][3] = hi_f(acc[t][1]) * al.w;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (!live[t] || 4 * qc[t] + k >= d.K) a[t][k] = -INFINITY;
+          lmax = fmaxf(lmax, a[t][k]);
         }
       }
-    }
-    // two largest scaled activations of this lane, then of the warp
-    float b1 = -INFINITY, b2 = -INFINITY;
-    int i1 = 0;
+      const float M = warp_max(lmax);
+      const float thr = M - theta;
+      int near = 0, cand = 0;
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      const int q = lane + 32 * t;
+      for (int t = 0; t < NT; ++t)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int mu = 4 * q + k;
-        if (mu < d.K) {
-          const float a = acc[t][k] * af[t][k];
-          if (a > b1) {
-            b2 = b1;
-            b1 = a;
-            i1 = mu;
-          } else if (a > b2) {
-            b2 = a;
+        for (int k = 0; k < 4; ++k)
+          if (a[t][k] >= thr) {
+            ++near;
+            cand = 4 * qc[t] + k;
           }
-        }
-      }
-    }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-      const float ob1 = __shfl_xor_sync(FULL, b1, o);
-      const float ob2 = __shfl_xor_sync(FULL, b2, o);
-      const int oi1 = __shfl_xor_sync(FULL, i1, o);
-      if (ob1 > b1) {
-        b2 = fmaxf(b1, ob2);
-        b1 = ob1;
-        i1 = oi1;
+      const int total = __reduce_add_sync(FULL, near);
+      if (total == 1 && !force64) {
+        const unsigned holder = __ballot_sync(FULL, near != 0);
+        winner = __shfl_sync(FULL, cand, __ffs(holder) - 1);
       } else {
-        b2 = fmaxf(b2, ob1);
+        winner = exact_winner(d.wt, alpha, d.Kp, Kq, d.K, d.W, zrow, my, lane, -1);
       }
-    }
-    xmax = warp_max(xmax);
-    int winner = i1;
-    if (force64 || !((b1 - b2) > tol * xmax)) winner = exact_winner<NT>(d, alpha, my, lane, -1);
-
-    // weighted activation of the winner: float product with 1/count, double sum over c
-    float x = 0.f;
-    if (lane < d.W && my >= 0) {
-      const float wv = (float)((double)d.wt[(size_t)my * d.Kp + winner] * alpha[winner]);
-      x = wv * __ldg(d.f + (my % d.V));
-    }
-    double s = 0.0;
-    for (int c = 0; c < d.W; ++c) {
-      const float xc = __shfl_sync(FULL, x, c);
-      const int idc = __shfl_sync(FULL, my, c);
-      if (idc >= 0) s += (double)xc;
+      awv = weighted_activation(d, alpha, my, winner, lane);
+    } else {
+      jn = __shfl_sync(FULL, jn, 0);
+      if (jn < d.B && lane < d.W) n_my = idx_own[(size_t)jn * d.W + lane];
     }
     if (lane == 0) {
       win_out[j] = winner;
-      d.aw[j] = (float)s;
+      d.aw[j] = awv;
     }
+    j = jn;
+    my = n_my;
   }
 }
 
 // ---------------------------------------------------------------------------
 // xx[mu] = sum over this rank's windows won by mu of the weighted activation
-// (cuda_funcs.cu:722-744 does this with float atomics in arbitrary order; here
-// the order is fixed: lane-strided partial sums, then a butterfly).
-// One warp per unit; written behind the winners in the outgoing packet.
+// (cuda_funcs.cu:722-744 does this with float atomics in arbitrary order; any order
+// is admissible, this one repeats from run to run).  CTA b takes a contiguous block
+// of windows, warp w of it a contiguous sub-block, 32 windows at a time: lanes with
+// the same winner are found with match.any, the lowest adds their activations in
+// lane order into the warp's private bin array.  Bins are added warp by warp, CTA
+// partials CTA by CTA (by the CTA that finishes last), and xx lands behind the
+// winners in the outgoing packet.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) k_xx(Dev d) {
-  const int lane = threadIdx.x & 31;
-  const int mu = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (mu >= d.Kp) return;
+constexpr int XX_THREADS = 512;
+constexpr int XX_WARPS = XX_THREADS / 32;
+__device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsigned char* xx_smem) {
+  float* bins = reinterpret_cast<float*>(xx_smem);  // [XX_WARPS][Kp]
+  __shared__ unsigned s_ticket;
+  const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
   const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(d.pkt_send);
-  float acc = 0.f;
-  if (mu < d.K)
-    for (int j = lane; j < d.B; j += 32)
-      if (win[j] == mu) acc += d.aw[j];
+  for (int i = threadIdx.x; i < XX_WARPS * d.Kp; i += XX_THREADS) bins[i] = 0.f;
+  __syncthreads();
+  const int per_cta = (d.B + nctas - 1) / nctas;
+  const int per_warp = (per_cta + XX_WARPS - 1) / XX_WARPS;
+  const int lo = cta * per_cta + wic * per_warp;
+  const int hi = min(min(lo + per_warp, (cta + 1) * per_cta), d.B);
+  float* mybins = bins + wic * d.Kp;
+  for (int base = lo; base < hi; base += 32) {
+    const int jw = base + lane;
+    const int w = (jw < hi) ? win[jw] : -1;
+    const float a = (jw < hi) ? d.aw[jw] : 0.f;
+    unsigned m = __match_any_sync(FULL, w);
+    const bool leader = (__ffs(m) - 1) == lane;
+    const int rounds = __reduce_max_sync(FULL, __popc(m));
+    float sum = 0.f;
+    for (int it = 0; it < rounds; ++it) {
+      const int src = m ? (__ffs(m) - 1) : 0;
+      const float v = __shfl_sync(FULL, a, src);
+      if (m) {
+        sum += v;
+        m &= m - 1;
+      }
+    }
+    if (leader && w >= 0) mybins[w] += sum;
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
+    float p = 0.f;
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(FULL, acc, o);
-  if (lane == 0) reinterpret_cast<float*>(d.pkt_send)[d.B + mu] = acc;
+    for (int w = 0; w < XX_WARPS; ++w) p += bins[w * d.Kp + mu];
+    d.xx_part[(size_t)cta * d.Kp + mu] = p;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&d.ctl->xx_ticket, 1u);
+  __syncthreads();
+  if (s_ticket == (unsigned)nctas - 1) {
+    __threadfence();
+    float* __restrict__ xx_out = reinterpret_cast<float*>(d.pkt_send) + d.B;
+    for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
+      float acc = 0.f;
+      if (mu < d.K)
+        for (int c = 0; c < nctas; ++c) acc += __ldcg(d.xx_part + (size_t)c * d.Kp + mu);
+      xx_out[mu] = acc;
+    }
+    if (threadIdx.x == 0) {
+      d.ctl->xx_ticket = 0u;
+      d.ctl->fwd_next = 0u;
+    }
+  }
+}
+__global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d) {
+  extern __shared__ __align__(16) unsigned char xx_smem[];
+  xx_body(d, blockIdx.x, gridDim.x, xx_smem);
 }
 
 // ---------------------------------------------------------------------------
@@ -346,9 +462,20 @@ __global__ void __launch_bounds__(128) k_xx(Dev d) {
 // reference drops a replica's whole row from the combine in that case
 // (cu_special_reduction.cu:42-66).
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_tag(Dev d, const int32_t* __restrict__ idx) {
+// With xx_ctas > 0 (single rank) the first xx_ctas CTAs compute xx instead, side by
+// side with the tagging; tagging then cannot ask whether the rank was active for a
+// unit and tags every slot -- a unit that turns out inactive simply gets its parked
+// weights back unchanged in k_apply.
+__global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, const int32_t* __restrict__ idx, int xx_ctas) {
+  extern __shared__ __align__(16) unsigned char tag_smem[];
+  if ((int)blockIdx.x < xx_ctas) {
+    xx_body(d, blockIdx.x, xx_ctas, tag_smem);
+    return;
+  }
   const int E = d.G * d.B * d.W;
-  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
+  const bool check_active = (xx_ctas == 0);
+  const int nthreads = (gridDim.x - xx_ctas) * blockDim.x;
+  for (int e = (blockIdx.x - xx_ctas) * blockDim.x + threadIdx.x; e < E; e += nthreads) {
     const int i = idx[e];
     if (i < 0) continue;
     const int q = e / d.W;
@@ -356,7 +483,7 @@ __global__ void __launch_bounds__(256) k_tag(Dev d, const int32_t* __restrict__ 
     const uint32_t* __restrict__ pkt = d.pkt_recv + (size_t)r * d.P;
     const int mu = (int)pkt[j];
     if (mu < 0) continue;
-    if (__uint_as_float(pkt[d.B + mu]) == 0.f) continue;
+    if (check_active && __uint_as_float(pkt[d.B + mu]) == 0.f) continue;
     uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt + (size_t)i * d.Kp + mu);
     uint32_t cur = __ldcg(addr);
     const uint32_t tag = TAG_BASE | (uint32_t)(e + 1);
@@ -404,14 +531,22 @@ __device__ __forceinline__ void unit_stats(const Dev& d, int mu, double* X, int*
 //   part 2: column maxima of |wt| over the untouched positions (tags read as 0)
 //           -> colmax; the dense term's maximum is |X*alpha| * colmax.
 // Non-negative floats order like their bit patterns, so maxima are integer.
+//
+// Every thread does both parts: it first loads the count of its slot(s), then
+// streams its rows -- a CTA is `groups` lanes of Kq threads, thread (g, q) owns the
+// four columns of float4 group q and walks rows g, g + stride, ... eight at a time,
+// so every load instruction of a lane covers one whole contiguous row -- and only
+// then finishes the slot's dependent loads, whose latency the row stream has hidden.
 // ---------------------------------------------------------------------------
-template <int NT>
-__global__ void __launch_bounds__(256) k_scan(Dev d, int local, const int32_t* __restrict__ idx) {
+constexpr int SCAN_THREADS = 512;
+constexpr int SCAN_UNROLL = 8;
+__global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, const int32_t* __restrict__ idx) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  double* sC = reinterpret_cast<double*>(smem_raw);          // X*alpha
-  int* sN = reinterpret_cast<int*>(sC + d.Kp);               // active ranks
-  uint32_t* sMax = reinterpret_cast<uint32_t*>(sN + d.Kp);   // CTA column maxima
+  double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
+  int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
+  uint32_t* sMax = reinterpret_cast<uint32_t*>(sN + d.Kp); // CTA column maxima
   const int p = (int)((d.ctl->tick + local) & 1);
+  const int lane = threadIdx.x & 31;
   const double* __restrict__ alpha = d.alpha + p * d.Kp;
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
@@ -423,85 +558,76 @@ __global__ void __launch_bounds__(256) k_scan(Dev d, int local, const int32_t* _
   }
   __syncthreads();
 
-  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  // part 1, first half: counts of this thread's slots (up to two per pass over the grid)
+  const int E = d.G * d.B * d.W;
   const int nthreads = gridDim.x * blockDim.x;
-  const int lane = threadIdx.x & 31;
+  const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
+  const int e1 = e0 + nthreads;
+  const int c0 = (e0 < E) ? d.cnt[e0] : 0;
+  const int c1 = (e1 < E) ? d.cnt[e1] : 0;
 
-  // part 1
-  {
-    const int E = d.G * d.B * d.W;
-    uint32_t tmax = 0u;
-    for (int e = tid; e < E; e += nthreads) {
-      const int c = d.cnt[e];
-      if (c <= 0) continue;
-      const int i = idx[e];
-      const int q = e / d.W;
-      const int r = q / d.B, j = q - r * d.B;
-      const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
-      const double D = -sC[mu] * (double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) / (double)sN[mu];
-      tmax = max(tmax, __float_as_uint(fabsf((float)D)));
-    }
-    tmax = warp_max_u32(tmax);
-    if (lane == 0 && tmax) atomicMax(&d.ncb[p], tmax);
-  }
-
-  // part 2
-  {
-    const int warp = tid >> 5, nwarps = nthreads >> 5;
-    const int Kq = d.Kq;
-    uint32_t m[NT][4];
-#pragma unroll
-    for (int t = 0; t < NT; ++t) m[t][0] = m[t][1] = m[t][2] = m[t][3] = 0u;
-    auto fold_in = [&](int t, const uint4& v) {
+  // part 2: column maxima of |wt| with tags read as 0
+  const int Kq = d.Kq;
+  const int groups = SCAN_THREADS / Kq;  // Kq <= 256, so at least 2
+  const int g = threadIdx.x / Kq, q = threadIdx.x - g * Kq;
+  if (g < groups) {
+    const int stride = gridDim.x * groups;
+    uint32_t m0 = 0u, m1 = 0u, m2 = 0u, m3 = 0u;
+    auto fold_in = [&](const uint4& v) {
       uint32_t u;
-      u = v.x & ABS_MASK; m[t][0] = max(m[t][0], u > TAG_BASE ? 0u : u);
-      u = v.y & ABS_MASK; m[t][1] = max(m[t][1], u > TAG_BASE ? 0u : u);
-      u = v.z & ABS_MASK; m[t][2] = max(m[t][2], u > TAG_BASE ? 0u : u);
-      u = v.w & ABS_MASK; m[t][3] = max(m[t][3], u > TAG_BASE ? 0u : u);
+      u = v.x & ABS_MASK; m0 = max(m0, u > TAG_BASE ? 0u : u);
+      u = v.y & ABS_MASK; m1 = max(m1, u > TAG_BASE ? 0u : u);
+      u = v.z & ABS_MASK; m2 = max(m2, u > TAG_BASE ? 0u : u);
+      u = v.w & ABS_MASK; m3 = max(m3, u > TAG_BASE ? 0u : u);
     };
-    int row = warp;
-    for (; row + nwarps < d.N; row += 2 * nwarps) {
-      const uint4* __restrict__ r0 = reinterpret_cast<const uint4*>(d.wt + (size_t)row * d.Kp);
-      const uint4* __restrict__ r1 = reinterpret_cast<const uint4*>(d.wt + (size_t)(row + nwarps) * d.Kp);
-      uint4 v0[NT], v1[NT];
+    const uint4* __restrict__ base = reinterpret_cast<const uint4*>(d.wt) + q;
+    int row = blockIdx.x * groups + g;
+    for (; row + (SCAN_UNROLL - 1) * stride < d.N; row += SCAN_UNROLL * stride) {
+      uint4 v[SCAN_UNROLL];
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const int q = lane + 32 * t;
-        if (q < Kq) {
-          v0[t] = __ldcg(r0 + q);
-          v1[t] = __ldcg(r1 + q);
-        } else {
-          v0[t] = make_uint4(0, 0, 0, 0);
-          v1[t] = make_uint4(0, 0, 0, 0);
-        }
-      }
+      for (int u = 0; u < SCAN_UNROLL; ++u) v[u] = __ldcg(base + (size_t)(row + u * stride) * Kq);
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        fold_in(t, v0[t]);
-        fold_in(t, v1[t]);
-      }
+      for (int u = 0; u < SCAN_UNROLL; ++u) fold_in(v[u]);
     }
-    for (; row < d.N; row += nwarps) {
-      const uint4* __restrict__ r0 = reinterpret_cast<const uint4*>(d.wt + (size_t)row * d.Kp);
+    if (row < d.N) {  // ragged end: same unrolled batch, rows past the end re-read the first one
+      uint4 v[SCAN_UNROLL];
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const int q = lane + 32 * t;
-        if (q < Kq) fold_in(t, __ldcg(r0 + q));
+      for (int u = 0; u < SCAN_UNROLL; ++u) {
+        const int rr = row + u * stride;
+        v[u] = __ldcg(base + (size_t)(rr < d.N ? rr : row) * Kq);
       }
-    }
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      const int q = lane + 32 * t;
-      if (q < Kq) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (m[t][k]) atomicMax(&sMax[4 * q + k], m[t][k]);
-      }
+      for (int u = 0; u < SCAN_UNROLL; ++u) fold_in(v[u]);
     }
+    if (m0) atomicMax(&sMax[4 * q + 0], m0);
+    if (m1) atomicMax(&sMax[4 * q + 1], m1);
+    if (m2) atomicMax(&sMax[4 * q + 2], m2);
+    if (m3) atomicMax(&sMax[4 * q + 3], m3);
   }
+
+  // part 1, second half: exact D at the touched positions this thread owns
+  uint32_t tmax = 0u;
+  auto touched = [&](int e, int c) {
+    if (c <= 0) return;
+    const int i = idx[e];
+    const int qq = e / d.W;
+    const int r = qq / d.B, j = qq - r * d.B;
+    const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
+    if (sN[mu] == 0) return;  // tagged before the unit proved inactive: no update there
+    const double D = -sC[mu] * (double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) / (double)sN[mu];
+    tmax = max(tmax, __float_as_uint(fabsf((float)D)));
+  };
+  touched(e0, c0);
+  touched(e1, c1);
+  for (int e = e1 + nthreads; e < E; e += nthreads) touched(e, d.cnt[e]);
+  tmax = warp_max_u32(tmax);
+  if (lane == 0 && tmax) atomicMax(&d.ncb[p], tmax);
+
   __syncthreads();
-  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x)
-    if (sMax[mu]) atomicMax(&d.colmax[p * d.Kp + mu], sMax[mu]);
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    const uint32_t v = sMax[mu];
+    if (v && v > __ldcg(&d.colmax[p * d.Kp + mu])) atomicMax(&d.colmax[p * d.Kp + mu], v);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -511,9 +637,11 @@ __global__ void __launch_bounds__(256) k_scan(Dev d, int local, const int32_t* _
 // and clear their count.  CTA 0 publishes alpha' and the step's nc and s, and
 // clears the maxima the next step will accumulate into.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx) {
+__global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx,
+                                               int32_t* __restrict__ idx_next) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  double* sCoef = reinterpret_cast<double*>(smem_raw);  // s / (n * alpha')
+  double* sX = reinterpret_cast<double*>(smem_raw);  // mean xx over active ranks, later s / (n * alpha')
+  int* sN = reinterpret_cast<int*>(sX + d.Kp);
   __shared__ float sRed[8];
   __shared__ float sScale;
   const int p = (int)((d.ctl->tick + local) & 1);
@@ -521,10 +649,12 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   double* __restrict__ alpha_next = d.alpha + (p ^ 1) * d.Kp;
 
   float dense = 0.f;
-  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x) {
-    double X;
-    int n;
-    unit_stats(d, mu, &X, &n);
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    double X = 0.0;
+    int n = 0;
+    if (mu < d.K) unit_stats(d, mu, &X, &n);
+    sX[mu] = X;
+    sN[mu] = n;
     if (n > 0) dense = fmaxf(dense, (float)(fabs(X * alpha[mu]) * (double)__uint_as_float(d.colmax[p * d.Kp + mu])));
   }
   dense = warp_max(dense);
@@ -544,38 +674,48 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   __syncthreads();
   const float s = sScale;
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
-    double X = 0.0;
-    int n = 0;
-    if (mu < d.K) unit_stats(d, mu, &X, &n);
+    const int n = sN[mu];
     double a = alpha[mu];
     double coef = 0.0;
     if (n > 0) {
-      a = a * (1.0 - (double)s * X);
+      a = a * (1.0 - (double)s * sX[mu]);
       if (a != 0.0)
         coef = (double)s / ((double)n * a);
       else
         atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
     }
-    sCoef[mu] = coef;
+    sX[mu] = coef;
     if (blockIdx.x == 0) {
       alpha_next[mu] = a;
       d.colmax[(p ^ 1) * d.Kp + mu] = 0u;
     }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) d.ncb[p ^ 1] = 0u;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    d.ncb[p ^ 1] = 0u;
+    d.ctl->fwd_next = 0u;
+  }
   __syncthreads();
 
   const int E = d.G * d.B * d.W;
+  const unsigned long long next_step = d.ctl->base + local + 1;
+  uint32_t vmax = 0u;
   for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
+    // input ids of the next step: independent of the weights, so they are prepared here
+    if (idx_next) idx_next[e] = input_id(d, next_step, e);
     const int c = d.cnt[e];
     if (c <= 0) continue;
     const int i = idx[e];
     const int q = e / d.W;
     const int r = q / d.B, j = q - r * d.B;
     const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
-    d.wt[(size_t)i * d.Kp + mu] = (float)((double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) * sCoef[mu]);
+    const float v = (float)((double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) * sX[mu]);
+    d.wt[(size_t)i * d.Kp + mu] = v;
     d.cnt[e] = 0;
+    vmax = max(vmax, __float_as_uint(fabsf(v)));
   }
+  // keep the bound on max |wt| valid for the next forward pass
+  vmax = warp_max_u32(vmax);
+  if ((threadIdx.x & 31) == 0 && vmax > d.ctl->wabsmax) atomicMax(&d.ctl->wabsmax, vmax);
 }
 
 // ---------------------------------------------------------------------------
@@ -585,6 +725,7 @@ __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
   // `local` = steps already launched in this call: the buffer the next step would read
   const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
   const size_t total = (size_t)d.N * d.Kq;
+  float vmax = 0.f;
   for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (size_t)gridDim.x * blockDim.x) {
     const int q = (int)(v % d.Kq);
     float4* ptr = reinterpret_cast<float4*>(d.wt) + v;
@@ -594,11 +735,27 @@ __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
     x.z = (float)((double)x.z * alpha[4 * q + 2]);
     x.w = (float)((double)x.w * alpha[4 * q + 3]);
     *ptr = x;
+    vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
   }
+  vmax = warp_max(vmax);
+  if ((threadIdx.x & 31) == 0) atomicMax(&d.ctl->wabsmax_fold, __float_as_uint(vmax));
 }
+// Runs after k_fold or after new weights were loaded; both collect max |wt| in wabsmax_fold.
 __global__ void k_reset_alpha(Dev d) {
   // both buffers become 1, so the parity of the next step does not matter
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 2 * d.Kp; i += gridDim.x * blockDim.x) d.alpha[i] = 1.0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    d.ctl->wabsmax = d.ctl->wabsmax_fold;
+    d.ctl->wabsmax_fold = 0u;
+  }
+}
+__global__ void k_absmax(Dev d) {
+  const size_t total = (size_t)d.N * d.Kp;
+  float vmax = 0.f;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (size_t)gridDim.x * blockDim.x)
+    vmax = fmaxf(vmax, fabsf(d.wt[v]));
+  vmax = warp_max(vmax);
+  if ((threadIdx.x & 31) == 0) atomicMax(&d.ctl->wabsmax_fold, __float_as_uint(vmax));
 }
 
 // ---------------------------------------------------------------------------
@@ -738,6 +895,7 @@ struct fv_trainer {
   int32_t* d_idx = nullptr;
   int32_t* d_idx_stage[2] = {nullptr, nullptr};
   uint32_t* d_pkt = nullptr;
+  float* d_xx_part = nullptr;
   float* d_aw = nullptr;
   int32_t* d_cnt = nullptr;
   float* d_saved = nullptr;
@@ -747,8 +905,9 @@ struct fv_trainer {
   float* d_log = nullptr;
   size_t log_cap = 0;
   unsigned long long steps_since_fold = 0;
-  int fwd_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
-  size_t scan_smem = 0, apply_smem = 0;
+  unsigned long long ticks = 0;  // host copy of StepCtl::tick
+  int fwd_grid = 0, xx_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
+  size_t fwd_smem = 0, xx_smem = 0, scan_smem = 0, apply_smem = 0;
 };
 
 namespace {
@@ -779,16 +938,11 @@ int grid_for(size_t work, int block, int cap) {
 
 template <int NT>
 void launch_forward(fv_trainer* tr, int local, const int32_t* idx) {
-  k_forward<NT><<<tr->fwd_grid, 256, 0, tr->stream>>>(tr->d, local, idx);
+  k_forward<NT><<<tr->fwd_grid, FWD_THREADS, tr->fwd_smem, tr->stream>>>(tr->d, local, idx);
 }
 template <int NT>
-void launch_scan(fv_trainer* tr, int local, const int32_t* idx) {
-  k_scan<NT><<<tr->scan_grid, 256, tr->scan_smem, tr->stream>>>(tr->d, local, idx);
-}
-template <int NT>
-void occupancy(int* fwd, int* scan, size_t scan_smem, cudaError_t* err) {
-  *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(fwd, k_forward<NT>, 256, 0);
-  if (*err == cudaSuccess) *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(scan, k_scan<NT>, 256, scan_smem);
+void forward_occupancy(int* fwd, size_t fwd_smem, cudaError_t* err) {
+  *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(fwd, k_forward<NT>, FWD_THREADS, fwd_smem);
 }
 
 #define FV_DISPATCH_NT(nt, fn, ...)     \
@@ -814,44 +968,48 @@ int fold_weights(fv_trainer* tr, int local) {
   return FV_OK;
 }
 
-// One global step on tr->stream; `idx` = device array of this step's input ids.
-// Returns the number of kernels launched through *launches.
-int enqueue_step(fv_trainer* tr, int local, int32_t* idx, bool build_idx, cudaEvent_t* marks, uint64_t* launches) {
+// One global step on tr->stream.  `idx` holds this step's input ids (all ranks'
+// windows); when idx_next is given, the step also prepares the next step's ids there.
+// Adds the kernels launched to *launches.
+int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, int32_t* idx_next, cudaEvent_t* marks,
+                 uint64_t* launches) {
   const Dev& d = tr->d;
-  if (build_idx) {
-    k_build_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, local, idx);
-    *launches += 1;
-  }
+  const bool emulate = (d.flags & FV_FLAG_EMULATE_RANKS) != 0;
+  const bool single = (d.G == 1);
   if (marks) FV_CUDA(cudaEventRecord(marks[0], tr->stream));
-  if (d.flags & FV_FLAG_EMULATE_RANKS) {
+  if (emulate && !single) {
     // every rank's block in turn, each into its own packet slot
     const Dev own = tr->d;
     for (int r = 0; r < own.G; ++r) {
       tr->d.rank = r;
       tr->d.pkt_send = own.pkt_recv + (size_t)r * own.P;
       FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
-      k_xx<<<(own.Kp * 32 + 127) / 128, 128, 0, tr->stream>>>(tr->d);
+      k_xx<<<tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream>>>(tr->d);
       *launches += 2;
     }
     tr->d = own;
-    *launches -= 2;
     if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
   } else {
     FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
+    *launches += 1;
     if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
-    k_xx<<<(d.Kp * 32 + 127) / 128, 128, 0, tr->stream>>>(d);
-  }
-  if (d.G > 1 && !(d.flags & FV_FLAG_EMULATE_RANKS)) {
-    const int rc = g_nccl.AllGather(d.pkt_send, d.pkt_recv, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
-    if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+    if (!single) {
+      k_xx<<<tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream>>>(d);
+      *launches += 1;
+      const int rc = g_nccl.AllGather(d.pkt_send, d.pkt_recv, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
+      if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+    }
   }
   if (marks) FV_CUDA(cudaEventRecord(marks[2], tr->stream));
-  k_tag<<<tr->entry_grid, 256, 0, tr->stream>>>(d, idx);
-  FV_DISPATCH_NT(tr->NT, launch_scan, tr, local, idx);
-  k_apply<<<tr->apply_grid, 256, tr->apply_smem, tr->stream>>>(d, local, idx);
+  if (single)  // xx is computed by the first CTAs of the tagging kernel
+    k_tag<<<tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream>>>(d, idx, tr->xx_grid);
+  else
+    k_tag<<<tr->tag_grid, XX_THREADS, 0, tr->stream>>>(d, idx, 0);
+  k_scan<<<tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream>>>(d, local, idx);
+  k_apply<<<tr->apply_grid, 256, tr->apply_smem, tr->stream>>>(d, local, idx, idx_next);
   if (marks) FV_CUDA(cudaEventRecord(marks[3], tr->stream));
   FV_CUDA(cudaGetLastError());
-  *launches += 5;
+  *launches += 3;
   tr->steps_since_fold += 1;
   return FV_OK;
 }
@@ -907,11 +1065,16 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   }
 
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps);
-  FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   uint64_t launches = 1;
+  if (!idx_host) {  // ids of the first step; every later step's are prepared by the step before
+    k_build_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, 0, tr->d_idx + (tr->ticks & 1) * step_ids);
+    launches += 1;
+  }
+  FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   unsigned long long chunk_id = 0;
   for (unsigned long long k = 0; k < nsteps; ++k) {
-    int32_t* idx = tr->d_idx;
+    const int32_t* idx = tr->d_idx + ((tr->ticks + k) & 1) * step_ids;
+    int32_t* idx_next = tr->d_idx + ((tr->ticks + k + 1) & 1) * step_ids;
     if (idx_host) {
       const int b = (int)(chunk_id & 1);
       if (k % STAGE_STEPS == 0) {
@@ -926,9 +1089,10 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
         launches += 1;
       }
       idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * step_ids;
+      idx_next = nullptr;
     }
     cudaEvent_t* marks = (k % PHASE_SAMPLE == 0) ? &tr->phase_events[(k / PHASE_SAMPLE) * 4] : nullptr;
-    FV_TRY(enqueue_step(tr, (int)k, idx, idx_host == nullptr, marks, &launches));
+    FV_TRY(enqueue_step(tr, (int)k, idx, idx_next, marks, &launches));
     if (idx_host && ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps)) {
       FV_CUDA(cudaEventRecord(tr->ev_used[chunk_id & 1], tr->stream));
       ++chunk_id;
@@ -939,6 +1103,7 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
     }
   }
   k_advance<<<1, 1, 0, tr->stream>>>(tr->d_ctl, nsteps);
+  tr->ticks += nsteps;
   launches += 1;
   FV_CUDA(cudaEventRecord(tr->ev_end, tr->stream));
   std::vector<float> log(2 * nsteps);
@@ -997,7 +1162,7 @@ void free_all(fv_trainer* tr) {
   cudaSetDevice(tr->device);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,   tr->d_idx,
-                  tr->d_pkt, tr->d_aw,    tr->d_cnt,    tr->d_saved,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+                  tr->d_pkt, tr->d_xx_part, tr->d_aw, tr->d_cnt,    tr->d_saved,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -1043,12 +1208,11 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->NT = (d.Kq + 31) / 32;
 
   const size_t E = (size_t)d.G * d.B * d.W;
-  FV_TRY(dev_alloc(&tr->d_wt, (size_t)d.N * d.Kp));
+  FV_TRY(dev_alloc(&tr->d_wt, ((size_t)d.N + 1) * d.Kp));  // one extra all-zero row for padding positions
   FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
-  FV_TRY(dev_alloc(&tr->d_idx, E));
+  FV_TRY(dev_alloc(&tr->d_idx, 2 * E));  // this step's ids and the next step's
   FV_TRY(dev_alloc(&tr->d_pkt, (size_t)d.G * d.P));
-  FV_TRY(dev_alloc(&tr->d_aw, (size_t)d.B));
   FV_TRY(dev_alloc(&tr->d_cnt, E));
   FV_TRY(dev_alloc(&tr->d_saved, E));
   FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
@@ -1065,7 +1229,6 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.f = tr->d_f;
   d.pkt_recv = tr->d_pkt;
   d.pkt_send = tr->d_pkt + (size_t)d.rank * d.P;  // in-place all-gather
-  d.aw = tr->d_aw;
   d.cnt = tr->d_cnt;
   d.saved = tr->d_saved;
   d.colmax = tr->d_colmax;
@@ -1075,19 +1238,28 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_CUDA(cudaGetLastError());
 
   // launch geometry: whole multiples of the SM count
+  tr->fwd_smem = (size_t)d.Kp * sizeof(float);
+  tr->xx_smem = (size_t)XX_WARPS * d.Kp * sizeof(float);
   tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + sizeof(uint32_t));
-  tr->apply_smem = (size_t)d.Kp * sizeof(double);
-  int fwd_bps = 0, scan_bps = 0;
+  tr->apply_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int));
+  FV_CUDA(cudaFuncSetAttribute(k_xx, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
+  FV_CUDA(cudaFuncSetAttribute(k_tag, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
+  int fwd_bps = 0;
   cudaError_t oerr = cudaSuccess;
-  FV_DISPATCH_NT(tr->NT, occupancy, &fwd_bps, &scan_bps, tr->scan_smem, &oerr);
+  FV_DISPATCH_NT(tr->NT, forward_occupancy, &fwd_bps, tr->fwd_smem, &oerr);
   FV_CUDA(oerr);
   if (fwd_bps < 1) fwd_bps = 1;
-  if (scan_bps < 1) scan_bps = 1;
-  if (scan_bps > 2) scan_bps = 2;
-  tr->fwd_grid = grid_for((size_t)d.B * 32, 256, tr->num_sms * fwd_bps);
-  tr->scan_grid = tr->num_sms * scan_bps;
+  tr->fwd_grid = grid_for((size_t)d.B * 32, FWD_THREADS, tr->num_sms * fwd_bps);
+  tr->xx_grid = grid_for((size_t)d.B, 2048, 8);
+  tr->scan_grid = tr->num_sms * 2;
+  tr->tag_grid = grid_for(E, XX_THREADS, tr->num_sms * 4);
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
   tr->apply_grid = grid_for(E, 256, tr->num_sms * 4);
+  FV_TRY(dev_alloc(&tr->d_xx_part, (size_t)tr->xx_grid * d.Kp));
+  FV_TRY(dev_alloc(&tr->d_aw, (size_t)d.B));
+  d.xx_part = tr->d_xx_part;
+  d.aw = tr->d_aw;
+  FV_CUDA(cudaMemsetAsync(tr->d_wt, 0, ((size_t)d.N + 1) * d.Kp * sizeof(float), tr->stream));
   FV_CUDA(cudaStreamSynchronize(tr->stream));
   return FV_OK;
 }
@@ -1215,6 +1387,7 @@ int fv_trainer_set_weights(fv_trainer* tr, const float* w_kn) {
   if (e == cudaSuccess) {
     dim3 grid((d.N + 31) / 32, (d.Kp + 31) / 32), block(32, 8);
     k_to_device_layout<<<grid, block, 0, tr->stream>>>(tmp, tr->d_wt, d.K, d.Kp, d.N);
+    k_absmax<<<tr->num_sms * 4, 256, 0, tr->stream>>>(d);
     k_reset_alpha<<<4, 256, 0, tr->stream>>>(d);
     e = cudaGetLastError();
   }
