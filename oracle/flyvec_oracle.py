@@ -15,7 +15,7 @@ Pinning status
 --------------
 * window enumeration: pinned against the reference's own ``prune_input.cpp``
   compiled for the host (see ``oracle/build_oracle.py`` and
-  ``tests/test_oracle_pins.py``).
+  ``tests/test_oracle.py``).
 * hashing: pinned against golden vectors produced by executing the reference's
   unmodified ``flyvec/core.py`` (see ``tests/golden/make_hash_golden.py``).
 * training step: the reference ships no test, golden vector or fixture for its
@@ -368,3 +368,38 @@ def pack_codes(codes: np.ndarray) -> np.ndarray:
     """Bit-pack {0,1} codes little-endian within each byte: unit ``mu`` is bit
     ``mu % 8`` of byte ``mu // 8``."""
     return np.packbits(codes.astype(np.uint8), axis=-1, bitorder="little")
+
+
+# --------------------------------------------------------------------------
+# The same step in the form the CUDA kernels use (no dense ds): what a rank can
+# rebuild from the winners and xx vectors of all ranks plus the shared corpus.
+# --------------------------------------------------------------------------
+def closed_form_update(Wm, idx_per_device, win_per_device, xx_per_device, f, V, eps, prec=1e-30):
+    """``W_mu <- (1 - s X_mu) W_mu + s S_mu`` for units active on at least one rank.
+
+    ``X_mu`` is the mean of ``xx_dev[mu]`` over the ranks where it is non-zero and
+    ``S_mu,i`` the mean over those ranks of ``count_dev(mu, i) * f_i``; this is
+    cu_special_reduction.cu:42-67 applied to ``ds = -xx W + scatter``
+    (cuda_funcs.cu:394-406, 657-672) and the update of
+    cu_special_reduction.cu:336-348, evaluated in double instead of following the
+    reference's float rounding steps.  Returns ``(W_new, nc, s)``.
+    """
+    K, N = Wm.shape
+    xx = np.stack(xx_per_device).astype(F64)
+    act = xx != 0
+    n = act.sum(axis=0)
+    X = np.where(n > 0, xx.sum(axis=0, where=act) / np.maximum(n, 1), 0.0)
+    S = np.zeros((K, N), dtype=F64)
+    for idx, win, a in zip(idx_per_device, win_per_device, act):
+        if idx.shape[0] == 0:
+            continue
+        rows = np.repeat(win, idx.shape[1])
+        flat = idx.reshape(-1)
+        ok = (flat >= 0) & a[rows]
+        np.add.at(S, (rows[ok], flat[ok]), f[flat[ok] % V].astype(F64))
+    S /= np.maximum(n, 1)[:, None]
+    D = np.where((n > 0)[:, None], -X[:, None] * Wm.astype(F64) + S, 0.0)
+    nc = F32(np.abs(D).max())
+    s = F32(F32(eps) / F32(prec)) if F32(prec) > nc else F32(F32(eps) / nc)
+    W_new = np.where((n > 0)[:, None], Wm.astype(F64) + F64(s) * D, Wm.astype(F64)).astype(F32)
+    return W_new, nc, s
