@@ -93,6 +93,7 @@ _PROTOTYPES = {
     "fv_hasher_destroy": ([_P], C.c_int),
     "fv_hasher_get_weights": ([_P, _P], C.c_int),
     "fv_hash_tokens": ([_P, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P], C.c_int),
+    "fv_hash_tokens_static": ([_P, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P], C.c_int),
     "fv_hash_windows": ([_P, _P, C.c_uint64, C.c_uint32, _P, C.c_uint32, C.c_uint32, _P], C.c_int),
     "fv_hash_tokens_device": ([_P, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P, C.POINTER(C.c_double)], C.c_int),
     "fv_hash_windows_device": ([_P, _P, C.c_uint64, C.c_uint32, C.c_int, C.c_uint32, C.c_uint32, _P,

@@ -504,6 +504,66 @@ int fv_hash_tokens(fv_hasher* hs, const int32_t* ids, uint64_t n, uint32_t hash_
   return hash_host(hs, 0, ids, n, 1, 0, hash_length, flags, out);
 }
 
+// ---------------------------------------------------------------------------
+// Token hashing without any allocation.
+//
+// fv_hash_tokens stages the ids and the codes in device buffers it allocates and
+// frees on every call.  That is fine for bulk work, but it hurts two kinds of
+// callers of this library: a service that hashes a few query tokens at a time on
+// the GPU a trainer is running on (cudaFree waits for the whole device, so every
+// small request would stall the training stream), and a process whose device
+// memory is owned up front by somebody else's pool, where an extra cudaMalloc may
+// simply fail.  For them the staging area is the fixed array below: it is part of
+// the library image, so every GPU that loads the library holds these
+// FV_STATIC_SCRATCH_BYTES until the process exits, whether the call is used or not.
+//
+// The array's name is only a handle on the host; the device address is looked up
+// once per device with cudaGetSymbolAddress (with that device current) the first
+// time the entry point runs there.  Make that first call before starting any
+// stream capture.  All calls share the one array and it keeps whatever the last
+// call left in it: the ids are overwritten by the upload and the kernel writes every
+// output byte that is copied back, so nothing in it has to be cleared (the error
+// word the kernel reports through is reset before each launch).  Two calls that
+// overlap on the same GPU -- different hashers, different host threads -- would
+// race on the array; callers must serialise them.
+// ---------------------------------------------------------------------------
+#define FV_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_hash_scratch[FV_STATIC_SCRATCH_BYTES];
+static void* g_hash_scratch_addr[64] = {nullptr};
+
+int fv_hash_tokens_static(fv_hasher* hs, const int32_t* ids, uint64_t n, uint32_t hash_length, uint32_t flags,
+                          uint8_t* out) {
+  FV_REQUIRE(hs && (n == 0 || (ids && out)), FV_ERR_INVALID, "fv_hash_tokens_static: NULL argument");
+  FV_REQUIRE(hash_length >= 1 && (int)hash_length < hs->h.K, FV_ERR_INVALID,
+             "hash_length must be in [1, K-1] (K = %d), got %u", hs->h.K, hash_length);
+  FV_REQUIRE(hs->device >= 0 && hs->device < 64, FV_ERR_INVALID, "device %d out of range", hs->device);
+  if (n == 0) return FV_OK;
+  const size_t out_per = (flags & FV_HASH_BYTES) ? (size_t)hs->h.K : (size_t)((hs->h.K + 7) / 8);
+  const size_t per_item = sizeof(int32_t) + out_per;
+  const size_t max_items = (FV_STATIC_SCRATCH_BYTES - 256) / per_item;
+  FV_REQUIRE(n <= max_items, FV_ERR_INVALID,
+             "fv_hash_tokens_static: %llu tokens need %llu bytes of staging, the fixed area holds %u bytes "
+             "(at most %llu tokens for K = %d in this output format); split the batch or use fv_hash_tokens",
+             (unsigned long long)n, (unsigned long long)(n * per_item + 256), FV_STATIC_SCRATCH_BYTES,
+             (unsigned long long)max_items, hs->h.K);
+  fv::DeviceGuard guard(hs->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", hs->device);
+  if (!g_hash_scratch_addr[hs->device]) {
+    void* p = nullptr;
+    FV_CUDA(cudaGetSymbolAddress(&p, g_hash_scratch));
+    g_hash_scratch_addr[hs->device] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_hash_scratch_addr[hs->device]);
+  int32_t* d_ids = reinterpret_cast<int32_t*>(base);
+  uint8_t* d_out = base + ((n * sizeof(int32_t) + 255) & ~(size_t)255);
+  FV_CUDA(cudaMemcpyAsync(d_ids, ids, n * sizeof(int32_t), cudaMemcpyHostToDevice, hs->stream));
+  const int rc = run_hash(hs, 0, d_ids, n, 0, hash_length, flags, d_out, nullptr);
+  if (rc != FV_OK) return rc;
+  FV_CUDA(cudaMemcpyAsync(out, d_out, n * out_per, cudaMemcpyDeviceToHost, hs->stream));
+  FV_CUDA(cudaStreamSynchronize(hs->stream));
+  return FV_OK;
+}
+
 int fv_hash_windows(fv_hasher* hs, const int32_t* idx, uint64_t nwin, uint32_t window, const float* inv_freq,
                     uint32_t hash_length, uint32_t flags, uint8_t* out) {
   FV_REQUIRE(hs && (nwin == 0 || (idx && out)), FV_ERR_INVALID, "fv_hash_windows: NULL argument");

@@ -204,6 +204,21 @@ class Hasher:
         check(_lib.lib().fv_hash_tokens(self._h, ptr(ids), ids.size, hash_length, flags, ptr(out)))
         return out if packed else out.view(np.int8)
 
+    #: size of the library's fixed staging area used by :meth:`hash_tokens_static`
+    STATIC_SCRATCH_BYTES = 8 << 20
+
+    def hash_tokens_static(self, ids, hash_length: int = 50, packed: bool = False) -> np.ndarray:
+        """Like :meth:`hash_tokens`, but through the entry point that allocates no device
+        memory: for hashing small batches while a trainer is busy on the same GPU, or when
+        another pool owns the device memory.  The batch must fit the fixed staging area
+        (``len(ids) * (4 + bytes per code) + 256 <= 8 MiB``); concurrent calls on one GPU
+        must be serialised by the caller."""
+        ids = as_c(ids, np.int32).reshape(-1)
+        flags = _lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES
+        out = np.empty((ids.size, self.code_bytes(packed)), np.uint8)
+        check(_lib.lib().fv_hash_tokens_static(self._h, ptr(ids), ids.size, hash_length, flags, ptr(out)))
+        return out if packed else out.view(np.int8)
+
     def hash_windows(self, idx, inv_freq=None, hash_length: int = 50, packed: bool = False) -> np.ndarray:
         idx = as_c(idx, np.int32)
         assert idx.ndim == 2

@@ -176,6 +176,14 @@ int fv_hasher_get_weights(fv_hasher* h, float* w_kn);
  * activations = column V+id, code = activation > midpoint of the hash_length-th
  * and next largest; id 0 gives zeros. */
 int fv_hash_tokens(fv_hasher* h, const int32_t* ids, uint64_t n, uint32_t hash_length, uint32_t flags, uint8_t* out);
+/* No counterpart in the reference.  Same result as fv_hash_tokens, but the call allocates nothing: ids and codes
+ * are staged in a fixed 8 MiB device array that is part of the library (held by every GPU that loads it).  Meant for
+ * callers that must not allocate while they hash: small requests served next to a running trainer (cudaFree would
+ * stall its stream) or processes whose device memory belongs to another pool.  n * (4 + bytes per code) + 256 must
+ * fit into 8 MiB, else FV_ERR_INVALID.  The first call on a device looks up the array's address and should be made
+ * before any stream capture is started; overlapping calls on one GPU race on the array. */
+int fv_hash_tokens_static(fv_hasher* h, const int32_t* ids, uint64_t n, uint32_t hash_length, uint32_t flags,
+                          uint8_t* out);
 /* Context-dependent codes: activation of a window as the trainer's forward pass
  * computes it (cuda_funcs.cu:289-305 weighted by inv_freq, or 248-263 with
  * FV_HASH_RAW / inv_freq == NULL), then the same threshold rule. */
