@@ -78,6 +78,12 @@ struct Dev {
   float* s_log;
 };
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization
+// attribute may start while its predecessor in the stream is still draining; it must
+// not touch anything the predecessor writes before this wait returns (the wait ends
+// when the predecessor grid has completed and its memory is visible).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
@@ -95,6 +101,7 @@ __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps) {
   ctl->xx_ticket = 0u;
 }
 __global__ void k_advance(StepCtl* ctl, unsigned long long n) {
+  grid_dependency_wait();
   ctl->base += n;
   ctl->tick += n;
 }
@@ -131,6 +138,7 @@ __device__ __forceinline__ int input_id(const Dev& d, unsigned long long step, i
   return val;
 }
 __global__ void k_build_idx(Dev d, int local, int32_t* __restrict__ idx) {
+  grid_dependency_wait();
   const unsigned long long step = d.ctl->base + local;
   const int total = d.G * d.B * d.W;
   for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x)
@@ -139,6 +147,7 @@ __global__ void k_build_idx(Dev d, int local, int32_t* __restrict__ idx) {
 
 // Checks host-supplied input ids (streaming mode) against [ -2, N ).
 __global__ void k_check_idx(Dev d, const int32_t* __restrict__ idx, size_t total) {
+  grid_dependency_wait();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
     const int v = idx[e];
     if (v >= d.N || v < -2) atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
@@ -261,6 +270,7 @@ __device__ __forceinline__ float weighted_activation(const Dev& d, const double*
 //     maximum; otherwise the window is redone in double on the spot.
 template <int NT>
 __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const int32_t* __restrict__ idx) {
+  grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char fwd_smem[];
   float* s_alpha = reinterpret_cast<float*>(fwd_smem);  // [Kp] the units' scales as floats
 
@@ -449,6 +459,7 @@ __device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsign
   }
 }
 __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d) {
+  grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char xx_smem[];
   xx_body(d, blockIdx.x, gridDim.x, xx_smem);
 }
@@ -467,6 +478,7 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d) {
 // unit and tags every slot -- a unit that turns out inactive simply gets its parked
 // weights back unchanged in k_apply.
 __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, const int32_t* __restrict__ idx, int xx_ctas) {
+  grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char tag_smem[];
   if ((int)blockIdx.x < xx_ctas) {
     xx_body(d, blockIdx.x, xx_ctas, tag_smem);
@@ -541,6 +553,7 @@ __device__ __forceinline__ void unit_stats(const Dev& d, int mu, double* X, int*
 constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_UNROLL = 8;
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, const int32_t* __restrict__ idx) {
+  grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
   int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
@@ -639,6 +652,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx,
                                                int32_t* __restrict__ idx_next) {
+  grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sX = reinterpret_cast<double*>(smem_raw);  // mean xx over active ranks, later s / (n * alpha')
   int* sN = reinterpret_cast<int*>(sX + d.Kp);
@@ -722,6 +736,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
 // Folding the scale into the weights: wt[i][mu] *= alpha[mu]; then alpha = 1.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
+  grid_dependency_wait();
   // `local` = steps already launched in this call: the buffer the next step would read
   const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
   const size_t total = (size_t)d.N * d.Kq;
@@ -742,6 +757,7 @@ __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
 }
 // Runs after k_fold or after new weights were loaded; both collect max |wt| in wabsmax_fold.
 __global__ void k_reset_alpha(Dev d) {
+  grid_dependency_wait();
   // both buffers become 1, so the parity of the next step does not matter
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 2 * d.Kp; i += gridDim.x * blockDim.x) d.alpha[i] = 1.0;
   if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -936,9 +952,25 @@ int grid_for(size_t work, int block, int cap) {
   return (int)g;
 }
 
+// Launch with programmatic stream serialization (see grid_dependency_wait).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <int NT>
 void launch_forward(fv_trainer* tr, int local, const int32_t* idx) {
-  k_forward<NT><<<tr->fwd_grid, FWD_THREADS, tr->fwd_smem, tr->stream>>>(tr->d, local, idx);
+  launch_pdl(k_forward<NT>, tr->fwd_grid, FWD_THREADS, tr->fwd_smem, tr->stream, tr->d, local, idx);
 }
 template <int NT>
 void forward_occupancy(int* fwd, size_t fwd_smem, cudaError_t* err) {
@@ -984,7 +1016,7 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, int32_t* idx_nex
       tr->d.rank = r;
       tr->d.pkt_send = own.pkt_recv + (size_t)r * own.P;
       FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
-      k_xx<<<tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream>>>(tr->d);
+      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, tr->d);
       *launches += 2;
     }
     tr->d = own;
@@ -994,7 +1026,7 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, int32_t* idx_nex
     *launches += 1;
     if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
     if (!single) {
-      k_xx<<<tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream>>>(d);
+      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d);
       *launches += 1;
       const int rc = g_nccl.AllGather(d.pkt_send, d.pkt_recv, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
       if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
@@ -1002,11 +1034,11 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, int32_t* idx_nex
   }
   if (marks) FV_CUDA(cudaEventRecord(marks[2], tr->stream));
   if (single)  // xx is computed by the first CTAs of the tagging kernel
-    k_tag<<<tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream>>>(d, idx, tr->xx_grid);
+    launch_pdl(k_tag, tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, idx, tr->xx_grid);
   else
-    k_tag<<<tr->tag_grid, XX_THREADS, 0, tr->stream>>>(d, idx, 0);
-  k_scan<<<tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream>>>(d, local, idx);
-  k_apply<<<tr->apply_grid, 256, tr->apply_smem, tr->stream>>>(d, local, idx, idx_next);
+    launch_pdl(k_tag, tr->tag_grid, XX_THREADS, (size_t)0, tr->stream, d, idx, 0);
+  launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
+  launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx, idx_next);
   if (marks) FV_CUDA(cudaEventRecord(marks[3], tr->stream));
   FV_CUDA(cudaGetLastError());
   *launches += 3;
