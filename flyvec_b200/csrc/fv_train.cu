@@ -30,6 +30,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -83,6 +84,9 @@ struct Dev {
 // not touch anything the predecessor writes before this wait returns (the wait ends
 // when the predecessor grid has completed and its memory is visible).
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// (An explicit early griddepcontrol.launch_dependents made the step slower on B200 --
+// resident-but-waiting CTAs of the next kernel take slots from the running one -- so
+// the dependents start at the implicit trigger, when this grid's CTAs exit.)
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -413,24 +417,36 @@ __device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsign
   const int lo = cta * per_cta + wic * per_warp;
   const int hi = min(min(lo + per_warp, (cta + 1) * per_cta), d.B);
   float* mybins = bins + wic * d.Kp;
-  for (int base = lo; base < hi; base += 32) {
-    const int jw = base + lane;
-    const int w = (jw < hi) ? win[jw] : -1;
-    const float a = (jw < hi) ? d.aw[jw] : 0.f;
-    unsigned m = __match_any_sync(FULL, w);
-    const bool leader = (__ffs(m) - 1) == lane;
-    const int rounds = __reduce_max_sync(FULL, __popc(m));
-    float sum = 0.f;
-    for (int it = 0; it < rounds; ++it) {
-      const int src = m ? (__ffs(m) - 1) : 0;
-      const float v = __shfl_sync(FULL, a, src);
-      if (m) {
-        sum += v;
-        m &= m - 1;
-      }
+  constexpr int XX_PRE = 4;  // chunks of 32 windows whose loads are issued together
+  for (int base0 = lo; base0 < hi; base0 += 32 * XX_PRE) {
+    int wv[XX_PRE];
+    float av[XX_PRE];
+#pragma unroll
+    for (int u = 0; u < XX_PRE; ++u) {
+      const int jw = base0 + 32 * u + lane;
+      wv[u] = (jw < hi) ? win[jw] : -1;
+      av[u] = (jw < hi) ? d.aw[jw] : 0.f;
     }
-    if (leader && w >= 0) mybins[w] += sum;
-    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < XX_PRE; ++u) {
+      if (base0 + 32 * u >= hi) break;
+      const int w = wv[u];
+      const float a = av[u];
+      unsigned m = __match_any_sync(FULL, w);
+      const bool leader = (__ffs(m) - 1) == lane;
+      const int rounds = __reduce_max_sync(FULL, __popc(m));
+      float sum = 0.f;
+      for (int it = 0; it < rounds; ++it) {
+        const int src = m ? (__ffs(m) - 1) : 0;
+        const float v = __shfl_sync(FULL, a, src);
+        if (m) {
+          sum += v;
+          m &= m - 1;
+        }
+      }
+      if (leader && w >= 0) mybins[w] += sum;
+      __syncwarp();
+    }
   }
   __syncthreads();
   for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
@@ -448,8 +464,14 @@ __device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsign
     float* __restrict__ xx_out = reinterpret_cast<float*>(d.pkt_send) + d.B;
     for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
       float acc = 0.f;
-      if (mu < d.K)
-        for (int c = 0; c < nctas; ++c) acc += __ldcg(d.xx_part + (size_t)c * d.Kp + mu);
+      if (mu < d.K) {
+        float part[8];  // nctas <= 8: fetch all partials, then add them in CTA order
+#pragma unroll
+        for (int c = 0; c < 8; ++c) part[c] = (c < nctas) ? __ldcg(d.xx_part + (size_t)c * d.Kp + mu) : 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c < nctas) acc += part[c];
+      }
       xx_out[mu] = acc;
     }
     if (threadIdx.x == 0) {
@@ -714,18 +736,59 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   const unsigned long long next_step = d.ctl->base + local + 1;
   uint32_t vmax = 0u;
   for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
-    // input ids of the next step: independent of the weights, so they are prepared here
-    if (idx_next) idx_next[e] = input_id(d, next_step, e);
-    const int c = d.cnt[e];
-    if (c <= 0) continue;
-    const int i = idx[e];
-    const int q = e / d.W;
-    const int r = q / d.B, j = q - r * d.B;
-    const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
-    const float v = (float)((double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) * sX[mu]);
-    d.wt[(size_t)i * d.Kp + mu] = v;
-    d.cnt[e] = 0;
-    vmax = max(vmax, __float_as_uint(fabsf(v)));
+    // Two independent chains run through this loop body: the slot (count -> parked weight ->
+    // new weight) and the input id of the next step (order entry -> window start -> token),
+    // which does not depend on the weights.  Their loads are issued pairwise so that the
+    // round trips overlap.
+    const int q = e / d.W, cpos = e - q * d.W;
+    const unsigned long long pos = next_step * (unsigned long long)d.G * d.B + q;
+    const bool want_next = idx_next != nullptr && pos < d.Ns;
+    unsigned long long pw = 0;
+    if (want_next) pw = d.perm[pos];                          // chain B, load 1
+    const int c = d.cnt[e];                                   // chain A, load 1
+    int i = -1, mu = 0;
+    float sv = 0.f;
+    if (c > 0) {
+      i = idx[e];
+      const int r = q / d.B, j = q - r * d.B;
+      mu = (int)d.pkt_recv[(size_t)r * d.P + j];
+      sv = d.saved[e];
+    }
+    unsigned long long ws = 0;
+    bool ok_next = want_next;
+    if (want_next) {
+      if (pw >= d.Ns) {
+        atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
+        ok_next = false;
+      } else {
+        ws = d.wstart[pw];                                    // chain B, load 2
+      }
+    }
+    float fi = 0.f;
+    if (c > 0) fi = __ldg(d.f + (i % d.V));                   // chain A, load 2
+    int val = -2;
+    if (ok_next) {
+      if (ws + d.W > d.ntok) {
+        atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
+      } else {
+        const int tok = d.tokens[ws + cpos];                  // chain B, load 3
+        if (tok < 0) {
+          val = -1;
+        } else if (tok >= d.V) {
+          atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
+          val = -1;
+        } else {
+          val = tok + (cpos == d.W / 2 ? d.V : 0);
+        }
+      }
+    }
+    if (c > 0) {
+      const float v = (float)((double)sv + (double)c * (double)fi * sX[mu]);
+      d.wt[(size_t)i * d.Kp + mu] = v;
+      d.cnt[e] = 0;
+      vmax = max(vmax, __float_as_uint(fabsf(v)));
+    }
+    if (idx_next) idx_next[e] = val;
   }
   // keep the bound on max |wt| valid for the next forward pass
   vmax = warp_max_u32(vmax);
