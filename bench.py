@@ -260,6 +260,7 @@ def bench_train(args):
         "config": {"workload": "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000/GPU lr=2e-4 W0~N(0,1)",
                    "corpus_tokens": int(ntok), "windows": int(ns), "global_batch": world * B,
                    "parallelism": f"dp{world}",
+                   "exchange": {0: "none", 1: "nccl all-gather per step", 2: "peer-memory mailboxes"}[tr.comm_mode],
                    "l2": "inputs larger than L2: corpus + window tables (>0.6 GB) stream through; the 64 MB synapse "
                          "matrix is re-read every step by design"},
         "wall_ms_per_step": wall / steps * 1e3,

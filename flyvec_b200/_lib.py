@@ -87,6 +87,7 @@ _PROTOTYPES = {
                               C.c_int),
     "fv_comm_unique_id": ([_P], C.c_int),
     "fv_trainer_init_comm": ([_P, _P], C.c_int),
+    "fv_trainer_comm_mode": ([_P, C.POINTER(C.c_int)], C.c_int),
     "fv_shard_range": ([C.c_uint64, C.c_uint32, C.c_int32, C.c_int32, C.c_uint64, C.POINTER(C.c_uint64),
                         C.POINTER(C.c_uint64)], C.c_int),
     "fv_hasher_create": ([_P, C.c_uint32, C.c_uint32, C.c_int, C.c_float, C.c_int, C.POINTER(_P)], C.c_int),

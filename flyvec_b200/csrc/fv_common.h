@@ -47,3 +47,4 @@ struct DeviceGuard {
 #define FV_DEVERR_WINDOW_RANGE 2u // a window start or permutation entry was out of range
 #define FV_DEVERR_SLOT_RANGE 4u   // a scatter slot id did not fit its tag
 #define FV_DEVERR_NAN_WEIGHT 8u   // a NaN was found where a weight was expected
+#define FV_DEVERR_TIMEOUT 16u     // a bounded wait on a peer's flag ran out

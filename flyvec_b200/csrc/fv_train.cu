@@ -17,7 +17,7 @@
 //                T6-8 gather-sum, arg-max, weighted winner    (cuda_funcs.cu:248-305, 488-561)
 //                T8   xx[mu] = sum of weighted winning activations, in a fixed order
 //                     (cuda_funcs.cu:722-744)
-//   (k_build_idx      only when world > 1: ids of the other ranks' windows)
+//   (k_build_idx_block, on a side stream: ids of the next 32 steps, all ranks' windows)
 //   all-gather        winners + xx of every rank (NCCL)
 //   k_tag        T10  each touched (mu,i) gets one owner slot; its weight is parked in
 //                     `saved` and replaced by a tagged NaN     (cuda_funcs.cu:657-672)
@@ -52,11 +52,16 @@ struct StepCtl {
   uint32_t wabsmax_fold;  // the same, collected while folding
   uint32_t xx_ticket;     // CTAs of the running k_xx that have finished
   uint32_t fwd_next;      // next window index k_forward hands out beyond the first round
+  uint32_t scan_ticket;   // CTAs of the running k_scan that have finished
+  uint32_t apply_ticket;  // CTAs of the running k_apply that have finished their own slots
+  uint32_t out_count;     // entries in this step's outbox (sharded update)
+  uint32_t pad;
+  unsigned long long stamp[8];  // %globaltimer at phase boundaries of the last step (diagnostics)
 };
 
 // Everything a kernel needs, passed by value.
 struct Dev {
-  int K, Kp, Kq, V, N, W, B, G, rank, P;
+  int K, Kp, Kq, V, N, W, B, G, rank, P, XO;  // P = packet words, XO = offset of xx inside a packet
   unsigned long long Ns, ntok;
   float prec;
   uint32_t flags;
@@ -66,8 +71,11 @@ struct Dev {
   const unsigned long long* wstart;
   const unsigned long long* perm;
   const float* f;
-  uint32_t* pkt_send;
-  uint32_t* pkt_recv;
+  uint32_t* mail;          // this rank's mailbox: MAIL_HDR words of flags, then packets [2][G][P]
+  uint32_t* const* peers;  // device table of all ranks' mailboxes (peer-mapped), or null
+  unsigned spin_limit;     // polls before a wait on a peer's flag gives up
+  int shard;               // 1: rows i with i % G == rank are updated here, the rest arrives from their owners
+  size_t outbox_off;       // word offset of the outbox [2][G*B*W] of (position, value) pairs inside the mailbox
   float* aw;       // [B] weighted activation of each window's winner
   float* xx_part;  // [k_xx CTAs][Kp] partial sums of xx
   int32_t* cnt;
@@ -78,6 +86,81 @@ struct Dev {
   float* nc_log;
   float* s_log;
 };
+
+// Mailbox header (words).  Everything is indexed [parity][sender]; a flag holds the sequence number
+// (tick + local + 1) of the step whose data is complete.
+constexpr int MAX_RANKS = 16;
+constexpr int FLAG_PKT = 0;                    // packets (winners + xx) delivered
+// The partial normaliser and the outbox count travel inside their flag: one 64-bit word
+// (sequence number in the high half, payload in the low half) written with a single store.
+constexpr int WORD_NC = 2 * MAX_RANKS;         // u64 [2][MAX_RANKS]: seq | float bits of sender's partial nc
+constexpr int WORD_OUT = 6 * MAX_RANKS;        // u64 [2][MAX_RANKS]: seq | entries in sender's outbox
+constexpr int MAIL_HDR = 10 * MAX_RANKS + 96;  // 256 words, keeps the packets 1 KiB aligned
+// Packet of rank r for the step of the given parity: B winners, then (at XO) Kp floats of xx.
+__device__ __forceinline__ uint32_t* packet(const Dev& d, int parity, int r) {
+  return d.mail + MAIL_HDR + ((size_t)parity * d.G + r) * d.P;
+}
+
+__device__ __forceinline__ uint2* outbox(const Dev& d, const uint32_t* mail, int parity) {
+  return reinterpret_cast<uint2*>(const_cast<uint32_t*>(mail) + d.outbox_off) + (size_t)parity * d.G * d.B * d.W;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Message passing between GPUs.  Producer: payload stores, ONE system-scope fence by one thread,
+// then relaxed flag stores.  Consumer: relaxed polls of the flag (they are served by the local L2,
+// where a peer's store over NVLink lands), one acquire load once the flag matches.
+__device__ __forceinline__ void store_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void store_relaxed_sys64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t load_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long load_relaxed_sys64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_expired(const Dev& d, unsigned& polls) {
+  if (++polls > d.spin_limit || (*reinterpret_cast<volatile uint32_t*>(&d.ctl->error) & FV_DEVERR_TIMEOUT)) {
+    atomicOr(&d.ctl->error, FV_DEVERR_TIMEOUT);
+    return true;
+  }
+  if (polls > 64) __nanosleep(128);
+  return false;
+}
+// Bounded wait until flag == seq.  Returns false (and raises FV_DEVERR_TIMEOUT) when the limit
+// is reached or another wait already failed; no wait in this library spins without a limit.
+__device__ __forceinline__ bool wait_flag(const Dev& d, const uint32_t* flag, uint32_t seq) {
+  unsigned polls = 0;
+  while (load_relaxed_sys(flag) != seq)
+    if (wait_expired(d, polls)) return false;
+  return load_acquire_sys(flag) == seq;
+}
+// Bounded wait for a {seq, payload} word; the payload needs no further ordering.
+__device__ __forceinline__ bool wait_word(const Dev& d, const unsigned long long* word, uint32_t seq, uint32_t* payload) {
+  unsigned polls = 0;
+  for (;;) {
+    const unsigned long long v = load_relaxed_sys64(word);
+    if ((uint32_t)(v >> 32) == seq) {
+      *payload = (uint32_t)v;
+      return true;
+    }
+    if (wait_expired(d, polls)) return false;
+  }
+}
 
 // Programmatic dependent launch: a kernel launched with the stream-serialization
 // attribute may start while its predecessor in the stream is still draining; it must
@@ -141,12 +224,17 @@ __device__ __forceinline__ int input_id(const Dev& d, unsigned long long step, i
   }
   return val;
 }
-__global__ void k_build_idx(Dev d, int local, int32_t* __restrict__ idx) {
-  grid_dependency_wait();
-  const unsigned long long step = d.ctl->base + local;
-  const int total = d.G * d.B * d.W;
-  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x)
-    idx[e] = input_id(d, step, e);
+// Ids of `nsteps` consecutive global steps starting at `step0`, written back to back.  Runs on a
+// side stream a block of steps ahead of the step loop: the ids depend on the corpus and the window
+// order only, so the three dependent loads per id stay off the step's critical path.
+__global__ void __launch_bounds__(256) k_build_idx_block(Dev d, unsigned long long step0, int nsteps,
+                                                         int32_t* __restrict__ out) {
+  const size_t per_step = (size_t)d.G * d.B * d.W;
+  const size_t total = per_step * nsteps;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t s = t / per_step;
+    out[t] = input_id(d, step0 + s, (int)(t - s * per_step));
+  }
 }
 
 // Checks host-supplied input ids (streaming mode) against [ -2, N ).
@@ -275,6 +363,7 @@ __device__ __forceinline__ float weighted_activation(const Dev& d, const double*
 template <int NT>
 __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const int32_t* __restrict__ idx) {
   grid_dependency_wait();
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char fwd_smem[];
   float* s_alpha = reinterpret_cast<float*>(fwd_smem);  // [Kp] the units' scales as floats
 
@@ -298,7 +387,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   const float theta = 4.0f * (float)(d.W * d.W + 2 * d.W + 4) * 5.9604645e-8f * amax * __uint_as_float(d.ctl->wabsmax);
   const bool force64 = (d.flags & FV_FLAG_ACC_FP64) != 0;
 
-  int32_t* __restrict__ win_out = reinterpret_cast<int32_t*>(d.pkt_send);
+  int32_t* __restrict__ win_out = reinterpret_cast<int32_t*>(packet(d, (int)((d.ctl->tick + local) & 1), d.rank));
   const int zrow = d.N;  // the all-zero row
   const int nbatch = (d.W + 3) >> 2;
   int qc[NT];
@@ -309,10 +398,14 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
     qc[t] = min(lane + 32 * t, Kq - 1);
   }
 
+  int jlast = j;  // last window of the block this warp currently owns
   while (j < d.B) {
-    // ask for the next window now; its ids are fetched while this one is summed
-    int jn = 0;
-    if (lane == 0) jn = nwarps + (int)atomicAdd(&d.ctl->fwd_next, 1u);
+    // decide on the next window now; its ids are fetched while this one is summed.  Windows
+    // beyond the first round are handed out in pairs: same-address atomics complete at about
+    // one per nanosecond, so one ticket per window would cost as much as the gather itself.
+    int jn = j + 1;
+    const bool need_ticket = (j >= jlast);
+    if (need_ticket && lane == 0) jn = nwarps + 2 * (int)atomicAdd(&d.ctl->fwd_next, 1u);
     int winner = -1;
     float awv = 0.f;
     int n_my = -1;
@@ -335,6 +428,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
           for (int t = 0; t < NT; ++t) v[u][t] = __ldg(r[u] + qc[t]);
         if (b == 0) {
           jn = __shfl_sync(FULL, jn, 0);
+          if (need_ticket) jlast = jn + 1;
           if (jn < d.B && lane < d.W) n_my = idx_own[(size_t)jn * d.W + lane];
         }
 #pragma unroll
@@ -382,6 +476,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
       awv = weighted_activation(d, alpha, my, winner, lane);
     } else {
       jn = __shfl_sync(FULL, jn, 0);
+      if (need_ticket) jlast = jn + 1;
       if (jn < d.B && lane < d.W) n_my = idx_own[(size_t)jn * d.W + lane];
     }
     if (lane == 0) {
@@ -405,11 +500,13 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
 // ---------------------------------------------------------------------------
 constexpr int XX_THREADS = 512;
 constexpr int XX_WARPS = XX_THREADS / 32;
-__device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsigned char* xx_smem) {
+__device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nctas, unsigned char* xx_smem) {
   float* bins = reinterpret_cast<float*>(xx_smem);  // [XX_WARPS][Kp]
   __shared__ unsigned s_ticket;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
-  const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(d.pkt_send);
+  const int parity = (int)((d.ctl->tick + local) & 1);
+  uint32_t* __restrict__ mine = packet(d, parity, d.rank);
+  const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(mine);
   for (int i = threadIdx.x; i < XX_WARPS * d.Kp; i += XX_THREADS) bins[i] = 0.f;
   __syncthreads();
   const int per_cta = (d.B + nctas - 1) / nctas;
@@ -461,7 +558,7 @@ __device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsign
   __syncthreads();
   if (s_ticket == (unsigned)nctas - 1) {
     __threadfence();
-    float* __restrict__ xx_out = reinterpret_cast<float*>(d.pkt_send) + d.B;
+    float* __restrict__ xx_out = reinterpret_cast<float*>(mine) + d.XO;
     for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
       float acc = 0.f;
       if (mu < d.K) {
@@ -478,12 +575,32 @@ __device__ __forceinline__ void xx_body(const Dev& d, int cta, int nctas, unsign
       d.ctl->xx_ticket = 0u;
       d.ctl->fwd_next = 0u;
     }
+    if (d.peers != nullptr && d.G > 1) {
+      // Exchange fused into the producer: push the finished packet (winners + xx) into every
+      // peer's mailbox over NVLink with plain stores, make the stores visible system-wide, then
+      // publish the step's sequence number in the peer's flag word.  The peers' k_tag polls it.
+      __syncthreads();
+      const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
+      const uint4* __restrict__ src4 = reinterpret_cast<const uint4*>(mine);
+      const int n4 = d.P >> 2;
+      for (int r = 0; r < d.G; ++r) {
+        if (r == d.rank) continue;
+        uint4* dst4 = reinterpret_cast<uint4*>(d.peers[r] + MAIL_HDR + ((size_t)parity * d.G + d.rank) * d.P);
+        for (int i = threadIdx.x; i < n4; i += XX_THREADS) dst4[i] = __ldcg(src4 + i);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < d.G && (int)threadIdx.x != d.rank)
+        store_relaxed_sys(d.peers[threadIdx.x] + FLAG_PKT + parity * MAX_RANKS + d.rank, seq);
+    }
   }
 }
-__global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d) {
+__global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
   grid_dependency_wait();
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char xx_smem[];
-  xx_body(d, blockIdx.x, gridDim.x, xx_smem);
+  xx_body(d, local, blockIdx.x, gridDim.x, xx_smem);
 }
 
 // ---------------------------------------------------------------------------
@@ -499,12 +616,25 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d) {
 // side with the tagging; tagging then cannot ask whether the rank was active for a
 // unit and tags every slot -- a unit that turns out inactive simply gets its parked
 // weights back unchanged in k_apply.
-__global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, const int32_t* __restrict__ idx, int xx_ctas) {
+__global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas) {
   grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char tag_smem[];
   if ((int)blockIdx.x < xx_ctas) {
-    xx_body(d, blockIdx.x, xx_ctas, tag_smem);
+    xx_body(d, local, blockIdx.x, xx_ctas, tag_smem);
     return;
+  }
+  const int parity = (int)((d.ctl->tick + local) & 1);
+  if (d.peers != nullptr && d.G > 1) {
+    // wait (bounded) until every peer has published this step's packet in our mailbox
+    __shared__ int s_fail;
+    if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
+      const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
+      if (!wait_flag(d, d.mail + FLAG_PKT + parity * MAX_RANKS + threadIdx.x, seq)) s_fail = 1;
+    }
+    __syncthreads();
+    if (s_fail) return;
   }
   const int E = d.G * d.B * d.W;
   const bool check_active = (xx_ctas == 0);
@@ -512,12 +642,13 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, const int32_t* __rest
   for (int e = (blockIdx.x - xx_ctas) * blockDim.x + threadIdx.x; e < E; e += nthreads) {
     const int i = idx[e];
     if (i < 0) continue;
+    if (d.shard && (i % d.G) != d.rank) continue;  // another rank owns this row
     const int q = e / d.W;
     const int r = q / d.B, j = q - r * d.B;
-    const uint32_t* __restrict__ pkt = d.pkt_recv + (size_t)r * d.P;
+    const uint32_t* __restrict__ pkt = packet(d, parity, r);
     const int mu = (int)pkt[j];
     if (mu < 0) continue;
-    if (check_active && __uint_as_float(pkt[d.B + mu]) == 0.f) continue;
+    if (check_active && __uint_as_float(pkt[d.XO + mu]) == 0.f) continue;
     uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt + (size_t)i * d.Kp + mu);
     uint32_t cur = __ldcg(addr);
     const uint32_t tag = TAG_BASE | (uint32_t)(e + 1);
@@ -545,11 +676,11 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, const int32_t* __rest
 // Per-unit combine over ranks: n = number of ranks with xx != 0, X = mean of xx
 // over those ranks (the closed form of cu_special_reduction.cu:42-67 applied to
 // the -xx*W term).
-__device__ __forceinline__ void unit_stats(const Dev& d, int mu, double* X, int* n) {
+__device__ __forceinline__ void unit_stats(const Dev& d, int parity, int mu, double* X, int* n) {
   double sum = 0.0;
   int cnt = 0;
   for (int r = 0; r < d.G; ++r) {
-    const float x = __uint_as_float(d.pkt_recv[(size_t)r * d.P + d.B + mu]);
+    const float x = __uint_as_float(packet(d, parity, r)[d.XO + mu]);
     if (x != 0.f) {
       sum += (double)x;
       ++cnt;
@@ -576,6 +707,7 @@ constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_UNROLL = 8;
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, const int32_t* __restrict__ idx) {
   grid_dependency_wait();
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
   int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
@@ -586,7 +718,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
-    if (mu < d.K) unit_stats(d, mu, &X, &n);
+    if (mu < d.K) unit_stats(d, p, mu, &X, &n);
     sC[mu] = X * alpha[mu];
     sN[mu] = n;
     sMax[mu] = 0u;
@@ -616,20 +748,23 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
       u = v.w & ABS_MASK; m3 = max(m3, u > TAG_BASE ? 0u : u);
     };
     const uint4* __restrict__ base = reinterpret_cast<const uint4*>(d.wt) + q;
+    // sharded: only the rows this rank owns (rank, rank + G, ...), i.e. row = rank + G * k
+    const int rmul = d.shard ? d.G : 1, radd = d.shard ? d.rank : 0;
+    const int nrows = d.shard ? (d.N - d.rank + d.G - 1) / d.G : d.N;
     int row = blockIdx.x * groups + g;
-    for (; row + (SCAN_UNROLL - 1) * stride < d.N; row += SCAN_UNROLL * stride) {
+    for (; row + (SCAN_UNROLL - 1) * stride < nrows; row += SCAN_UNROLL * stride) {
       uint4 v[SCAN_UNROLL];
 #pragma unroll
-      for (int u = 0; u < SCAN_UNROLL; ++u) v[u] = __ldcg(base + (size_t)(row + u * stride) * Kq);
+      for (int u = 0; u < SCAN_UNROLL; ++u) v[u] = __ldcg(base + (size_t)(radd + rmul * (row + u * stride)) * Kq);
 #pragma unroll
       for (int u = 0; u < SCAN_UNROLL; ++u) fold_in(v[u]);
     }
-    if (row < d.N) {  // ragged end: same unrolled batch, rows past the end re-read the first one
+    if (row < nrows) {  // ragged end: same unrolled batch, rows past the end re-read the first one
       uint4 v[SCAN_UNROLL];
 #pragma unroll
       for (int u = 0; u < SCAN_UNROLL; ++u) {
         const int rr = row + u * stride;
-        v[u] = __ldcg(base + (size_t)(rr < d.N ? rr : row) * Kq);
+        v[u] = __ldcg(base + (size_t)(radd + rmul * (rr < nrows ? rr : row)) * Kq);
       }
 #pragma unroll
       for (int u = 0; u < SCAN_UNROLL; ++u) fold_in(v[u]);
@@ -647,7 +782,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     const int i = idx[e];
     const int qq = e / d.W;
     const int r = qq / d.B, j = qq - r * d.B;
-    const int mu = (int)d.pkt_recv[(size_t)r * d.P + j];
+    const int mu = (int)packet(d, p, r)[j];
     if (sN[mu] == 0) return;  // tagged before the unit proved inactive: no update there
     const double D = -sC[mu] * (double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) / (double)sN[mu];
     tmax = max(tmax, __float_as_uint(fabsf((float)D)));
@@ -655,13 +790,47 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   touched(e0, c0);
   touched(e1, c1);
   for (int e = e1 + nthreads; e < E; e += nthreads) touched(e, d.cnt[e]);
-  tmax = warp_max_u32(tmax);
-  if (lane == 0 && tmax) atomicMax(&d.ncb[p], tmax);
-
+  __shared__ uint32_t s_tmax;
+  if (threadIdx.x == 0) s_tmax = 0u;
   __syncthreads();
+  tmax = warp_max_u32(tmax);
+  if (lane == 0 && tmax) atomicMax(&s_tmax, tmax);
+  __syncthreads();
+  if (threadIdx.x == 0 && s_tmax) atomicMax(&d.ncb[p], s_tmax);  // one global atomic per CTA
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     const uint32_t v = sMax[mu];
     if (v && v > __ldcg(&d.colmax[p * d.Kp + mu])) atomicMax(&d.colmax[p * d.Kp + mu], v);
+  }
+  if (!d.shard) return;
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->stamp[6] = global_timer();
+
+  // Sharded update: the CTA that finishes last turns this rank's maxima into its partial
+  // normaliser and pushes it, with a flag, into every rank's mailbox (its own included).
+  __shared__ unsigned s_last;
+  __shared__ float s_red[SCAN_THREADS / 32];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&d.ctl->scan_ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float dense = 0.f;
+  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x)
+    if (sN[mu] > 0) dense = fmaxf(dense, (float)(fabs(sC[mu]) * (double)__uint_as_float(__ldcg(&d.colmax[p * d.Kp + mu]))));
+  dense = warp_max(dense);
+  if (lane == 0) s_red[threadIdx.x >> 5] = dense;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float nc = __uint_as_float(__ldcg(&d.ncb[p]));
+    for (int w = 0; w < SCAN_THREADS / 32; ++w) nc = fmaxf(nc, s_red[w]);
+    s_red[0] = nc;
+    d.ctl->scan_ticket = 0u;
+  }
+  __syncthreads();
+  if (threadIdx.x < d.G) {
+    const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
+    unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
+    store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_red[0]));
   }
 }
 
@@ -672,9 +841,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 // and clear their count.  CTA 0 publishes alpha' and the step's nc and s, and
 // clears the maxima the next step will accumulate into.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx,
-                                               int32_t* __restrict__ idx_next) {
+__global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx) {
   grid_dependency_wait();
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sX = reinterpret_cast<double*>(smem_raw);  // mean xx over active ranks, later s / (n * alpha')
   int* sN = reinterpret_cast<int*>(sX + d.Kp);
@@ -688,7 +857,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
-    if (mu < d.K) unit_stats(d, mu, &X, &n);
+    if (mu < d.K) unit_stats(d, p, mu, &X, &n);
     sX[mu] = X;
     sN[mu] = n;
     if (n > 0) dense = fmaxf(dense, (float)(fabs(X * alpha[mu]) * (double)__uint_as_float(d.colmax[p * d.Kp + mu])));
@@ -696,9 +865,29 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   dense = warp_max(dense);
   if ((threadIdx.x & 31) == 0) sRed[threadIdx.x >> 5] = dense;
   __syncthreads();
+  __shared__ int sFail;
+  if (threadIdx.x == 0) sFail = 0;
+  const bool stamper = blockIdx.x == 0 && threadIdx.x == 0;
+  if (stamper) d.ctl->stamp[0] = global_timer();
+  __syncthreads();
+  const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
+  __shared__ uint32_t sWord[MAX_RANKS];
+  if (d.shard && threadIdx.x < d.G) {
+    // every rank's partial normaliser (pushed by its k_scan) must have arrived, ours included
+    const unsigned long long* words = reinterpret_cast<const unsigned long long*>(d.mail + WORD_NC);
+    if (!wait_word(d, words + p * MAX_RANKS + threadIdx.x, seq, &sWord[threadIdx.x])) sFail = 1;
+  }
+  __syncthreads();
+  if (sFail) return;
+  if (stamper) d.ctl->stamp[1] = global_timer();
   if (threadIdx.x == 0) {
-    float nc = __uint_as_float(d.ncb[p]);
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) nc = fmaxf(nc, sRed[w]);
+    float nc = 0.f;
+    if (d.shard) {
+      for (int r = 0; r < d.G; ++r) nc = fmaxf(nc, __uint_as_float(sWord[r]));
+    } else {
+      nc = __uint_as_float(d.ncb[p]);
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) nc = fmaxf(nc, sRed[w]);
+    }
     const float eps = d.ctl->eps;
     const float s = (d.prec > nc) ? eps / d.prec : eps / nc;  // cuda_funcs.cu:1797-1799
     sScale = s;
@@ -733,62 +922,111 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   __syncthreads();
 
   const int E = d.G * d.B * d.W;
-  const unsigned long long next_step = d.ctl->base + local + 1;
+  uint2* __restrict__ my_out = outbox(d, d.mail, p);
   uint32_t vmax = 0u;
-  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
-    // Two independent chains run through this loop body: the slot (count -> parked weight ->
-    // new weight) and the input id of the next step (order entry -> window start -> token),
-    // which does not depend on the weights.  Their loads are issued pairwise so that the
-    // round trips overlap.
-    const int q = e / d.W, cpos = e - q * d.W;
-    const unsigned long long pos = next_step * (unsigned long long)d.G * d.B + q;
-    const bool want_next = idx_next != nullptr && pos < d.Ns;
-    unsigned long long pw = 0;
-    if (want_next) pw = d.perm[pos];                          // chain B, load 1
-    const int c = d.cnt[e];                                   // chain A, load 1
+  __shared__ unsigned s_wcount[8], s_base;
+  for (int e0 = blockIdx.x * blockDim.x; e0 < E; e0 += gridDim.x * blockDim.x) {
+    const int e = min(e0 + (int)threadIdx.x, E - 1);
+    const bool in_range = e0 + (int)threadIdx.x < E;
+    // the slot chain: count -> (id, winner, parked weight) -> 1/count of the token -> new weight
+    const int q = e / d.W;
+    const int c = in_range ? d.cnt[e] : 0;
     int i = -1, mu = 0;
-    float sv = 0.f;
+    float sv = 0.f, fi = 0.f;
     if (c > 0) {
       i = idx[e];
       const int r = q / d.B, j = q - r * d.B;
-      mu = (int)d.pkt_recv[(size_t)r * d.P + j];
+      mu = (int)packet(d, p, r)[j];
       sv = d.saved[e];
+      fi = __ldg(d.f + (i % d.V));
     }
-    unsigned long long ws = 0;
-    bool ok_next = want_next;
-    if (want_next) {
-      if (pw >= d.Ns) {
-        atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
-        ok_next = false;
-      } else {
-        ws = d.wstart[pw];                                    // chain B, load 2
-      }
-    }
-    float fi = 0.f;
-    if (c > 0) fi = __ldg(d.f + (i % d.V));                   // chain A, load 2
-    int val = -2;
-    if (ok_next) {
-      if (ws + d.W > d.ntok) {
-        atomicOr(&d.ctl->error, FV_DEVERR_WINDOW_RANGE);
-      } else {
-        const int tok = d.tokens[ws + cpos];                  // chain B, load 3
-        if (tok < 0) {
-          val = -1;
-        } else if (tok >= d.V) {
-          atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
-          val = -1;
-        } else {
-          val = tok + (cpos == d.W / 2 ? d.V : 0);
-        }
-      }
-    }
+    float v = 0.f;
     if (c > 0) {
-      const float v = (float)((double)sv + (double)c * (double)fi * sX[mu]);
+      v = (float)((double)sv + (double)c * (double)fi * sX[mu]);
       d.wt[(size_t)i * d.Kp + mu] = v;
       d.cnt[e] = 0;
       vmax = max(vmax, __float_as_uint(fabsf(v)));
     }
-    if (idx_next) idx_next[e] = val;
+    if (d.shard) {
+      // the other replicas need this value too: append (position, value) to this step's outbox;
+      // slots are handed out per CTA and loop round (one global atomic), then per warp, then per lane
+      const unsigned owners = __ballot_sync(FULL, c > 0);
+      const int wic = threadIdx.x >> 5, ln = threadIdx.x & 31;
+      if (ln == 0) s_wcount[wic] = (unsigned)__popc(owners);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        unsigned tot = 0;
+        for (int w = 0; w < 8; ++w) {
+          const unsigned cw = s_wcount[w];
+          s_wcount[w] = tot;
+          tot += cw;
+        }
+        s_base = tot ? atomicAdd(&d.ctl->out_count, tot) : 0u;
+      }
+      __syncthreads();
+      if (c > 0) {
+        const unsigned slot = s_base + s_wcount[wic] + __popc(owners & ((1u << ln) - 1u));
+        my_out[slot] = make_uint2((unsigned)((size_t)i * d.Kp + mu), __float_as_uint(v));
+      }
+      __syncthreads();
+    }
+  }
+  if (d.shard) {
+    // publish: when every CTA has written its entries, the last one tells the peers how many there are
+    __shared__ unsigned s_last;
+    if (stamper) d.ctl->stamp[2] = global_timer();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // device-scope fence per CTA (covers the CTA's entries, ordered before it by the barrier); the one
+      // system-scope fence is issued by the CTA that publishes.  A system fence from every CTA costs
+      // several microseconds when hundreds of them do it at once.
+      __threadfence();
+      s_last = (atomicAdd(&d.ctl->apply_ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last) {
+      if (threadIdx.x == 0) __threadfence_system();
+      __syncthreads();
+      const unsigned count = *reinterpret_cast<volatile unsigned*>(&d.ctl->out_count);
+      if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
+        // thread 0's system fence above (before the ticket) ordered this CTA's entries; the other
+        // CTAs did the same before their tickets, which this CTA has observed
+        unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
+        store_relaxed_sys64(words + p * MAX_RANKS + d.rank, ((unsigned long long)seq << 32) | count);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        d.ctl->apply_ticket = 0u;
+        d.ctl->out_count = 0u;
+      }
+    }
+    // pull: the rows owned elsewhere take the values their owners computed.  All CTAs of this
+    // grid are resident (the launch is sized for that), so waiting here cannot starve the
+    // CTAs that still have to publish.
+    if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
+      const unsigned long long* words = reinterpret_cast<const unsigned long long*>(d.mail + WORD_OUT);
+      if (!wait_word(d, words + p * MAX_RANKS + threadIdx.x, seq, &sWord[threadIdx.x])) sFail = 1;
+      (void)load_acquire_sys(d.mail + WORD_OUT + 2 * (p * MAX_RANKS + threadIdx.x));  // order the list reads after it
+    }
+    __syncthreads();
+    if (sFail) return;
+    if (stamper) d.ctl->stamp[3] = global_timer();
+    const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gthreads = gridDim.x * blockDim.x;
+    for (int r = 0; r < d.G; ++r) {
+      if (r == d.rank) continue;
+      const unsigned n_r = sWord[r];
+      const uint2* __restrict__ theirs = outbox(d, d.peers[r], p);
+      for (unsigned k = gtid; k < n_r; k += gthreads) {
+        const uint2 pv = __ldcg(theirs + k);
+        if (pv.x < (unsigned)((size_t)d.N * d.Kp)) {
+          reinterpret_cast<uint32_t*>(d.wt)[pv.x] = pv.y;
+          vmax = max(vmax, pv.y & ABS_MASK);
+        } else {
+          atomicOr(&d.ctl->error, FV_DEVERR_SLOT_RANGE);
+        }
+      }
+    }
+    if (stamper) d.ctl->stamp[4] = global_timer();
   }
   // keep the bound on max |wt| valid for the next forward pass
   vmax = warp_max_u32(vmax);
@@ -971,9 +1209,12 @@ struct fv_trainer {
   unsigned long long* d_wstart = nullptr;
   unsigned long long* d_perm = nullptr;
   float* d_f = nullptr;
-  int32_t* d_idx = nullptr;
   int32_t* d_idx_stage[2] = {nullptr, nullptr};
-  uint32_t* d_pkt = nullptr;
+  uint32_t* d_mail = nullptr;               // local mailbox (flags + packets)
+  size_t mail_words = 0;
+  uint32_t* peer_mail[16] = {nullptr};      // peers' mailboxes mapped into this process
+  uint32_t** d_peer_table = nullptr;
+  int comm_mode = 0;                         // 0 none, 1 NCCL all-gather per step, 2 peer-memory mailboxes
   float* d_xx_part = nullptr;
   float* d_aw = nullptr;
   int32_t* d_cnt = nullptr;
@@ -1063,45 +1304,47 @@ int fold_weights(fv_trainer* tr, int local) {
   return FV_OK;
 }
 
-// One global step on tr->stream.  `idx` holds this step's input ids (all ranks'
-// windows); when idx_next is given, the step also prepares the next step's ids there.
+// One global step on tr->stream.  `idx` holds this step's input ids (all ranks' windows).
 // Adds the kernels launched to *launches.
-int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, int32_t* idx_next, cudaEvent_t* marks,
-                 uint64_t* launches) {
+int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, cudaEvent_t* marks, uint64_t* launches) {
   const Dev& d = tr->d;
   const bool emulate = (d.flags & FV_FLAG_EMULATE_RANKS) != 0;
   const bool single = (d.G == 1);
   if (marks) FV_CUDA(cudaEventRecord(marks[0], tr->stream));
   if (emulate && !single) {
     // every rank's block in turn, each into its own packet slot
-    const Dev own = tr->d;
-    for (int r = 0; r < own.G; ++r) {
+    const int own_rank = tr->d.rank;
+    for (int r = 0; r < d.G; ++r) {
       tr->d.rank = r;
-      tr->d.pkt_send = own.pkt_recv + (size_t)r * own.P;
       FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
-      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, tr->d);
+      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, tr->d, local);
       *launches += 2;
     }
-    tr->d = own;
+    tr->d.rank = own_rank;
     if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
   } else {
     FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
     *launches += 1;
     if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
     if (!single) {
-      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d);
+      // k_xx finishes the packet; with mailboxes its last CTA also pushes it to the peers
+      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local);
       *launches += 1;
-      const int rc = g_nccl.AllGather(d.pkt_send, d.pkt_recv, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
-      if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+      if (tr->comm_mode == 1) {
+        const int parity = (int)((tr->ticks + (unsigned long long)local) & 1);
+        uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P;
+        const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P, base, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
+        if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+      }
     }
   }
   if (marks) FV_CUDA(cudaEventRecord(marks[2], tr->stream));
   if (single)  // xx is computed by the first CTAs of the tagging kernel
-    launch_pdl(k_tag, tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, idx, tr->xx_grid);
+    launch_pdl(k_tag, tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local, idx, tr->xx_grid);
   else
-    launch_pdl(k_tag, tr->tag_grid, XX_THREADS, (size_t)0, tr->stream, d, idx, 0);
+    launch_pdl(k_tag, tr->tag_grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, 0);
   launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
-  launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx, idx_next);
+  launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
   if (marks) FV_CUDA(cudaEventRecord(marks[3], tr->stream));
   FV_CUDA(cudaGetLastError());
   *launches += 3;
@@ -1137,7 +1380,7 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   FV_REQUIRE(tr->have_weights, FV_ERR_STATE, "trainer has no weights: call fv_trainer_set_weights first");
   if (!idx_host) FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus: call fv_trainer_set_corpus first");
   if (tr->d.G > 1 && !(tr->d.flags & FV_FLAG_EMULATE_RANKS))
-    FV_REQUIRE(tr->comm != nullptr, FV_ERR_STATE, "world > 1 but fv_trainer_init_comm was not called");
+    FV_REQUIRE(tr->comm_mode != 0, FV_ERR_STATE, "world > 1 but fv_trainer_init_comm was not called");
   if (stats) memset(stats, 0, sizeof(*stats));
   if (nsteps == 0) return FV_OK;
   FV_REQUIRE(nsteps <= (1ull << 30), FV_ERR_INVALID, "too many steps in one call");
@@ -1154,41 +1397,40 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
     FV_CUDA(cudaEventCreate(&e));
     tr->phase_events.push_back(e);
   }
-  if (idx_host) {
-    for (int b = 0; b < 2; ++b)
-      if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
-  }
+  for (int b = 0; b < 2; ++b)
+    if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
 
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps);
   uint64_t launches = 1;
-  if (!idx_host) {  // ids of the first step; every later step's are prepared by the step before
-    k_build_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, 0, tr->d_idx + (tr->ticks & 1) * step_ids);
-    launches += 1;
-  }
   FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   unsigned long long chunk_id = 0;
   for (unsigned long long k = 0; k < nsteps; ++k) {
-    const int32_t* idx = tr->d_idx + ((tr->ticks + k) & 1) * step_ids;
-    int32_t* idx_next = tr->d_idx + ((tr->ticks + k + 1) & 1) * step_ids;
-    if (idx_host) {
-      const int b = (int)(chunk_id & 1);
-      if (k % STAGE_STEPS == 0) {
-        const unsigned long long n = (nsteps - k < STAGE_STEPS) ? nsteps - k : STAGE_STEPS;
-        // the buffer must no longer be read by the chunk that used it two chunks ago
-        if (chunk_id >= 2) FV_CUDA(cudaStreamWaitEvent(tr->copy_stream, tr->ev_used[b], 0));
+    // Input ids arrive in chunks of STAGE_STEPS steps through two device buffers filled on a second
+    // stream, one chunk ahead of the step loop: uploaded from the caller's host memory, or derived
+    // from the resident corpus and window order.
+    const int b = (int)(chunk_id & 1);
+    if (k % STAGE_STEPS == 0) {
+      const unsigned long long n = (nsteps - k < STAGE_STEPS) ? nsteps - k : STAGE_STEPS;
+      // the buffer must no longer be read by the chunk that used it two chunks ago
+      if (chunk_id >= 2) FV_CUDA(cudaStreamWaitEvent(tr->copy_stream, tr->ev_used[b], 0));
+      if (idx_host) {
         FV_CUDA(cudaMemcpyAsync(tr->d_idx_stage[b], idx_host + k * step_ids, n * step_ids * sizeof(int32_t),
                                 cudaMemcpyHostToDevice, tr->copy_stream));
-        FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
-        FV_CUDA(cudaStreamWaitEvent(tr->stream, tr->ev_copy[b], 0));
+      } else {
+        k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->copy_stream>>>(d, first_step + k, (int)n, tr->d_idx_stage[b]);
+        launches += 1;
+      }
+      FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
+      FV_CUDA(cudaStreamWaitEvent(tr->stream, tr->ev_copy[b], 0));
+      if (idx_host) {
         k_check_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, tr->d_idx_stage[b], n * step_ids);
         launches += 1;
       }
-      idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * step_ids;
-      idx_next = nullptr;
     }
+    const int32_t* idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * step_ids;
     cudaEvent_t* marks = (k % PHASE_SAMPLE == 0) ? &tr->phase_events[(k / PHASE_SAMPLE) * 4] : nullptr;
-    FV_TRY(enqueue_step(tr, (int)k, idx, idx_next, marks, &launches));
-    if (idx_host && ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps)) {
+    FV_TRY(enqueue_step(tr, (int)k, idx, marks, &launches));
+    if ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps) {
       FV_CUDA(cudaEventRecord(tr->ev_used[chunk_id & 1], tr->stream));
       ++chunk_id;
     }
@@ -1211,6 +1453,13 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
 
   uint32_t dev_err = 0;
   FV_TRY(read_device_error(tr, &dev_err));
+  if (getenv("FV_STAMPS")) {
+    StepCtl h;
+    FV_CUDA(cudaMemcpy(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost));
+    fprintf(stderr, "[rank %d] apply: start->nc %.1f us, own slots %.1f us, ->lists %.1f us, merge %.1f us; scan end->apply start %.1f us\n",
+            tr->d.rank, (h.stamp[1] - h.stamp[0]) * 1e-3, (h.stamp[2] - h.stamp[1]) * 1e-3, (h.stamp[3] - h.stamp[2]) * 1e-3,
+            (h.stamp[4] - h.stamp[3]) * 1e-3, ((double)h.stamp[0] - (double)h.stamp[6]) * 1e-3);
+  }
   if (stats) {
     float ms = 0.f;
     FV_CUDA(cudaEventElapsedTime(&ms, tr->ev_begin, tr->ev_end));
@@ -1248,6 +1497,8 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   if (dev_err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "a token id was outside [0, V) (device check)");
   if (dev_err & FV_DEVERR_WINDOW_RANGE)
     return fv::fail(FV_ERR_DATA, "a window order entry or window start was out of range (device check)");
+  if (dev_err & FV_DEVERR_TIMEOUT)
+    return fv::fail(FV_ERR_TIMEOUT, "a peer rank did not deliver its step packet in time; the replicas are out of step");
   if (dev_err & FV_DEVERR_NAN_WEIGHT)
     return fv::fail(FV_ERR_DATA, "a weight was NaN or a unit's scale collapsed to zero (device check)");
   return FV_OK;
@@ -1255,9 +1506,11 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
 
 void free_all(fv_trainer* tr) {
   cudaSetDevice(tr->device);
+  for (int r = 0; r < 16; ++r)
+    if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
-  void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,   tr->d_idx,
-                  tr->d_pkt, tr->d_xx_part, tr->d_aw, tr->d_cnt,    tr->d_saved,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+  void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
+                  tr->d_mail, tr->d_peer_table, tr->d_xx_part, tr->d_aw, tr->d_cnt,    tr->d_saved,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -1297,7 +1550,9 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.B = (int)cfg->batch;
   d.G = cfg->world;
   d.rank = cfg->rank;
-  d.P = d.B + d.Kp;
+  d.XO = (d.B + 3) & ~3;  // keeps every packet 16-byte aligned
+  d.P = d.XO + d.Kp;
+  d.spin_limit = 8u << 20;  // ~10 s of polling with back-off
   d.prec = cfg->prec;
   d.flags = cfg->flags;
   tr->NT = (d.Kq + 31) / 32;
@@ -1306,8 +1561,9 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_TRY(dev_alloc(&tr->d_wt, ((size_t)d.N + 1) * d.Kp));  // one extra all-zero row for padding positions
   FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
-  FV_TRY(dev_alloc(&tr->d_idx, 2 * E));  // this step's ids and the next step's
-  FV_TRY(dev_alloc(&tr->d_pkt, (size_t)d.G * d.P));
+  d.outbox_off = (MAIL_HDR + 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
+  tr->mail_words = d.outbox_off + (d.G > 1 ? 2 * 2 * (size_t)d.G * d.B * d.W : 0);
+  FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
   FV_TRY(dev_alloc(&tr->d_cnt, E));
   FV_TRY(dev_alloc(&tr->d_saved, E));
   FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
@@ -1317,13 +1573,13 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_CUDA(cudaMemsetAsync(tr->d_colmax, 0, 2 * (size_t)d.Kp * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_ncb, 0, 2 * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_ctl, 0, sizeof(StepCtl), tr->stream));
-  FV_CUDA(cudaMemsetAsync(tr->d_pkt, 0, (size_t)d.G * d.P * sizeof(uint32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_mail, 0, tr->mail_words * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_f, 0, (size_t)d.V * sizeof(float), tr->stream));
   d.wt = tr->d_wt;
   d.alpha = tr->d_alpha;
   d.f = tr->d_f;
-  d.pkt_recv = tr->d_pkt;
-  d.pkt_send = tr->d_pkt + (size_t)d.rank * d.P;  // in-place all-gather
+  d.mail = tr->d_mail;
+  d.peers = nullptr;
   d.cnt = tr->d_cnt;
   d.saved = tr->d_saved;
   d.colmax = tr->d_colmax;
@@ -1349,7 +1605,14 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->scan_grid = tr->num_sms * 2;
   tr->tag_grid = grid_for(E, XX_THREADS, tr->num_sms * 4);
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
-  tr->apply_grid = grid_for(E, 256, tr->num_sms * 4);
+  {
+    // k_apply waits on peers inside the kernel (sharded update), so its grid must be fully resident
+    int apply_bps = 0;
+    FV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&apply_bps, k_apply, 256, tr->apply_smem));
+    if (apply_bps < 1) apply_bps = 1;
+    if (apply_bps > 4) apply_bps = 4;
+    tr->apply_grid = grid_for(E, 256, tr->num_sms * apply_bps);
+  }
   FV_TRY(dev_alloc(&tr->d_xx_part, (size_t)tr->xx_grid * d.Kp));
   FV_TRY(dev_alloc(&tr->d_aw, (size_t)d.B));
   d.xx_part = tr->d_xx_part;
@@ -1372,6 +1635,7 @@ int fv_trainer_create(const fv_config* cfg, fv_trainer** out) {
   FV_REQUIRE(cfg->vocab >= 1 && cfg->vocab <= (1u << 29), FV_ERR_INVALID, "vocab out of range: %u", cfg->vocab);
   FV_REQUIRE(cfg->window >= 1 && cfg->window <= 32, FV_ERR_INVALID, "window must be in [1, 32], got %u", cfg->window);
   FV_REQUIRE(cfg->batch >= 1, FV_ERR_INVALID, "batch must be >= 1");
+  FV_REQUIRE(cfg->world <= MAX_RANKS, FV_ERR_INVALID, "world must be at most %d", MAX_RANKS);
   FV_REQUIRE(cfg->world >= 1 && cfg->rank >= 0 && cfg->rank < cfg->world, FV_ERR_INVALID,
              "need world >= 1 and 0 <= rank < world (rank %d, world %d)", cfg->rank, cfg->world);
   FV_REQUIRE((uint64_t)cfg->world * cfg->batch * cfg->window < 0x7ffffeull, FV_ERR_INVALID,
@@ -1584,11 +1848,14 @@ int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* win
   FV_TRY(run_steps_impl(tr, step, 1, eps, nullptr, &nc1, &s1, nullptr));
   fv::DeviceGuard guard(tr->device);
   const Dev& d = tr->d;
+  // the step just run had parity (ticks - 1) & 1
+  const int parity = (int)((tr->ticks - 1) & 1);
   std::vector<uint32_t> pkt((size_t)d.G * d.P);
-  FV_CUDA(cudaMemcpy(pkt.data(), tr->d_pkt, pkt.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  FV_CUDA(cudaMemcpy(pkt.data(), tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P, pkt.size() * sizeof(uint32_t),
+                     cudaMemcpyDeviceToHost));
   for (int r = 0; r < d.G; ++r) {
     if (winners) memcpy(winners + (size_t)r * d.B, pkt.data() + (size_t)r * d.P, (size_t)d.B * sizeof(int32_t));
-    if (xx) memcpy(xx + (size_t)r * d.K, pkt.data() + (size_t)r * d.P + d.B, (size_t)d.K * sizeof(float));
+    if (xx) memcpy(xx + (size_t)r * d.K, pkt.data() + (size_t)r * d.P + d.XO, (size_t)d.K * sizeof(float));
   }
   if (nc) *nc = nc1;
   if (scale) *scale = s1;
@@ -1616,9 +1883,100 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
   Id128 uid;
   memcpy(uid.bytes, id, 128);
   void* comm = nullptr;
-  const int rc = g_nccl.CommInitRank(&comm, tr->d.G, uid, tr->d.rank);
+  int rc = g_nccl.CommInitRank(&comm, tr->d.G, uid, tr->d.rank);
   if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(rc));
   tr->comm = comm;
+  tr->comm_mode = 1;
+
+  // Peer-memory mailboxes: every rank exports its mailbox, the handles travel through the
+  // communicator just created, every rank maps the others'.  If any rank cannot (no peer
+  // access between the GPUs, handle not importable), all ranks stay with the all-gather.
+  const char* force = getenv("FV_COMM");
+  const int G = tr->d.G;
+  constexpr int HB = (int)sizeof(cudaIpcMemHandle_t);  // 64 bytes
+  static_assert(sizeof(cudaIpcMemHandle_t) % 4 == 0, "handle size");
+  int ok = (force && strcmp(force, "nccl") == 0) ? 0 : 1;
+  cudaIpcMemHandle_t mine;
+  memset(&mine, 0, sizeof(mine));
+  if (ok && cudaIpcGetMemHandle(&mine, tr->d_mail) != cudaSuccess) {
+    cudaGetLastError();
+    ok = 0;
+  }
+  uint32_t* d_ex = nullptr;  // [G][HB/4 + 1]: handle words, then an "ok" word
+  const int words = HB / 4 + 1;
+  FV_TRY(dev_alloc(&d_ex, (size_t)G * words));
+  std::vector<uint32_t> ex((size_t)G * words, 0u);
+  memcpy(ex.data() + (size_t)tr->d.rank * words, &mine, HB);
+  ex[(size_t)tr->d.rank * words + HB / 4] = (uint32_t)ok;
+  cudaError_t e = cudaMemcpyAsync(d_ex, ex.data(), ex.size() * 4, cudaMemcpyHostToDevice, tr->stream);
+  if (e == cudaSuccess) {
+    rc = g_nccl.AllGather(d_ex + (size_t)tr->d.rank * words, d_ex, (size_t)words, NCCL_UINT32, tr->comm, tr->stream);
+    if (rc != 0) {
+      cudaFree(d_ex);
+      return fv::fail(FV_ERR_COMM, "ncclAllGather (handles) failed: %s", g_nccl.GetErrorString(rc));
+    }
+    e = cudaMemcpyAsync(ex.data(), d_ex, ex.size() * 4, cudaMemcpyDeviceToHost, tr->stream);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(tr->stream);
+  if (e != cudaSuccess) {
+    cudaFree(d_ex);
+    FV_CUDA(e);
+  }
+  int all_ok = 1;
+  for (int r = 0; r < G; ++r) all_ok &= (int)ex[(size_t)r * words + HB / 4];
+  int mapped = all_ok;
+  if (all_ok) {
+    for (int r = 0; r < G && mapped; ++r) {
+      if (r == tr->d.rank) {
+        tr->peer_mail[r] = tr->d_mail;
+        continue;
+      }
+      cudaIpcMemHandle_t hnd;
+      memcpy(&hnd, ex.data() + (size_t)r * words, HB);
+      void* p = nullptr;
+      if (cudaIpcOpenMemHandle(&p, hnd, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        mapped = 0;
+      } else {
+        tr->peer_mail[r] = static_cast<uint32_t*>(p);
+      }
+    }
+  }
+  // second round: did everybody manage to map everybody?
+  ex.assign((size_t)G * words, 0u);
+  ex[(size_t)tr->d.rank * words] = (uint32_t)mapped;
+  e = cudaMemcpyAsync(d_ex, ex.data(), ex.size() * 4, cudaMemcpyHostToDevice, tr->stream);
+  if (e == cudaSuccess) {
+    rc = g_nccl.AllGather(d_ex + (size_t)tr->d.rank * words, d_ex, (size_t)words, NCCL_UINT32, tr->comm, tr->stream);
+    if (rc != 0) {
+      cudaFree(d_ex);
+      return fv::fail(FV_ERR_COMM, "ncclAllGather (mapping) failed: %s", g_nccl.GetErrorString(rc));
+    }
+    e = cudaMemcpyAsync(ex.data(), d_ex, ex.size() * 4, cudaMemcpyDeviceToHost, tr->stream);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(tr->stream);
+  cudaFree(d_ex);
+  FV_CUDA(e);
+  int all_mapped = 1;
+  for (int r = 0; r < G; ++r) all_mapped &= (int)ex[(size_t)r * words];
+  if (all_mapped) {
+    FV_TRY(dev_alloc(&tr->d_peer_table, (size_t)MAX_RANKS));
+    FV_CUDA(cudaMemcpy(tr->d_peer_table, tr->peer_mail, sizeof(uint32_t*) * MAX_RANKS, cudaMemcpyHostToDevice));
+    tr->d.peers = tr->d_peer_table;
+    tr->d.shard = getenv("FV_NO_SHARD") ? 0 : 1;
+    tr->comm_mode = 2;
+  } else {
+    for (int r = 0; r < G; ++r) {
+      if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
+      tr->peer_mail[r] = nullptr;
+    }
+  }
+  return FV_OK;
+}
+
+int fv_trainer_comm_mode(fv_trainer* tr, int* mode) {
+  FV_REQUIRE(tr && mode, FV_ERR_INVALID, "fv_trainer_comm_mode: NULL argument");
+  *mode = tr->comm_mode;
   return FV_OK;
 }
 

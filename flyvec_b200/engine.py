@@ -140,6 +140,14 @@ class Trainer:
         check(_lib.lib().fv_trainer_init_comm(self._h, buf))
 
 
+    @property
+    def comm_mode(self) -> int:
+        """0 = single rank, 1 = NCCL all-gather per step, 2 = peer-memory mailboxes."""
+        m = C.c_int(0)
+        check(_lib.lib().fv_trainer_comm_mode(self._h, C.byref(m)))
+        return m.value
+
+
 def shard_range(num_windows: int, batch: int, world: int, rank: int, step: int):
     """Windows ``[first, first+count)`` of the current order that ``rank`` owns in
     global step ``step`` (flyvec/src/cuda_funcs.cu:1667-1670)."""

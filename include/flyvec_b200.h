@@ -158,6 +158,12 @@ int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* win
  * (cu_special_reduction.cu:61-66, 345-346). */
 int fv_comm_unique_id(uint8_t id[128]);
 int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
+/* How the ranks exchange their per-step packets: 0 = single rank / not initialised, 1 = one NCCL
+ * all-gather per step, 2 = peer-memory mailboxes (the producing kernel stores its packet into every
+ * peer's memory over NVLink and raises a flag; waits on those flags are bounded and end the call
+ * with FV_ERR_TIMEOUT).  Mode 2 is chosen when every rank can map every other rank's mailbox;
+ * the environment variable FV_COMM=nccl forces mode 1. */
+int fv_trainer_comm_mode(fv_trainer* tr, int* mode);
 /* Which windows of the current order rank `rank` owns in global step `step`
  * (cuda_funcs.cu:1667-1670); pure arithmetic, usable without a GPU. */
 int fv_shard_range(uint64_t num_windows, uint32_t batch, int32_t world, int32_t rank, uint64_t step,
