@@ -268,6 +268,32 @@ __global__ void __launch_bounds__(256) k_hash(HDev h, const int32_t* __restrict_
   }
 }
 
+// A vocabulary has only V distinct token codes.  For a batch much larger than V the codes of all
+// ids are computed once into a table (k_hash over 0..V-1) and the batch becomes a gather of
+// `stride` bytes per token; the table (1 MB at V = 20000, bit-packed) stays in L2.
+__global__ void k_iota32(int32_t* p, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) p[i] = i;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) k_gather_codes(const uint8_t* __restrict__ table, const int32_t* __restrict__ ids,
+                                                      unsigned long long n, int V, int stride, uint8_t* __restrict__ out,
+                                                      uint32_t* error) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned long long nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;
+  const int per = stride / (int)sizeof(T);
+  for (unsigned long long item = warp; item < n; item += nwarps) {
+    int id = ids[item];
+    if (id < 0 || id >= V) {
+      if (lane == 0) atomicOr(error, FV_DEVERR_TOKEN_RANGE);
+      id = 0;
+    }
+    const T* __restrict__ src = reinterpret_cast<const T*>(table + (size_t)id * stride);
+    T* __restrict__ dst = reinterpret_cast<T*>(out + (size_t)item * stride);
+    for (int k = lane; k < per; k += 32) dst[k] = src[k];
+  }
+}
+
 }  // namespace
 
 struct fv_hasher {
@@ -280,6 +306,10 @@ struct fv_hasher {
   uint32_t* d_err = nullptr;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // codes of the whole vocabulary for one (hash length, format), kept between calls
+  uint8_t* d_table = nullptr;
+  int32_t* d_iota = nullptr;
+  uint32_t table_hl = 0, table_flags = 0xffffffffu;
 };
 
 namespace {
@@ -302,11 +332,67 @@ void launch_hash(fv_hasher* hs, int mode, int grid, const int32_t* in, unsigned 
 }
 
 int run_hash(fv_hasher* hs, int mode, const int32_t* d_in, unsigned long long n, int W, uint32_t hash_len,
-             uint32_t flags, uint8_t* d_out, double* seconds) {
+             uint32_t flags, uint8_t* d_out, double* seconds, bool may_allocate = true);
+
+// Token hashing through the vocabulary table.  Builds (or reuses) the table, then gathers.
+int run_hash_table(fv_hasher* hs, const int32_t* d_in, unsigned long long n, uint32_t hash_len, uint32_t flags,
+                   uint8_t* d_out, double* seconds) {
+  const HDev& h = hs->h;
+  const int stride = (flags & FV_HASH_BYTES) ? h.K : (h.K + 7) / 8;
+  const uint32_t key_flags = flags & (FV_HASH_BYTES | FV_HASH_NO_UNK);
+  if (!hs->d_table || hs->table_hl != hash_len || hs->table_flags != key_flags) {
+    if (!hs->d_iota) {
+      FV_CUDA(cudaMalloc((void**)&hs->d_iota, (size_t)h.V * sizeof(int32_t)));
+      k_iota32<<<64, 256, 0, hs->stream>>>(hs->d_iota, h.V);
+      FV_CUDA(cudaGetLastError());
+    }
+    if (hs->d_table && (hs->table_flags & FV_HASH_BYTES) != (key_flags & FV_HASH_BYTES)) {
+      FV_CUDA(cudaFree(hs->d_table));
+      hs->d_table = nullptr;
+    }
+    if (!hs->d_table) FV_CUDA(cudaMalloc((void**)&hs->d_table, (size_t)h.V * stride));
+    hs->table_flags = 0xffffffffu;
+    const int rc = run_hash(hs, 0, hs->d_iota, (unsigned long long)h.V, 0, hash_len, key_flags, hs->d_table, nullptr, false);
+    if (rc != FV_OK) return rc;
+    hs->table_hl = hash_len;
+    hs->table_flags = key_flags;
+  }
+  const unsigned long long blocks = (n + 7) / 8;
+  const unsigned long long cap = (unsigned long long)hs->num_sms * 16;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  FV_CUDA(cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream));
+  FV_CUDA(cudaEventRecord(hs->ev0, hs->stream));
+  if (stride % 16 == 0)
+    k_gather_codes<uint4><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  else if (stride % 4 == 0)
+    k_gather_codes<uint32_t><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  else if (stride % 2 == 0)
+    k_gather_codes<uint16_t><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  else
+    k_gather_codes<uint8_t><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  FV_CUDA(cudaGetLastError());
+  FV_CUDA(cudaEventRecord(hs->ev1, hs->stream));
+  uint32_t err = 0;
+  FV_CUDA(cudaMemcpyAsync(&err, hs->d_err, sizeof(err), cudaMemcpyDeviceToHost, hs->stream));
+  FV_CUDA(cudaStreamSynchronize(hs->stream));
+  if (seconds) {
+    float ms = 0.f;
+    FV_CUDA(cudaEventElapsedTime(&ms, hs->ev0, hs->ev1));
+    *seconds = ms * 1e-3;
+  }
+  if (err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "an input id was out of range (device check)");
+  return FV_OK;
+}
+
+int run_hash(fv_hasher* hs, int mode, const int32_t* d_in, unsigned long long n, int W, uint32_t hash_len,
+             uint32_t flags, uint8_t* d_out, double* seconds, bool may_allocate) {
   FV_REQUIRE(hash_len >= 1 && (int)hash_len < hs->h.K, FV_ERR_INVALID,
              "hash_length must be in [1, K-1] (K = %d), got %u", hs->h.K, hash_len);
   if (seconds) *seconds = 0.0;
   if (n == 0) return FV_OK;
+  // many more tokens than vocabulary entries: hash the vocabulary once, then gather
+  if (mode == 0 && may_allocate && n >= 4ull * (unsigned long long)hs->h.V)
+    return run_hash_table(hs, d_in, n, hash_len, flags, d_out, seconds);
   unsigned long long blocks = (n + 7) / 8;
   const unsigned long long cap = (unsigned long long)hs->num_sms * 8;
   const int grid = (int)(blocks < cap ? blocks : cap);
@@ -341,6 +427,8 @@ void free_hasher(fv_hasher* hs) {
   if (hs->d_wt) cudaFree(hs->d_wt);
   if (hs->d_f) cudaFree(hs->d_f);
   if (hs->d_err) cudaFree(hs->d_err);
+  if (hs->d_table) cudaFree(hs->d_table);
+  if (hs->d_iota) cudaFree(hs->d_iota);
   if (hs->ev0) cudaEventDestroy(hs->ev0);
   if (hs->ev1) cudaEventDestroy(hs->ev1);
   if (hs->stream) cudaStreamDestroy(hs->stream);
@@ -557,7 +645,7 @@ int fv_hash_tokens_static(fv_hasher* hs, const int32_t* ids, uint64_t n, uint32_
   int32_t* d_ids = reinterpret_cast<int32_t*>(base);
   uint8_t* d_out = base + ((n * sizeof(int32_t) + 255) & ~(size_t)255);
   FV_CUDA(cudaMemcpyAsync(d_ids, ids, n * sizeof(int32_t), cudaMemcpyHostToDevice, hs->stream));
-  const int rc = run_hash(hs, 0, d_ids, n, 0, hash_length, flags, d_out, nullptr);
+  const int rc = run_hash(hs, 0, d_ids, n, 0, hash_length, flags, d_out, nullptr, /*may_allocate=*/false);
   if (rc != FV_OK) return rc;
   FV_CUDA(cudaMemcpyAsync(out, d_out, n * out_per, cudaMemcpyDeviceToHost, hs->stream));
   FV_CUDA(cudaStreamSynchronize(hs->stream));

@@ -10,7 +10,7 @@
 //   tokens, wstart, perm    corpus, window starts, window order.
 //   idx     int  [G*B][w]   input ids of the current global step (all ranks' windows).
 //   pkt     u32  [G][B+Kp]  per rank: B winners then Kp floats of xx; all-gathered.
-//   cnt/saved   [G*B*w]     scatter bookkeeping, one slot per (window, position).
+//   cnt/rec     [G*B*w]     scatter bookkeeping: one record per distinct touched position.
 //
 // One global step (reference: run_epoch, flyvec/src/cuda_funcs.cu:1662-1812):
 //   k_forward    T4   window -> input ids                    (cuda_funcs.cu:915-936)
@@ -20,7 +20,7 @@
 //   (k_build_idx_block, on a side stream: ids of the next 32 steps, all ranks' windows)
 //   all-gather        winners + xx of every rank (NCCL)
 //   k_tag        T10  each touched (mu,i) gets one owner slot; its weight is parked in
-//                     `saved` and replaced by a tagged NaN     (cuda_funcs.cu:657-672)
+//                     a record and replaced by a tagged NaN    (cuda_funcs.cu:657-672)
 //   k_scan       T11  nc = max|D|: exact D at touched positions, column max of |wt|
 //                     over untouched ones (tags read as 0)     (cu_special_reduction.cu:26-99)
 //   k_apply      T12-13 s = eps/max(prec,nc); alpha *= 1 - s*X; touched weights restored
@@ -56,6 +56,7 @@ struct StepCtl {
   uint32_t apply_ticket;  // CTAs of the running k_apply that have finished their own slots
   uint32_t out_count;     // entries in this step's outbox (sharded update)
   uint32_t pad;
+  uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
   unsigned long long stamp[8];  // %globaltimer at phase boundaries of the last step (diagnostics)
 };
 
@@ -79,7 +80,7 @@ struct Dev {
   float* aw;       // [B] weighted activation of each window's winner
   float* xx_part;  // [k_xx CTAs][Kp] partial sums of xx
   int32_t* cnt;
-  float* saved;
+  uint4* rec;      // [G*B*w] touched-position records {position, parked weight bits, 1/count bits, 0}
   uint32_t* colmax;
   uint32_t* ncb;
   StepCtl* ctl;
@@ -500,6 +501,8 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
 // ---------------------------------------------------------------------------
 constexpr int XX_THREADS = 512;
 constexpr int XX_WARPS = XX_THREADS / 32;
+constexpr int TAG_TABLE_LOG2 = 11;
+constexpr int TAG_TABLE = 1 << TAG_TABLE_LOG2;  // shared-memory hash table, at most half full
 __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nctas, unsigned char* xx_smem) {
   float* bins = reinterpret_cast<float*>(xx_smem);  // [XX_WARPS][Kp]
   __shared__ unsigned s_ticket;
@@ -604,18 +607,20 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
 }
 
 // ---------------------------------------------------------------------------
-// T10 bookkeeping.  Every (window, position) of every rank is a slot e.  The
-// first slot to reach a matrix position (i, mu) becomes its owner: it parks the
-// weight in saved[e] and leaves TAG_BASE|(e+1) -- a NaN bit pattern no weight
-// can have -- in its place; later slots for the same position find the tag and
-// bump the owner's count.  A slot is skipped when its rank's xx[mu] is zero: the
-// reference drops a replica's whole row from the combine in that case
-// (cu_special_reduction.cu:42-66).
+// T10 bookkeeping.  Every (window, position) of every rank wants to add f_i to the
+// matrix position (i, winner).  Each distinct position gets one record
+// {position, parked weight, f_i} in a compact list and a count of how many wanted
+// it: the claimant parks the weight in the record and leaves TAG_BASE|(record+1) --
+// a NaN bit pattern no weight can have -- in its place; later comers for the same
+// position find the tag and add to the claimant's count.  A (window, position) is
+// skipped when its rank's xx[winner] is zero: the reference drops a replica's whole
+// row from the combine in that case (cu_special_reduction.cu:42-66).
 // ---------------------------------------------------------------------------
 // With xx_ctas > 0 (single rank) the first xx_ctas CTAs compute xx instead, side by
 // side with the tagging; tagging then cannot ask whether the rank was active for a
 // unit and tags every slot -- a unit that turns out inactive simply gets its parked
 // weights back unchanged in k_apply.
+template <int UN>  // slots per thread and block round: a CTA deduplicates UN * XX_THREADS slots together
 __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas) {
   grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char tag_smem[];
@@ -636,40 +641,179 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int3
     __syncthreads();
     if (s_fail) return;
   }
+  // Stage 1: a block of TAG_BLOCK slots is deduplicated in a shared-memory hash table keyed by the
+  // matrix position, so a (unit, token) pair that occurs many times in the block -- frequent tokens
+  // do -- reaches global memory once, with its multiplicity.  Same-address global atomics complete
+  // at about one per nanosecond, which made the duplicates of the hottest pairs the bottleneck.
+  // Stage 2: every distinct position gets a record slot (one counter bump per block) and is claimed
+  // with one CAS; the winner of the claim writes the record, the others add their multiplicity to
+  // the claimant's count.
+  __shared__ uint32_t s_key[TAG_TABLE];
+  __shared__ int s_cnt[TAG_TABLE];
+  __shared__ uint32_t s_scan[XX_THREADS / 32 + 1];
   const int E = d.G * d.B * d.W;
   const bool check_active = (xx_ctas == 0);
-  const int nthreads = (gridDim.x - xx_ctas) * blockDim.x;
-  for (int e = (blockIdx.x - xx_ctas) * blockDim.x + threadIdx.x; e < E; e += nthreads) {
-    const int i = idx[e];
-    if (i < 0) continue;
-    if (d.shard && (i % d.G) != d.rank) continue;  // another rank owns this row
-    const int q = e / d.W;
-    const int r = q / d.B, j = q - r * d.B;
-    const uint32_t* __restrict__ pkt = packet(d, parity, r);
-    const int mu = (int)pkt[j];
-    if (mu < 0) continue;
-    if (check_active && __uint_as_float(pkt[d.XO + mu]) == 0.f) continue;
-    uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt + (size_t)i * d.Kp + mu);
-    uint32_t cur = __ldcg(addr);
-    const uint32_t tag = TAG_BASE | (uint32_t)(e + 1);
-    for (;;) {
-      if ((cur & ABS_MASK) > TAG_BASE) {
-        const uint32_t owner = (cur & 0x007fffffu) - 1u;
-        if ((cur >> 31) || owner >= (uint32_t)E) {
-          atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
-        } else {
-          atomicAdd(&d.cnt[owner], 1);
+  constexpr int TAG_BLOCK = UN * XX_THREADS;
+  const int nblocks = (E + TAG_BLOCK - 1) / TAG_BLOCK;
+  const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  for (int blk = blockIdx.x - xx_ctas; blk < nblocks; blk += gridDim.x - xx_ctas) {
+    if constexpr (UN == 1) {
+      // small steps: duplicates inside 512 slots are rare, so skip the table: number the live slots of
+      // the CTA with a ballot/prefix (one counter bump per CTA round) and claim directly
+      const int e = blk * TAG_BLOCK + threadIdx.x;
+      const int i0 = (e < E) ? idx[e] : -1;
+      bool go0 = i0 >= 0 && !(d.shard && (i0 % d.G) != d.rank);
+      int mu0 = -1;
+      if (go0) {
+        const int q = e / d.W;
+        const int r = q / d.B, j = q - r * d.B;
+        const uint32_t* __restrict__ pkt = packet(d, parity, r);
+        mu0 = (int)pkt[j];
+        go0 = mu0 >= 0 && !(check_active && __uint_as_float(pkt[d.XO + mu0]) == 0.f);
+      }
+      uint32_t c0 = 0u;
+      if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt + (size_t)i0 * d.Kp + mu0));
+      const unsigned live = __ballot_sync(FULL, go0);
+      if (lane == 0) s_scan[wic] = (uint32_t)__popc(live);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t tot = 0;
+        for (int w = 0; w < XX_THREADS / 32; ++w) {
+          const uint32_t c = s_scan[w];
+          s_scan[w] = tot;
+          tot += c;
         }
-        break;
+        s_scan[XX_THREADS / 32] = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
       }
-      const uint32_t prev = atomicCAS(addr, cur, tag);
-      if (prev == cur) {
-        d.saved[e] = __uint_as_float(cur);
-        atomicAdd(&d.cnt[e], 1);
-        break;
+      __syncthreads();
+      if (go0) {
+        const uint32_t slot = s_scan[XX_THREADS / 32] + s_scan[wic] + (uint32_t)__popc(live & ((1u << lane) - 1u));
+        const uint32_t pos = (uint32_t)((size_t)i0 * d.Kp + mu0);
+        uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
+        const uint32_t tag = TAG_BASE | (slot + 1u);
+        uint32_t c = c0;
+        for (;;) {
+          if ((c & ABS_MASK) > TAG_BASE) {
+            const uint32_t owner = (c & 0x007fffffu) - 1u;
+            if ((c >> 31) || owner >= (uint32_t)E) {
+              atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+            } else {
+              atomicAdd(&d.cnt[owner], 1);
+            }
+            break;
+          }
+          const uint32_t prev = atomicCAS(addr, c, tag);
+          if (prev == c) {
+            d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (i0 % d.V))), 1u);
+            break;
+          }
+          c = prev;
+        }
       }
-      cur = prev;
+      __syncthreads();
+    } else {
+    for (int t = threadIdx.x; t < TAG_TABLE; t += XX_THREADS) {
+      s_key[t] = 0u;
+      s_cnt[t] = 0;
     }
+    __syncthreads();
+    int i[UN], mu[UN];
+    bool go[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int e = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      i[u] = (e < E) ? idx[e] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int e = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      go[u] = i[u] >= 0 && !(d.shard && (i[u] % d.G) != d.rank);  // sharded: another rank owns this row
+      mu[u] = -1;
+      if (go[u]) {
+        const int q = e / d.W;
+        const int r = q / d.B, j = q - r * d.B;
+        mu[u] = (int)packet(d, parity, r)[j];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      go[u] = go[u] && mu[u] >= 0;
+      if (go[u] && check_active) {
+        const int e = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+        const int r = (e / d.W) / d.B;
+        go[u] = __uint_as_float(packet(d, parity, r)[d.XO + mu[u]]) != 0.f;
+      }
+      if (go[u]) {
+        const uint32_t key = (uint32_t)((size_t)i[u] * d.Kp + mu[u]) + 1u;
+        uint32_t h = (key * 2654435761u) >> (32 - TAG_TABLE_LOG2);
+        for (;;) {
+          const uint32_t old = atomicCAS(&s_key[h], 0u, key);
+          if (old == 0u || old == key) {
+            atomicAdd(&s_cnt[h], 1);
+            break;
+          }
+          h = (h + 1) & (TAG_TABLE - 1);
+        }
+      }
+    }
+    __syncthreads();
+    // compact numbering of the occupied table slots (each thread owns TAG_TABLE / XX_THREADS of them)
+    constexpr int PER = TAG_TABLE / XX_THREADS;
+    int occ = 0;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) occ += (s_key[threadIdx.x * PER + k] != 0u);
+    int incl = occ;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(FULL, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_scan[wic] = (uint32_t)incl;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t tot = 0;
+      for (int w = 0; w < XX_THREADS / 32; ++w) {
+        const uint32_t c = s_scan[w];
+        s_scan[w] = tot;
+        tot += c;
+      }
+      s_scan[XX_THREADS / 32] = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
+    }
+    __syncthreads();
+    uint32_t slot = s_scan[XX_THREADS / 32] + s_scan[wic] + (uint32_t)(incl - occ);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const uint32_t key = s_key[threadIdx.x * PER + k];
+      if (key == 0u) continue;
+      const int mult = s_cnt[threadIdx.x * PER + k];
+      const uint32_t pos = key - 1u;
+      uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
+      const uint32_t tag = TAG_BASE | (slot + 1u);
+      uint32_t c = __ldcg(addr);
+      for (;;) {
+        if ((c & ABS_MASK) > TAG_BASE) {
+          const uint32_t owner = (c & 0x007fffffu) - 1u;
+          if ((c >> 31) || owner >= (uint32_t)E) {
+            atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+          } else {
+            atomicAdd(&d.cnt[owner], mult);
+          }
+          break;
+        }
+        const uint32_t prev = atomicCAS(addr, c, tag);
+        if (prev == c) {
+          const int irow = (int)(pos / (uint32_t)d.Kp);
+          // the claimant's own multiplicity travels in the record; cnt[] only collects later comers,
+          // so a position touched from one block costs no counter atomic at all
+          d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (irow % d.V))), (uint32_t)mult);
+          break;
+        }
+        c = prev;
+      }
+      ++slot;
+    }
+    __syncthreads();
+    }  // table path
   }
 }
 
@@ -725,13 +869,21 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   }
   __syncthreads();
 
-  // part 1, first half: counts of this thread's slots (up to two per pass over the grid)
-  const int E = d.G * d.B * d.W;
+  // part 1, first half: counts and records of this thread's share of the touched-position list
+  // (coalesced loads, issued before the row stream so that their latency hides behind it)
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W));
   const int nthreads = gridDim.x * blockDim.x;
   const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
-  const int e1 = e0 + nthreads;
-  const int c0 = (e0 < E) ? d.cnt[e0] : 0;
-  const int c1 = (e1 < E) ? d.cnt[e1] : 0;
+  constexpr int TS = 4;
+  int cs[TS];
+  uint4 rc[TS];
+#pragma unroll
+  for (int u = 0; u < TS; ++u) {
+    const int k = e0 + u * nthreads;
+    cs[u] = (k < nrec) ? d.cnt[k] : 0;
+    rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+    cs[u] = rc[u].w ? cs[u] + (int)rc[u].w : 0;  // a record without a claimant (w == 0) is a hole
+  }
 
   // part 2: column maxima of |wt| with tags read as 0
   const int Kq = d.Kq;
@@ -775,21 +927,22 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     if (m3) atomicMax(&sMax[4 * q + 3], m3);
   }
 
-  // part 1, second half: exact D at the touched positions this thread owns
+  // part 1, second half: exact D at the touched positions (records with a count; reserved
+  // records whose position somebody else had claimed keep count 0)
   uint32_t tmax = 0u;
-  auto touched = [&](int e, int c) {
+  auto touched = [&](int c, const uint4& r) {
     if (c <= 0) return;
-    const int i = idx[e];
-    const int qq = e / d.W;
-    const int r = qq / d.B, j = qq - r * d.B;
-    const int mu = (int)packet(d, p, r)[j];
+    const int mu = (int)(r.x % (uint32_t)d.Kp);
     if (sN[mu] == 0) return;  // tagged before the unit proved inactive: no update there
-    const double D = -sC[mu] * (double)d.saved[e] + (double)c * (double)__ldg(d.f + (i % d.V)) / (double)sN[mu];
+    const double D = -sC[mu] * (double)__uint_as_float(r.y) + (double)c * (double)__uint_as_float(r.z) / (double)sN[mu];
     tmax = max(tmax, __float_as_uint(fabsf((float)D)));
   };
-  touched(e0, c0);
-  touched(e1, c1);
-  for (int e = e1 + nthreads; e < E; e += nthreads) touched(e, d.cnt[e]);
+#pragma unroll
+  for (int u = 0; u < TS; ++u) touched(cs[u], rc[u]);
+  for (int k = e0 + TS * nthreads; k < nrec; k += nthreads) {
+    const uint4 r = d.rec[k];
+    touched(r.w ? d.cnt[k] + (int)r.w : 0, r);
+  }
   __shared__ uint32_t s_tmax;
   if (threadIdx.x == 0) s_tmax = 0u;
   __syncthreads();
@@ -837,7 +990,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 // ---------------------------------------------------------------------------
 // T12 + T13.  Every CTA derives nc and the step size from the K column maxima
 // (cheap) and then walks its share of the slots: owners write
-//   wt = saved + cnt * f_i * s / (n * alpha')      with alpha' = alpha * (1 - s*X)
+//   wt = parked + cnt * f_i * s / (n * alpha')     with alpha' = alpha * (1 - s*X)
 // and clear their count.  CTA 0 publishes alpha' and the step's nc and s, and
 // clears the maxima the next step will accumulate into.
 // ---------------------------------------------------------------------------
@@ -924,30 +1077,48 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   const int E = d.G * d.B * d.W;
   uint2* __restrict__ my_out = outbox(d, d.mail, p);
   uint32_t vmax = 0u;
-  __shared__ unsigned s_wcount[8], s_base;
-  for (int e0 = blockIdx.x * blockDim.x; e0 < E; e0 += gridDim.x * blockDim.x) {
-    const int e = min(e0 + (int)threadIdx.x, E - 1);
-    const bool in_range = e0 + (int)threadIdx.x < E;
-    // the slot chain: count -> (id, winner, parked weight) -> 1/count of the token -> new weight
-    const int q = e / d.W;
-    const int c = in_range ? d.cnt[e] : 0;
-    int i = -1, mu = 0;
-    float sv = 0.f, fi = 0.f;
-    if (c > 0) {
-      i = idx[e];
-      const int r = q / d.B, j = q - r * d.B;
-      mu = (int)packet(d, p, r)[j];
-      sv = d.saved[e];
-      fi = __ldg(d.f + (i % d.V));
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)E);
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->list_count[p ^ 1] = 0u;  // the next step counts from zero
+  if (!d.shard) {
+    constexpr int UN = 4;
+    const int nthreads = gridDim.x * blockDim.x;
+    for (int k0 = blockIdx.x * blockDim.x + threadIdx.x; k0 < nrec; k0 += UN * nthreads) {
+      int c[UN];
+      uint4 r[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int k = k0 + u * nthreads;
+        c[u] = (k < nrec) ? d.cnt[k] : 0;
+        r[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+        c[u] = r[u].w ? c[u] + (int)r[u].w : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (c[u] <= 0) continue;
+        const int mu = (int)(r[u].x % (uint32_t)d.Kp);
+        const float v = (float)((double)__uint_as_float(r[u].y) + (double)c[u] * (double)__uint_as_float(r[u].z) * sX[mu]);
+        d.wt[r[u].x] = v;
+        d.rec[k0 + u * nthreads].w = 0u;  // the slot is a hole again until it is claimed anew
+        if (c[u] != (int)r[u].w) d.cnt[k0 + u * nthreads] = 0;
+        vmax = max(vmax, __float_as_uint(fabsf(v)));
+      }
     }
+  }
+  __shared__ unsigned s_wcount[8], s_base;
+  for (int k0 = blockIdx.x * blockDim.x; d.shard && k0 < nrec; k0 += gridDim.x * blockDim.x) {
+    const int k = k0 + (int)threadIdx.x;
+    uint4 r = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+    const int c = r.w ? d.cnt[k] + (int)r.w : 0;
     float v = 0.f;
     if (c > 0) {
-      v = (float)((double)sv + (double)c * (double)fi * sX[mu]);
-      d.wt[(size_t)i * d.Kp + mu] = v;
-      d.cnt[e] = 0;
+      const int mu = (int)(r.x % (uint32_t)d.Kp);
+      v = (float)((double)__uint_as_float(r.y) + (double)c * (double)__uint_as_float(r.z) * sX[mu]);
+      d.wt[r.x] = v;
+      d.rec[k].w = 0u;
+      d.cnt[k] = 0;
       vmax = max(vmax, __float_as_uint(fabsf(v)));
     }
-    if (d.shard) {
+    {
       // the other replicas need this value too: append (position, value) to this step's outbox;
       // slots are handed out per CTA and loop round (one global atomic), then per warp, then per lane
       const unsigned owners = __ballot_sync(FULL, c > 0);
@@ -966,7 +1137,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
       __syncthreads();
       if (c > 0) {
         const unsigned slot = s_base + s_wcount[wic] + __popc(owners & ((1u << ln) - 1u));
-        my_out[slot] = make_uint2((unsigned)((size_t)i * d.Kp + mu), __float_as_uint(v));
+        my_out[slot] = make_uint2(r.x, __float_as_uint(v));
       }
       __syncthreads();
     }
@@ -1218,7 +1389,7 @@ struct fv_trainer {
   float* d_xx_part = nullptr;
   float* d_aw = nullptr;
   int32_t* d_cnt = nullptr;
-  float* d_saved = nullptr;
+  uint4* d_rec = nullptr;
   uint32_t* d_colmax = nullptr;
   uint32_t* d_ncb = nullptr;
   StepCtl* d_ctl = nullptr;
@@ -1226,6 +1397,7 @@ struct fv_trainer {
   size_t log_cap = 0;
   unsigned long long steps_since_fold = 0;
   unsigned long long ticks = 0;  // host copy of StepCtl::tick
+  int tag_un = 1;
   int fwd_grid = 0, xx_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
   size_t fwd_smem = 0, xx_smem = 0, scan_smem = 0, apply_smem = 0;
 };
@@ -1340,9 +1512,10 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, cudaEvent_t* mar
   }
   if (marks) FV_CUDA(cudaEventRecord(marks[2], tr->stream));
   if (single)  // xx is computed by the first CTAs of the tagging kernel
-    launch_pdl(k_tag, tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local, idx, tr->xx_grid);
+    launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local, idx,
+               tr->xx_grid);
   else
-    launch_pdl(k_tag, tr->tag_grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, 0);
+    launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, 0);
   launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
   launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
   if (marks) FV_CUDA(cudaEventRecord(marks[3], tr->stream));
@@ -1510,7 +1683,7 @@ void free_all(fv_trainer* tr) {
     if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
-                  tr->d_mail, tr->d_peer_table, tr->d_xx_part, tr->d_aw, tr->d_cnt,    tr->d_saved,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+                  tr->d_mail, tr->d_peer_table, tr->d_xx_part, tr->d_aw, tr->d_cnt,    tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -1565,7 +1738,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->mail_words = d.outbox_off + (d.G > 1 ? 2 * 2 * (size_t)d.G * d.B * d.W : 0);
   FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
   FV_TRY(dev_alloc(&tr->d_cnt, E));
-  FV_TRY(dev_alloc(&tr->d_saved, E));
+  FV_TRY(dev_alloc(&tr->d_rec, E));
   FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_ncb, 2));
   FV_TRY(dev_alloc(&tr->d_ctl, 1));
@@ -1581,7 +1754,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.mail = tr->d_mail;
   d.peers = nullptr;
   d.cnt = tr->d_cnt;
-  d.saved = tr->d_saved;
+  d.rec = tr->d_rec;
   d.colmax = tr->d_colmax;
   d.ncb = tr->d_ncb;
   d.ctl = tr->d_ctl;
@@ -1594,7 +1767,8 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + sizeof(uint32_t));
   tr->apply_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int));
   FV_CUDA(cudaFuncSetAttribute(k_xx, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
-  FV_CUDA(cudaFuncSetAttribute(k_tag, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
+  FV_CUDA(cudaFuncSetAttribute(k_tag<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
+  FV_CUDA(cudaFuncSetAttribute(k_tag<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
   int fwd_bps = 0;
   cudaError_t oerr = cudaSuccess;
   FV_DISPATCH_NT(tr->NT, forward_occupancy, &fwd_bps, tr->fwd_smem, &oerr);
@@ -1603,7 +1777,9 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->fwd_grid = grid_for((size_t)d.B * 32, FWD_THREADS, tr->num_sms * fwd_bps);
   tr->xx_grid = grid_for((size_t)d.B, 2048, 8);
   tr->scan_grid = tr->num_sms * 2;
-  tr->tag_grid = grid_for(E, XX_THREADS, tr->num_sms * 4);
+  // small steps: one slot per thread keeps enough CTAs busy; large steps deduplicate 1024 slots per CTA
+  tr->tag_un = (E >= (size_t)tr->num_sms * 4 * XX_THREADS) ? 2 : 1;
+  tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, tr->num_sms * 4);
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
   {
     // k_apply waits on peers inside the kernel (sharded update), so its grid must be fully resident
@@ -1963,7 +2139,7 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
     FV_TRY(dev_alloc(&tr->d_peer_table, (size_t)MAX_RANKS));
     FV_CUDA(cudaMemcpy(tr->d_peer_table, tr->peer_mail, sizeof(uint32_t*) * MAX_RANKS, cudaMemcpyHostToDevice));
     tr->d.peers = tr->d_peer_table;
-    tr->d.shard = getenv("FV_NO_SHARD") ? 0 : 1;
+    tr->d.shard = getenv("FV_SHARD") ? 1 : 0;  // sharded update: opt-in (see the mode table in the header)
     tr->comm_mode = 2;
   } else {
     for (int r = 0; r < G; ++r) {
