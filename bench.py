@@ -31,6 +31,10 @@ sys.path.insert(0, str(ROOT))
 
 CFG = dict(K=400, V=20000, W=11, batch=10000, lr=2e-4, zipf_s=1.0, chunk_mean=25.0, tokens_per_gpu=50_000_000)
 CORPUS_SEED, WEIGHT_SEED, PERM_SEED = 101, 1, 201
+# DRAM bytes (read + write) of one k_forward launch at config-1 shapes inside the running step loop, from the
+# ncu capture summarised in profiles/train_step_config1.md (caches as the pipeline leaves them); with ncu's
+# cache flush before the launch the same kernel reads 27.4 MB.
+FWD_DRAM_TRAFFIC_BYTES = 1.8e6
 
 
 # ----------------------------------------------------------------------------
@@ -247,9 +251,12 @@ def bench_train(args):
     e2e_value = e2e_steps * world * B / e2e_wall
 
     # ---- roofline of the dominant kernel ---------------------------------------
+    # k_forward is timed live as 50 back-to-back launches between two CUDA events on the trainer's
+    # stream (an event pair around a single launch inside the step loop also counts the launch
+    # latency that the pipelined loop hides).
     peak, peak_src = measured_peaks()
     fwd_bytes = B * W * K * 4 + B * (8 + 4 * W) + B * 8  # gathered rows + order entry and ids + winner and activation out
-    fwd_avg = fwd_s / steps
+    fwd_avg = dist.max(tr.time_forward(warmup + steps, reps=50))
     achieved = fwd_bytes / fwd_avg / 1e9
     step_bytes = B * W * K * 4 + 3 * K * 2 * V * 4 + B * (8 + 4 * W) + B * 2 + K * 4  # the reference schedule's figure
 
@@ -271,10 +278,10 @@ def bench_train(args):
                         "per-step normaliser copied back"},
         "gpu_launches": int(st["kernel_launches"]),
         "roofline": {"kernel": "k_forward (fused gather-sum + arg-max)", "bound": "hbm", "achieved": achieved,
-                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": FWD_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": fwd_bytes, "avg_launch_ms": fwd_avg * 1e3,
                      "note": "rows are gathered from the L2-resident matrix, so achieved can exceed the HBM figure"},
-        "phases_ms_per_step": {"forward": fwd_avg * 1e3, "xx+exchange": dist.max(st["exch_seconds"]) / steps * 1e3,
+        "phases_ms_per_step": {"forward": fwd_s / steps * 1e3, "xx+exchange": dist.max(st["exch_seconds"]) / steps * 1e3,
                                "update": dist.max(st["upd_seconds"]) / steps * 1e3},
         "step_algorithmic_gbs": step_bytes / (sec / steps) / 1e9,
         "last_nc": st["last_nc"],
@@ -309,7 +316,8 @@ def bench_hash(args, windows: bool):
     else:
         n = args.items or 1_000_000
         ids = synth.make_hash_ids(n, V, seed=100)
-        per_item = K * 4 + code_b
+        # large batches go through the vocabulary table: an id in, a code gathered from the table and written out
+        per_item = (4 + 2 * code_b) if n >= 4 * V else (K * 4 + code_b)
     d_in = engine.DeviceBuffer(ids.nbytes)
     d_in.upload(ids)
     d_out = engine.DeviceBuffer(n * code_b)

@@ -51,7 +51,7 @@ struct StepCtl {
   uint32_t wabsmax;       // bit pattern of an upper bound of max |wt|
   uint32_t wabsmax_fold;  // the same, collected while folding
   uint32_t xx_ticket;     // CTAs of the running k_xx that have finished
-  uint32_t fwd_next;      // next window index k_forward hands out beyond the first round
+  uint32_t fwd_next[2];   // window tickets k_forward hands out beyond the first round, by step parity
   uint32_t scan_ticket;   // CTAs of the running k_scan that have finished
   uint32_t apply_ticket;  // CTAs of the running k_apply that have finished their own slots
   uint32_t out_count;     // entries in this step's outbox (sharded update)
@@ -185,7 +185,7 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) { return __reduce_m
 __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps) {
   ctl->base = base;
   ctl->eps = eps;
-  ctl->fwd_next = 0u;
+  ctl->fwd_next[0] = ctl->fwd_next[1] = 0u;
   ctl->xx_ticket = 0u;
 }
 __global__ void k_advance(StepCtl* ctl, unsigned long long n) {
@@ -375,6 +375,11 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   const int Kq = d.Kq;
   const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.B * d.W;
 
+  // tickets: this launch draws from the counter of its parity and clears the other one, so that
+  // consecutive launches need nobody else to reset anything
+  const int par = (int)((d.ctl->tick + local) & 1);
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->fwd_next[par ^ 1] = 0u;
+
   int j = warp;
   int my = (j < d.B && lane < d.W) ? idx_own[(size_t)j * d.W + lane] : -1;
 
@@ -406,7 +411,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
     // one per nanosecond, so one ticket per window would cost as much as the gather itself.
     int jn = j + 1;
     const bool need_ticket = (j >= jlast);
-    if (need_ticket && lane == 0) jn = nwarps + 2 * (int)atomicAdd(&d.ctl->fwd_next, 1u);
+    if (need_ticket && lane == 0) jn = nwarps + 2 * (int)atomicAdd(&d.ctl->fwd_next[par], 1u);
     int winner = -1;
     float awv = 0.f;
     int n_my = -1;
@@ -576,7 +581,7 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
     }
     if (threadIdx.x == 0) {
       d.ctl->xx_ticket = 0u;
-      d.ctl->fwd_next = 0u;
+      d.ctl->fwd_next[parity] = 0u;  // rank emulation runs several forward passes per step
     }
     if (d.peers != nullptr && d.G > 1) {
       // Exchange fused into the producer: push the finished packet (winners + xx) into every
@@ -1068,10 +1073,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
       d.colmax[(p ^ 1) * d.Kp + mu] = 0u;
     }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    d.ncb[p ^ 1] = 0u;
-    d.ctl->fwd_next = 0u;
-  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.ncb[p ^ 1] = 0u;
   __syncthreads();
 
   const int E = d.G * d.B * d.W;
@@ -2035,6 +2037,30 @@ int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* win
   }
   if (nc) *nc = nc1;
   if (scale) *scale = s1;
+  return FV_OK;
+}
+
+int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double* seconds_per_launch) {
+  FV_REQUIRE(tr && seconds_per_launch && reps >= 1, FV_ERR_INVALID, "fv_trainer_time_forward: bad argument");
+  FV_REQUIRE(tr->have_weights && tr->have_corpus, FV_ERR_STATE, "trainer needs a corpus and weights");
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  const Dev& d = tr->d;
+  const size_t step_ids = (size_t)d.G * d.B * d.W;
+  if (!tr->d_idx_stage[0]) FV_TRY(dev_alloc(&tr->d_idx_stage[0], step_ids * STAGE_STEPS));
+  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, step, 0.f);
+  k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->stream>>>(d, step, 1, tr->d_idx_stage[0]);
+  // the kernel only writes winners and activations, so it can be repeated on the same step;
+  // alternating the parity lets each launch clear the ticket counter of the next
+  for (uint32_t r = 0; r < 3; ++r) FV_DISPATCH_NT(tr->NT, launch_forward, tr, (int)(r & 1), tr->d_idx_stage[0]);
+  FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
+  for (uint32_t r = 0; r < reps; ++r) FV_DISPATCH_NT(tr->NT, launch_forward, tr, (int)((r + 1) & 1), tr->d_idx_stage[0]);
+  FV_CUDA(cudaEventRecord(tr->ev_end, tr->stream));
+  FV_CUDA(cudaGetLastError());
+  FV_CUDA(cudaStreamSynchronize(tr->stream));
+  float ms = 0.f;
+  FV_CUDA(cudaEventElapsedTime(&ms, tr->ev_begin, tr->ev_end));
+  *seconds_per_launch = ms * 1e-3 / reps;
   return FV_OK;
 }
 

@@ -127,6 +127,12 @@ class Trainer:
         check(_lib.lib().fv_trainer_step_debug(self._h, step, eps, ptr(win), ptr(xx), C.byref(nc), C.byref(sc)))
         return win.reshape(self.G, self.B), xx, np.float32(nc.value), np.float32(sc.value)
 
+    def time_forward(self, step: int, reps: int = 50) -> float:
+        """Seconds per launch of the fused gather/arg-max kernel, back-to-back launches."""
+        sec = C.c_double(0)
+        check(_lib.lib().fv_trainer_time_forward(self._h, step, reps, C.byref(sec)))
+        return sec.value
+
     # -- multi-GPU ----------------------------------------------------------
     @staticmethod
     def comm_unique_id() -> bytes:

@@ -152,6 +152,11 @@ int fv_trainer_run_steps_host(fv_trainer* tr, const int32_t* idx_host, uint64_t 
 int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* winners, float* xx, float* nc,
                           float* scale);
 
+/* Measurement aid: average duration of the fused gather/arg-max kernel (T4-T8 for this rank's block of
+ * global step `step`) over `reps` back-to-back launches, timed with CUDA events on the trainer's stream.
+ * The kernel only writes winners and activations, so repeating it leaves the weights untouched. */
+int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double* seconds_per_launch);
+
 /* Multi-GPU: one process per GPU.  Rank 0 draws an id, the caller ships the 128
  * bytes to the other ranks by any means, every rank calls init_comm.  Replaces
  * the reference's single-process peer access over managed memory
