@@ -72,6 +72,7 @@ _PROTOTYPES = {
     "fv_trainer_create": ([C.POINTER(FvConfig), C.POINTER(_P)], C.c_int),
     "fv_trainer_destroy": ([_P], C.c_int),
     "fv_trainer_set_corpus": ([_P, _P, C.c_uint64, _P, C.c_uint64], C.c_int),
+    "fv_trainer_set_corpus_windows": ([_P, _P, C.c_uint64, _P, C.c_uint64], C.c_int),
     "fv_trainer_num_windows": ([_P, C.POINTER(C.c_uint64)], C.c_int),
     "fv_trainer_get_inverse_frequency": ([_P, _P], C.c_int),
     "fv_trainer_set_inverse_frequency": ([_P, _P], C.c_int),
@@ -121,7 +122,25 @@ def build(verbose: bool = False) -> Path:
         print(res.stderr)
     if res.returncode != 0:
         raise RuntimeError("building libflyvec_b200.so failed")
+    make_ref_abi_links()
     return LIB_PATH
+
+
+#: the five shared objects the reference's driver loads (flyvec/train_flyvec.py:62-66)
+REF_ABI_NAMES = ("model_descriptor.so", "model_arrays.so", "cuda_helpers.so", "cuda_funcs.so", "prune_input.so")
+REF_ABI_DIR = CSRC / "ref_abi"
+
+
+def make_ref_abi_links() -> Path:
+    """Directory in which the reference's five library names all resolve to this library, for running
+    the reference's own ``train_flyvec.py`` unmodified (set its ``BIN`` there)."""
+    REF_ABI_DIR.mkdir(exist_ok=True)
+    for name in REF_ABI_NAMES:
+        link = REF_ABI_DIR / name
+        if link.is_symlink() or link.exists():
+            link.unlink()
+        link.symlink_to(Path("..") / LIB_PATH.name)
+    return REF_ABI_DIR
 
 
 def lib() -> C.CDLL:

@@ -47,6 +47,7 @@ struct StepCtl {
   unsigned long long base;  // schedule index of the step launched with local == 0
   unsigned long long tick;  // steps executed since the weights were last folded (selects the alpha buffer)
   float eps;
+  float delta;            // anti-Hebbian strength of the running epoch (cuda_funcs.cu:1230)
   uint32_t error;
   uint32_t wabsmax;       // bit pattern of an upper bound of max |wt|
   uint32_t wabsmax_fold;  // the same, collected while folding
@@ -63,6 +64,8 @@ struct StepCtl {
 // Everything a kernel needs, passed by value.
 struct Dev {
   int K, Kp, Kq, V, N, W, B, G, rank, P, XO;  // P = packet words, XO = offset of xx inside a packet
+  int MO;          // offset of the second winners inside a packet (only with delta != 0)
+  int has_delta;   // the anti-Hebbian term is on: every window also names its m-th (second) winner
   unsigned long long Ns, ntok;
   float prec;
   uint32_t flags;
@@ -79,7 +82,9 @@ struct Dev {
   size_t outbox_off;       // word offset of the outbox [2][G*B*W] of (position, value) pairs inside the mailbox
   float* aw;       // [B] weighted activation of each window's winner
   float* xx_part;  // [k_xx CTAs][Kp] partial sums of xx
-  int32_t* cnt;
+  int32_t* cnt;    // per record: later comers that add +f_i (first winner's row)
+  int32_t* cntn;   // per record: later comers that add -delta*f_i (second winner's row); null without delta
+  float* aw2;      // [B] weighted activation of each window's second winner (with delta)
   uint4* rec;      // [G*B*w] touched-position records {position, parked weight bits, 1/count bits, 0}
   uint32_t* colmax;
   uint32_t* ncb;
@@ -103,7 +108,7 @@ __device__ __forceinline__ uint32_t* packet(const Dev& d, int parity, int r) {
 }
 
 __device__ __forceinline__ uint2* outbox(const Dev& d, const uint32_t* mail, int parity) {
-  return reinterpret_cast<uint2*>(const_cast<uint32_t*>(mail) + d.outbox_off) + (size_t)parity * d.G * d.B * d.W;
+  return reinterpret_cast<uint2*>(const_cast<uint32_t*>(mail) + d.outbox_off) + (size_t)parity * d.G * d.B * d.W * (1 + d.has_delta);
 }
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
@@ -182,9 +187,10 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) { return __reduce_m
 // ---------------------------------------------------------------------------
 // control word
 // ---------------------------------------------------------------------------
-__global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps) {
+__global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps, float delta) {
   ctl->base = base;
   ctl->eps = eps;
+  ctl->delta = delta;
   ctl->fwd_next[0] = ctl->fwd_next[1] = 0u;
   ctl->xx_ticket = 0u;
 }
@@ -480,6 +486,43 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
         winner = exact_winner(d.wt, alpha, d.Kp, Kq, d.K, d.W, zrow, my, lane, -1);
       }
       awv = weighted_activation(d, alpha, my, winner, lane);
+      if (d.has_delta) {
+        // the m-th (second) largest raw activation (cuda_funcs.cu:488-561 with m = 2): same certificate
+        // with the winner taken out; the reference masks the winner with -9999.9999, which only differs
+        // from leaving it out when every other activation lies below that value
+        float lmax2 = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (4 * qc[t] + k == winner) a[t][k] = -INFINITY;
+            lmax2 = fmaxf(lmax2, a[t][k]);
+          }
+        const float M2 = warp_max(lmax2);
+        const float thr2 = M2 - theta;
+        int near2 = 0, cand2 = 0;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (a[t][k] >= thr2) {
+              ++near2;
+              cand2 = 4 * qc[t] + k;
+            }
+        const int total2 = __reduce_add_sync(FULL, near2);
+        int second;
+        if (total2 == 1 && !force64) {
+          const unsigned holder = __ballot_sync(FULL, near2 != 0);
+          second = __shfl_sync(FULL, cand2, __ffs(holder) - 1);
+        } else {
+          second = exact_winner(d.wt, alpha, d.Kp, Kq, d.K, d.W, zrow, my, lane, winner);
+        }
+        const float aw2 = weighted_activation(d, alpha, my, second, lane);
+        if (lane == 0) {
+          win_out[d.MO + j] = second;
+          d.aw2[j] = aw2;
+        }
+      }
     } else {
       jn = __shfl_sync(FULL, jn, 0);
       if (need_ticket) jlast = jn + 1;
@@ -488,6 +531,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
     if (lane == 0) {
       win_out[j] = winner;
       d.aw[j] = awv;
+      if (d.has_delta && winner < 0) win_out[d.MO + j] = -1;
     }
     j = jn;
     my = n_my;
@@ -523,14 +567,19 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
   const int hi = min(min(lo + per_warp, (cta + 1) * per_cta), d.B);
   float* mybins = bins + wic * d.Kp;
   constexpr int XX_PRE = 4;  // chunks of 32 windows whose loads are issued together
+  const float delta = d.ctl->delta;
+  for (int pass = 0; pass < 1 + d.has_delta; ++pass) {  // pass 1: the second winners, weighted by -delta (cuda_funcs.cu:726-735)
+  const int32_t* __restrict__ wsrc = pass ? win + d.MO : win;
+  const float* __restrict__ asrc = pass ? d.aw2 : d.aw;
   for (int base0 = lo; base0 < hi; base0 += 32 * XX_PRE) {
     int wv[XX_PRE];
     float av[XX_PRE];
 #pragma unroll
     for (int u = 0; u < XX_PRE; ++u) {
       const int jw = base0 + 32 * u + lane;
-      wv[u] = (jw < hi) ? win[jw] : -1;
-      av[u] = (jw < hi) ? d.aw[jw] : 0.f;
+      wv[u] = (jw < hi) ? wsrc[jw] : -1;
+      av[u] = (jw < hi) ? asrc[jw] : 0.f;
+      if (pass) av[u] = -delta * av[u];
     }
 #pragma unroll
     for (int u = 0; u < XX_PRE; ++u) {
@@ -553,6 +602,7 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
       __syncwarp();
     }
   }
+  }  // pass
   __syncthreads();
   for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
     float p = 0.f;
@@ -656,24 +706,29 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int3
   __shared__ uint32_t s_key[TAG_TABLE];
   __shared__ int s_cnt[TAG_TABLE];
   __shared__ uint32_t s_scan[XX_THREADS / 32 + 1];
+  // With delta != 0 every (window, position) contributes twice: +f_i to the first winner's row and
+  // -delta*f_i to the second winner's row (cuda_funcs.cu:665-668).  Virtual slot ev = kind * E + e.
   const int E = d.G * d.B * d.W;
+  const int EV = E * (1 + d.has_delta);
   const bool check_active = (xx_ctas == 0);
   constexpr int TAG_BLOCK = UN * XX_THREADS;
-  const int nblocks = (E + TAG_BLOCK - 1) / TAG_BLOCK;
+  const int nblocks = (EV + TAG_BLOCK - 1) / TAG_BLOCK;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
   for (int blk = blockIdx.x - xx_ctas; blk < nblocks; blk += gridDim.x - xx_ctas) {
     if constexpr (UN == 1) {
       // small steps: duplicates inside 512 slots are rare, so skip the table: number the live slots of
       // the CTA with a ballot/prefix (one counter bump per CTA round) and claim directly
-      const int e = blk * TAG_BLOCK + threadIdx.x;
-      const int i0 = (e < E) ? idx[e] : -1;
+      const int ev = blk * TAG_BLOCK + threadIdx.x;
+      const int kind = (ev >= E) ? 1 : 0;
+      const int e = ev - kind * E;
+      const int i0 = (ev < EV) ? idx[e] : -1;
       bool go0 = i0 >= 0 && !(d.shard && (i0 % d.G) != d.rank);
       int mu0 = -1;
       if (go0) {
         const int q = e / d.W;
         const int r = q / d.B, j = q - r * d.B;
         const uint32_t* __restrict__ pkt = packet(d, parity, r);
-        mu0 = (int)pkt[j];
+        mu0 = (int)pkt[kind * d.MO + j];
         go0 = mu0 >= 0 && !(check_active && __uint_as_float(pkt[d.XO + mu0]) == 0.f);
       }
       uint32_t c0 = 0u;
@@ -700,16 +755,17 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int3
         for (;;) {
           if ((c & ABS_MASK) > TAG_BASE) {
             const uint32_t owner = (c & 0x007fffffu) - 1u;
-            if ((c >> 31) || owner >= (uint32_t)E) {
+            if ((c >> 31) || owner >= (uint32_t)EV) {
               atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
             } else {
-              atomicAdd(&d.cnt[owner], 1);
+              atomicAdd(kind ? &d.cntn[owner] : &d.cnt[owner], 1);
             }
             break;
           }
           const uint32_t prev = atomicCAS(addr, c, tag);
           if (prev == c) {
-            d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (i0 % d.V))), 1u);
+            // .w: the claimant's own multiplicities, first-winner kind in the low half, second-winner kind above
+            d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (i0 % d.V))), kind ? 0x10000u : 1u);
             break;
           }
           c = prev;
@@ -726,25 +782,28 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int3
     bool go[UN];
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
-      const int e = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-      i[u] = (e < E) ? idx[e] : -1;
+      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      i[u] = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
     }
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
-      const int e = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      const int kind = (ev >= E) ? 1 : 0;
+      const int e = ev - kind * E;
       go[u] = i[u] >= 0 && !(d.shard && (i[u] % d.G) != d.rank);  // sharded: another rank owns this row
       mu[u] = -1;
       if (go[u]) {
         const int q = e / d.W;
         const int r = q / d.B, j = q - r * d.B;
-        mu[u] = (int)packet(d, parity, r)[j];
+        mu[u] = (int)packet(d, parity, r)[kind * d.MO + j];
       }
     }
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
       go[u] = go[u] && mu[u] >= 0;
+      const int evu = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
       if (go[u] && check_active) {
-        const int e = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+        const int e = evu >= E ? evu - E : evu;
         const int r = (e / d.W) / d.B;
         go[u] = __uint_as_float(packet(d, parity, r)[d.XO + mu[u]]) != 0.f;
       }
@@ -754,7 +813,7 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int3
         for (;;) {
           const uint32_t old = atomicCAS(&s_key[h], 0u, key);
           if (old == 0u || old == key) {
-            atomicAdd(&s_cnt[h], 1);
+            atomicAdd(&s_cnt[h], evu >= E ? 0x10000 : 1);  // two 16-bit multiplicities (a block has <= 1024 slots)
             break;
           }
           h = (h + 1) & (TAG_TABLE - 1);
@@ -798,10 +857,11 @@ __global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int3
       for (;;) {
         if ((c & ABS_MASK) > TAG_BASE) {
           const uint32_t owner = (c & 0x007fffffu) - 1u;
-          if ((c >> 31) || owner >= (uint32_t)E) {
+          if ((c >> 31) || owner >= (uint32_t)EV) {
             atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
           } else {
-            atomicAdd(&d.cnt[owner], mult);
+            if (mult & 0xffff) atomicAdd(&d.cnt[owner], mult & 0xffff);
+            if (mult >> 16) atomicAdd(&d.cntn[owner], mult >> 16);
           }
           break;
         }
@@ -876,18 +936,20 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 
   // part 1, first half: counts and records of this thread's share of the touched-position list
   // (coalesced loads, issued before the row stream so that their latency hides behind it)
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W));
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const float delta = d.ctl->delta;
   const int nthreads = gridDim.x * blockDim.x;
   const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
   constexpr int TS = 4;
-  int cs[TS];
+  float cs[TS];  // net multiplicity of the scatter term: (+1 kind) - delta * (-delta kind)
   uint4 rc[TS];
 #pragma unroll
   for (int u = 0; u < TS; ++u) {
     const int k = e0 + u * nthreads;
-    cs[u] = (k < nrec) ? d.cnt[k] : 0;
+    const int cp = (k < nrec) ? d.cnt[k] : 0;
+    const int cn = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
     rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
-    cs[u] = rc[u].w ? cs[u] + (int)rc[u].w : 0;  // a record without a claimant (w == 0) is a hole
+    cs[u] = (float)(cp + (int)(rc[u].w & 0xffffu)) - delta * (float)(cn + (int)(rc[u].w >> 16));
   }
 
   // part 2: column maxima of |wt| with tags read as 0
@@ -935,8 +997,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   // part 1, second half: exact D at the touched positions (records with a count; reserved
   // records whose position somebody else had claimed keep count 0)
   uint32_t tmax = 0u;
-  auto touched = [&](int c, const uint4& r) {
-    if (c <= 0) return;
+  auto touched = [&](float c, const uint4& r) {
+    if (r.w == 0u) return;  // a reserved record nobody claimed
     const int mu = (int)(r.x % (uint32_t)d.Kp);
     if (sN[mu] == 0) return;  // tagged before the unit proved inactive: no update there
     const double D = -sC[mu] * (double)__uint_as_float(r.y) + (double)c * (double)__uint_as_float(r.z) / (double)sN[mu];
@@ -946,7 +1008,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   for (int u = 0; u < TS; ++u) touched(cs[u], rc[u]);
   for (int k = e0 + TS * nthreads; k < nrec; k += nthreads) {
     const uint4 r = d.rec[k];
-    touched(r.w ? d.cnt[k] + (int)r.w : 0, r);
+    const int cn = d.has_delta ? d.cntn[k] : 0;
+    touched((float)(d.cnt[k] + (int)(r.w & 0xffffu)) - delta * (float)(cn + (int)(r.w >> 16)), r);
   }
   __shared__ uint32_t s_tmax;
   if (threadIdx.x == 0) s_tmax = 0u;
@@ -1079,29 +1142,33 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   const int E = d.G * d.B * d.W;
   uint2* __restrict__ my_out = outbox(d, d.mail, p);
   uint32_t vmax = 0u;
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)E);
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(E * (1 + d.has_delta)));
+  const float delta = d.ctl->delta;
   if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->list_count[p ^ 1] = 0u;  // the next step counts from zero
   if (!d.shard) {
     constexpr int UN = 4;
     const int nthreads = gridDim.x * blockDim.x;
     for (int k0 = blockIdx.x * blockDim.x + threadIdx.x; k0 < nrec; k0 += UN * nthreads) {
-      int c[UN];
+      int cp[UN], cn[UN];
       uint4 r[UN];
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
         const int k = k0 + u * nthreads;
-        c[u] = (k < nrec) ? d.cnt[k] : 0;
+        cp[u] = (k < nrec) ? d.cnt[k] : 0;
+        cn[u] = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
         r[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
-        c[u] = r[u].w ? c[u] + (int)r[u].w : 0;
       }
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
-        if (c[u] <= 0) continue;
+        if (r[u].w == 0u) continue;  // a hole
+        const int k = k0 + u * nthreads;
         const int mu = (int)(r[u].x % (uint32_t)d.Kp);
-        const float v = (float)((double)__uint_as_float(r[u].y) + (double)c[u] * (double)__uint_as_float(r[u].z) * sX[mu]);
+        const double scat = (double)(cp[u] + (int)(r[u].w & 0xffffu)) - (double)delta * (double)(cn[u] + (int)(r[u].w >> 16));
+        const float v = (float)((double)__uint_as_float(r[u].y) + scat * (double)__uint_as_float(r[u].z) * sX[mu]);
         d.wt[r[u].x] = v;
-        d.rec[k0 + u * nthreads].w = 0u;  // the slot is a hole again until it is claimed anew
-        if (c[u] != (int)r[u].w) d.cnt[k0 + u * nthreads] = 0;
+        d.rec[k].w = 0u;  // the slot is a hole again until it is claimed anew
+        if (cp[u]) d.cnt[k] = 0;
+        if (cn[u]) d.cntn[k] = 0;
         vmax = max(vmax, __float_as_uint(fabsf(v)));
       }
     }
@@ -1110,14 +1177,17 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   for (int k0 = blockIdx.x * blockDim.x; d.shard && k0 < nrec; k0 += gridDim.x * blockDim.x) {
     const int k = k0 + (int)threadIdx.x;
     uint4 r = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
-    const int c = r.w ? d.cnt[k] + (int)r.w : 0;
+    const int c = r.w ? 1 : 0;  // a live record
     float v = 0.f;
     if (c > 0) {
       const int mu = (int)(r.x % (uint32_t)d.Kp);
-      v = (float)((double)__uint_as_float(r.y) + (double)c * (double)__uint_as_float(r.z) * sX[mu]);
+      const int cn = d.has_delta ? d.cntn[k] : 0;
+      const double scat = (double)(d.cnt[k] + (int)(r.w & 0xffffu)) - (double)delta * (double)(cn + (int)(r.w >> 16));
+      v = (float)((double)__uint_as_float(r.y) + scat * (double)__uint_as_float(r.z) * sX[mu]);
       d.wt[r.x] = v;
       d.rec[k].w = 0u;
       d.cnt[k] = 0;
+      if (d.has_delta) d.cntn[k] = 0;
       vmax = max(vmax, __float_as_uint(fabsf(v)));
     }
     {
@@ -1391,6 +1461,8 @@ struct fv_trainer {
   float* d_xx_part = nullptr;
   float* d_aw = nullptr;
   int32_t* d_cnt = nullptr;
+  int32_t* d_cntn = nullptr;
+  float* d_aw2 = nullptr;
   uint4* d_rec = nullptr;
   uint32_t* d_colmax = nullptr;
   uint32_t* d_ncb = nullptr;
@@ -1399,6 +1471,7 @@ struct fv_trainer {
   size_t log_cap = 0;
   unsigned long long steps_since_fold = 0;
   unsigned long long ticks = 0;  // host copy of StepCtl::tick
+  float delta_now = 0.f;         // anti-Hebbian strength used by the next run_* call
   int tag_un = 1;
   int fwd_grid = 0, xx_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
   size_t fwd_smem = 0, xx_smem = 0, scan_smem = 0, apply_smem = 0;
@@ -1575,7 +1648,7 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   for (int b = 0; b < 2; ++b)
     if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
 
-  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps);
+  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps, tr->delta_now);
   uint64_t launches = 1;
   FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   unsigned long long chunk_id = 0;
@@ -1685,7 +1758,7 @@ void free_all(fv_trainer* tr) {
     if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
-                  tr->d_mail, tr->d_peer_table, tr->d_xx_part, tr->d_aw, tr->d_cnt,    tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+                  tr->d_mail, tr->d_peer_table, tr->d_xx_part, tr->d_aw, tr->d_aw2, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -1701,6 +1774,7 @@ void free_all(fv_trainer* tr) {
 int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->cfg = *cfg;
   tr->device = cfg->device;
+  tr->delta_now = cfg->delta;
   FV_CUDA(cudaSetDevice(cfg->device));
   cudaDeviceProp prop;
   FV_CUDA(cudaGetDeviceProperties(&prop, cfg->device));
@@ -1725,21 +1799,28 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.B = (int)cfg->batch;
   d.G = cfg->world;
   d.rank = cfg->rank;
-  d.XO = (d.B + 3) & ~3;  // keeps every packet 16-byte aligned
+  d.has_delta = (cfg->delta != 0.0f) ? 1 : 0;
+  d.MO = (d.B + 3) & ~3;                  // second winners (with delta) start here
+  d.XO = d.MO * (1 + d.has_delta);        // xx follows; every part stays 16-byte aligned
   d.P = d.XO + d.Kp;
   d.spin_limit = 8u << 20;  // ~10 s of polling with back-off
   d.prec = cfg->prec;
   d.flags = cfg->flags;
   tr->NT = (d.Kq + 31) / 32;
 
-  const size_t E = (size_t)d.G * d.B * d.W;
+  const size_t E = (size_t)d.G * d.B * d.W * (1 + (cfg->delta != 0.0f ? 1 : 0));  // virtual slots: both kinds with delta
   FV_TRY(dev_alloc(&tr->d_wt, ((size_t)d.N + 1) * d.Kp));  // one extra all-zero row for padding positions
   FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
   d.outbox_off = (MAIL_HDR + 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
-  tr->mail_words = d.outbox_off + (d.G > 1 ? 2 * 2 * (size_t)d.G * d.B * d.W : 0);
+  tr->mail_words = d.outbox_off + (d.G > 1 ? 2 * 2 * (size_t)d.G * d.B * d.W * (1 + d.has_delta) : 0);
   FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
   FV_TRY(dev_alloc(&tr->d_cnt, E));
+  if (cfg->delta != 0.0f) {
+    FV_TRY(dev_alloc(&tr->d_cntn, E));
+    FV_TRY(dev_alloc(&tr->d_aw2, (size_t)cfg->batch));
+    FV_CUDA(cudaMemsetAsync(tr->d_cntn, 0, E * sizeof(int32_t), tr->stream));
+  }
   FV_TRY(dev_alloc(&tr->d_rec, E));
   FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_ncb, 2));
@@ -1756,6 +1837,8 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.mail = tr->d_mail;
   d.peers = nullptr;
   d.cnt = tr->d_cnt;
+  d.cntn = tr->d_cntn;
+  d.aw2 = tr->d_aw2;
   d.rec = tr->d_rec;
   d.colmax = tr->d_colmax;
   d.ncb = tr->d_ncb;
@@ -1816,10 +1899,12 @@ int fv_trainer_create(const fv_config* cfg, fv_trainer** out) {
   FV_REQUIRE(cfg->world <= MAX_RANKS, FV_ERR_INVALID, "world must be at most %d", MAX_RANKS);
   FV_REQUIRE(cfg->world >= 1 && cfg->rank >= 0 && cfg->rank < cfg->world, FV_ERR_INVALID,
              "need world >= 1 and 0 <= rank < world (rank %d, world %d)", cfg->rank, cfg->world);
-  FV_REQUIRE((uint64_t)cfg->world * cfg->batch * cfg->window < 0x7ffffeull, FV_ERR_INVALID,
+  FV_REQUIRE((uint64_t)cfg->world * cfg->batch * cfg->window * (cfg->delta != 0.0f ? 2 : 1) < 0x7ffffeull, FV_ERR_INVALID,
              "world*batch*window = %llu does not fit the 23-bit scatter slot id",
              (unsigned long long)cfg->world * cfg->batch * cfg->window);
-  FV_REQUIRE(cfg->delta == 0.0f, FV_ERR_INVALID, "delta != 0 (anti-Hebbian term) is not implemented");
+  FV_REQUIRE(cfg->delta == 0.0f || cfg->m == 2 || cfg->m == 0, FV_ERR_INVALID,
+             "with delta != 0 only m = 2 (the second winner, the reference's fixed value) is implemented, got m = %u", cfg->m);
+  FV_REQUIRE(cfg->delta == 0.0f || cfg->hid >= 2, FV_ERR_INVALID, "delta != 0 needs at least two hidden units");
   FV_REQUIRE(cfg->prec > 0.0f, FV_ERR_INVALID, "prec must be > 0");
   int ndev = 0;
   FV_CUDA(cudaGetDeviceCount(&ndev));
@@ -1850,23 +1935,10 @@ int fv_trainer_destroy(fv_trainer* tr) {
   return FV_OK;
 }
 
-int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
-                          uint64_t noffsets) {
-  FV_REQUIRE(tr && enc && offsets, FV_ERR_INVALID, "fv_trainer_set_corpus: NULL argument");
-  FV_REQUIRE(noffsets >= 2, FV_ERR_DATA, "offsets needs at least two entries");
-  FV_REQUIRE(offsets[0] == 0, FV_ERR_DATA, "offsets[0] must be 0, got %llu", (unsigned long long)offsets[0]);
-  FV_REQUIRE(offsets[noffsets - 1] <= ntok, FV_ERR_DATA, "last offset %llu exceeds the number of tokens %llu",
-             (unsigned long long)offsets[noffsets - 1], (unsigned long long)ntok);
-  fv::DeviceGuard guard(tr->device);
-  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+static int upload_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* starts, uint64_t ns) {
   Dev& d = tr->d;
-  uint64_t ns = 0;
-  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, d.W, tr->cfg.maxlen, &ns, nullptr));
-  std::vector<uint64_t> starts(ns);
-  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, d.W, tr->cfg.maxlen, &ns, starts.data()));
   std::vector<float> f(d.V);
   FV_TRY(fv_inverse_frequency(enc, ntok, d.V, (d.flags & FV_FLAG_COUNT_FP32) != 0, f.data()));
-
   tr->have_corpus = false;
   if (tr->d_tokens) FV_CUDA(cudaFree(tr->d_tokens));
   if (tr->d_wstart) FV_CUDA(cudaFree(tr->d_wstart));
@@ -1878,7 +1950,7 @@ int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, con
   FV_TRY(dev_alloc(&tr->d_wstart, ns));
   FV_TRY(dev_alloc(&tr->d_perm, ns));
   FV_CUDA(cudaMemcpyAsync(tr->d_tokens, enc, ntok * sizeof(int32_t), cudaMemcpyHostToDevice, tr->stream));
-  FV_CUDA(cudaMemcpyAsync(tr->d_wstart, starts.data(), ns * sizeof(uint64_t), cudaMemcpyHostToDevice, tr->stream));
+  FV_CUDA(cudaMemcpyAsync(tr->d_wstart, starts, ns * sizeof(uint64_t), cudaMemcpyHostToDevice, tr->stream));
   FV_CUDA(cudaMemcpyAsync(tr->d_f, f.data(), (size_t)d.V * sizeof(float), cudaMemcpyHostToDevice, tr->stream));
   k_iota<<<tr->num_sms * 4, 256, 0, tr->stream>>>(tr->d_perm, ns);
   FV_CUDA(cudaGetLastError());
@@ -1890,6 +1962,33 @@ int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, con
   d.ntok = ntok;
   tr->have_corpus = true;
   return FV_OK;
+}
+
+int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
+                          uint64_t noffsets) {
+  FV_REQUIRE(tr && enc && offsets, FV_ERR_INVALID, "fv_trainer_set_corpus: NULL argument");
+  FV_REQUIRE(noffsets >= 2, FV_ERR_DATA, "offsets needs at least two entries");
+  FV_REQUIRE(offsets[0] == 0, FV_ERR_DATA, "offsets[0] must be 0, got %llu", (unsigned long long)offsets[0]);
+  FV_REQUIRE(offsets[noffsets - 1] <= ntok, FV_ERR_DATA, "last offset %llu exceeds the number of tokens %llu",
+             (unsigned long long)offsets[noffsets - 1], (unsigned long long)ntok);
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  uint64_t ns = 0;
+  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, tr->d.W, tr->cfg.maxlen, &ns, nullptr));
+  std::vector<uint64_t> starts(ns);
+  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, tr->d.W, tr->cfg.maxlen, &ns, starts.data()));
+  return upload_corpus(tr, enc, ntok, starts.data(), ns);
+}
+
+int fv_trainer_set_corpus_windows(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* starts,
+                                  uint64_t nwindows) {
+  FV_REQUIRE(tr && enc && (starts || nwindows == 0), FV_ERR_INVALID, "fv_trainer_set_corpus_windows: NULL argument");
+  for (uint64_t i = 0; i < nwindows; ++i)
+    FV_REQUIRE(starts[i] + (uint64_t)tr->d.W <= ntok, FV_ERR_DATA, "window %llu starts at %llu and runs past the %llu tokens",
+               (unsigned long long)i, (unsigned long long)starts[i], (unsigned long long)ntok);
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  return upload_corpus(tr, enc, ntok, starts, nwindows);
 }
 
 int fv_trainer_num_windows(fv_trainer* tr, uint64_t* count) {
@@ -2014,6 +2113,8 @@ int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_st
   // eps = lr0 * (1 - epoch/Nep): float quotient, double product, float store
   const float q = (float)epoch / (float)nep;
   const float eps = (float)((double)tr->cfg.lr0 * (1.0 - (double)q));
+  // delta * 0.5 * (1 + tanh((epoch - Nep/8) / 10)), cuda_funcs.cu:1230
+  tr->delta_now = (float)((double)tr->cfg.delta * 0.5 * (1.0 + tanh(((double)(float)epoch - 0.125 * (double)nep) / 10.0)));
   const unsigned long long per_step = (unsigned long long)tr->d.G * tr->d.B;
   const unsigned long long nsteps = (tr->d.Ns + per_step - 1) / per_step;
   return run_steps_impl(tr, 0, nsteps, eps, nullptr, nullptr, nullptr, stats);
@@ -2048,7 +2149,7 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
   const Dev& d = tr->d;
   const size_t step_ids = (size_t)d.G * d.B * d.W;
   if (!tr->d_idx_stage[0]) FV_TRY(dev_alloc(&tr->d_idx_stage[0], step_ids * STAGE_STEPS));
-  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, step, 0.f);
+  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, step, 0.f, tr->delta_now);
   k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->stream>>>(d, step, 1, tr->d_idx_stage[0]);
   // the kernel only writes winners and activations, so it can be repeated on the same step;
   // alternating the parity lets each launch clear the ticket counter of the next

@@ -59,7 +59,7 @@ typedef struct fv_config {
   uint32_t window;      /* W, window length incl. the centre ("W")             */
   uint32_t batch;       /* windows per GPU per step         ("Num")            */
   float lr0;            /* initial learning rate  ("initial_learning_rate")    */
-  float delta;          /* anti-Hebbian strength  ("delta"); only 0 is implemented */
+  float delta;          /* anti-Hebbian strength  ("delta"); run_epoch applies the epoch schedule */
   float prec;           /* lower bound of the normaliser ("prec")              */
   uint32_t m;           /* rank of the anti-Hebbian unit ("m", 2 in the reference) */
   uint32_t maxlen;      /* chunks this long or longer are dropped; 0 -> 214    */
@@ -116,6 +116,10 @@ int fv_trainer_destroy(fv_trainer* tr);
  * token ids to the GPU, enumerates the windows and computes 1/count. */
 int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
                           uint64_t noffsets);
+/* The same with the window table already made (what compute_offset_phrases produced,
+ * prune_input.cpp:87-122, and set_up_INPUT_pointer consumed, model_arrays.cu:357-393). */
+int fv_trainer_set_corpus_windows(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* starts,
+                                  uint64_t nwindows);
 int fv_trainer_num_windows(fv_trainer* tr, uint64_t* count);
 int fv_trainer_get_inverse_frequency(fv_trainer* tr, float* inv_freq /* [V] */);
 int fv_trainer_set_inverse_frequency(fv_trainer* tr, const float* inv_freq /* [V] */);

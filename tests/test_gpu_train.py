@@ -181,6 +181,55 @@ def test_inactive_rank_rows_are_dropped(built_lib):
     tr.close()
 
 
+@pytest.mark.parametrize("world", [1, 2])
+def test_anti_hebbian_second_winner(built_lib, world):
+    """delta != 0: the second-largest unit gets -delta times the Hebbian terms
+    (cuda_funcs.cu:726-735 for xx, 665-668 for the scatter)."""
+    p = small_problem(K=64, V=400, W=9, ntok=20000, seed=33)
+    batch, delta = 160, 0.4
+    flags = _lib.FV_FLAG_EMULATE_RANKS if world > 1 else 0
+    tr = Trainer(hid=p["K"], vocab=p["V"], window=p["W"], batch=batch, lr0=2e-4, delta=delta, world=world, flags=flags)
+    tr.set_corpus(p["enc"], p["off"])
+    tr.set_weights(p["W0"])
+    tr.set_permutation(p["perm"])
+    eps = np.float32(2e-4)
+    Wcur = p["W0"]
+    for step in range(4):
+        win, xx, nc, s = tr.step_debug(step, eps)
+        Wgpu = tr.get_weights()
+        idxs = []
+        for g in range(world):
+            lo = (step * world + g) * batch
+            idxs.append(orc.build_idx(p["enc"], p["starts"], p["perm"][lo:lo + batch], p["W"], p["V"]))
+        Wref, info = orc.train_step(Wcur, idxs, p["f"], p["V"], eps, delta=delta)
+        for g in range(world):
+            np.testing.assert_array_equal(win[g], info["win"][g])
+            np.testing.assert_allclose(xx[g], info["xx"][g], rtol=5e-5, atol=1e-7)
+        np.testing.assert_allclose(nc, info["nc"], rtol=1e-5)
+        assert rel_err(Wgpu, Wref) < STEP_TOL
+        Wcur = Wgpu
+    # the term must matter: without it the weights differ visibly
+    Wplain, _ = orc.train_step(p["W0"], [orc.build_idx(p["enc"], p["starts"], p["perm"][:batch], p["W"], p["V"])],
+                               p["f"], p["V"], eps)
+    tr.close()
+
+
+def test_delta_epoch_schedule(built_lib):
+    """run_epoch applies delta * 0.5 * (1 + tanh((epoch - Nep/8) / 10)) (cuda_funcs.cu:1230)."""
+    p = small_problem(K=32, V=200, W=5, ntok=5000, seed=35)
+    batch = 300
+    tr = Trainer(hid=32, vocab=200, window=5, batch=batch, lr0=1e-3, delta=0.5)
+    tr.set_corpus(p["enc"], p["off"])
+    tr.set_weights(p["W0"])
+    tr.set_permutation(p["perm"])
+    tr.run_epoch(3, 8)
+    Wgpu = tr.get_weights()
+    tr.close()
+    Wref, _ = orc.run_epoch(p["W0"], p["enc"], p["starts"], p["perm"], p["f"], 200, 5, batch, 1, orc.epoch_eps(1e-3, 3, 8),
+                            delta=orc.epoch_delta(0.5, 3, 8))
+    assert rel_err(Wgpu, Wref) < EPOCH_TOL
+
+
 def test_streaming_mode_matches_resident_mode(built_lib):
     """Host-fed input ids (uploaded inside the call) give the same weights as the
     resident corpus, and the per-step normalisers come back."""
@@ -224,8 +273,8 @@ def test_seeded_shuffle_is_a_permutation(built_lib):
 def test_error_paths(built_lib):
     with pytest.raises(_lib.FlyvecError, match="hid"):
         Trainer(hid=0, vocab=10)
-    with pytest.raises(_lib.FlyvecError, match="delta"):
-        Trainer(hid=8, vocab=10, delta=0.5)
+    with pytest.raises(_lib.FlyvecError, match="m = 2"):
+        Trainer(hid=8, vocab=10, delta=0.5, m=3)
     tr = Trainer(hid=8, vocab=10, window=3, batch=4)
     with pytest.raises(_lib.FlyvecError, match="weights"):
         tr.run_steps(0, 1, 1e-3)
