@@ -73,6 +73,7 @@ _PROTOTYPES = {
     "fv_trainer_destroy": ([_P], C.c_int),
     "fv_trainer_set_corpus": ([_P, _P, C.c_uint64, _P, C.c_uint64], C.c_int),
     "fv_trainer_set_corpus_windows": ([_P, _P, C.c_uint64, _P, C.c_uint64], C.c_int),
+    "fv_trainer_get_window_starts": ([_P, _P], C.c_int),
     "fv_trainer_num_windows": ([_P, C.POINTER(C.c_uint64)], C.c_int),
     "fv_trainer_get_inverse_frequency": ([_P, _P], C.c_int),
     "fv_trainer_set_inverse_frequency": ([_P, _P], C.c_int),

@@ -171,6 +171,17 @@ class FlyVec:
             out[t] = list(c) if output_list else c
         return out
 
+    def save_simple_word_vectors(self, fname, k: int = 51, exclude_stop_words: bool = False) -> int:
+        """Write the context-independent codes of the whole vocabulary as JSON, ``{token: [0/1, ...]}`` --
+        the shape of the reference's precomputed ``simple-flyvec-embeddings.json`` (README, "Simple word
+        embeddings", hash length 51).  Returns the number of tokens written."""
+        import json
+
+        vecs = self.simple_word_vectors(k=k, exclude_stop_words=exclude_stop_words)
+        with open(fname, "w") as fp:
+            json.dump({t: [int(x) for x in v] for t, v in vecs.items()}, fp)
+        return len(vecs)
+
     # -- batch additions ------------------------------------------------------
     def get_sparse_embeddings(self, ids, hash_length: int = 50, packed: bool = False) -> np.ndarray:
         """Codes for an array of token ids: int8 ``[n][K]`` or bit-packed uint8 ``[n][ceil(K/8)]``."""

@@ -1388,6 +1388,112 @@ __global__ void k_iota(unsigned long long* __restrict__ perm, unsigned long long
 }
 
 // ---------------------------------------------------------------------------
+// Corpus preparation on the GPU (T1: prune_input.cpp:63-122, T2: model_arrays.cu:395-424).
+//   k_chunk_windows   windows per chunk: len - w + 1 when w <= len < maxlen, else 0
+//   k_block_scan      exclusive prefix of those counts, 1024 chunks per CTA (the CTA totals are
+//                     prefixed on the host: a few thousand numbers)
+//   k_fill_starts     one thread per window: binary search for its chunk, start = running sum of
+//                     the chunk lengths before it (= offsets[s] - offsets[0]) + position in the chunk
+//   k_count_tokens    histogram of the token ids: per-CTA shared-memory bins when the vocabulary
+//                     fits, merged with 64-bit atomics; ids >= V raise the device error word
+//   k_inverse_counts  f[v] = (float)(1.0 / count), 0 for unseen ids, counts capped at 2^24 on request
+// ---------------------------------------------------------------------------
+__global__ void k_chunk_windows(const unsigned long long* __restrict__ off, unsigned long long nchunks, unsigned W,
+                                unsigned maxlen, uint32_t* __restrict__ nwin, uint32_t* error) {
+  for (unsigned long long s = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; s < nchunks;
+       s += (unsigned long long)gridDim.x * blockDim.x) {
+    const unsigned long long a = off[s], b = off[s + 1];
+    uint32_t n = 0;
+    if (b < a) {
+      atomicOr(error, FV_DEVERR_WINDOW_RANGE);
+    } else {
+      const unsigned long long len = b - a;
+      if (len >= W && len < maxlen) n = (uint32_t)(len - W + 1);
+    }
+    nwin[s] = n;
+  }
+}
+constexpr int SCAN_BLOCK = 1024;
+__global__ void __launch_bounds__(SCAN_BLOCK) k_block_scan(const uint32_t* __restrict__ nwin, unsigned long long nchunks,
+                                                           const unsigned long long* __restrict__ block_base,
+                                                           unsigned long long* __restrict__ wbase,
+                                                           unsigned long long* __restrict__ block_total) {
+  __shared__ unsigned long long s_w[SCAN_BLOCK / 32];
+  const unsigned long long s = (unsigned long long)blockIdx.x * SCAN_BLOCK + threadIdx.x;
+  const unsigned long long v = (s < nchunks) ? nwin[s] : 0ull;
+  unsigned long long incl = v;
+  const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(FULL, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) s_w[wic] = incl;
+  __syncthreads();
+  if (wic == 0) {
+    unsigned long long t = s_w[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long u = __shfl_up_sync(FULL, t, o);
+      if (lane >= o) t += u;
+    }
+    s_w[lane] = t;  // inclusive prefix of the warp totals
+  }
+  __syncthreads();
+  const unsigned long long before = (wic ? s_w[wic - 1] : 0ull) + incl - v;
+  if (block_base) {
+    if (s < nchunks) wbase[s] = block_base[blockIdx.x] + before;
+  } else if (threadIdx.x == SCAN_BLOCK - 1) {
+    block_total[blockIdx.x] = before + v;
+  }
+}
+__global__ void k_fill_starts(const unsigned long long* __restrict__ off, const unsigned long long* __restrict__ wbase,
+                              unsigned long long nchunks, unsigned long long ns, unsigned long long* __restrict__ starts) {
+  const unsigned long long origin = off[0];
+  for (unsigned long long p = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; p < ns;
+       p += (unsigned long long)gridDim.x * blockDim.x) {
+    // last chunk s with wbase[s] <= p (chunks without windows share their successor's base and are skipped)
+    unsigned long long lo = 0, hi = nchunks;
+    while (hi - lo > 1) {
+      const unsigned long long mid = (lo + hi) >> 1;
+      if (wbase[mid] <= p) lo = mid; else hi = mid;
+    }
+    starts[p] = (off[lo] - origin) + (p - wbase[lo]);
+  }
+}
+__global__ void __launch_bounds__(512) k_count_tokens(const int32_t* __restrict__ tok, unsigned long long n, int V,
+                                                      int use_smem, unsigned long long* __restrict__ counts,
+                                                      uint32_t* error) {
+  extern __shared__ uint32_t s_bins[];
+  if (use_smem) {
+    for (int v = threadIdx.x; v < V; v += blockDim.x) s_bins[v] = 0u;
+    __syncthreads();
+  }
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (unsigned long long)gridDim.x * blockDim.x) {
+    const int t = tok[i];
+    if (t < 0) continue;  // negative ids are padding and do not count (model_arrays.cu:414)
+    if (t >= V) {
+      atomicOr(error, FV_DEVERR_TOKEN_RANGE);
+      continue;
+    }
+    if (use_smem) atomicAdd(&s_bins[t], 1u); else atomicAdd(&counts[t], 1ull);
+  }
+  if (use_smem) {
+    __syncthreads();
+    for (int v = threadIdx.x; v < V; v += blockDim.x)
+      if (s_bins[v]) atomicAdd(&counts[v], (unsigned long long)s_bins[v]);
+  }
+}
+__global__ void k_inverse_counts(const unsigned long long* __restrict__ counts, int V, int saturate, float* __restrict__ f) {
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x) {
+    unsigned long long c = counts[v];
+    if (saturate && c > (1ull << 24)) c = 1ull << 24;  // a float counter stops growing here (model_arrays.cu:413-416)
+    f[v] = c ? (float)(1.0 / (double)c) : 0.f;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // NCCL, bound at run time so that a single-GPU process never needs it.
 // ---------------------------------------------------------------------------
 struct Id128 {
@@ -1935,6 +2041,92 @@ int fv_trainer_destroy(fv_trainer* tr) {
   return FV_OK;
 }
 
+// Tokens and chunk boundaries go up once; window table and 1/count are made on the GPU.
+static int prepare_corpus_on_device(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
+                                    uint64_t noffsets) {
+  Dev& d = tr->d;
+  const unsigned long long nchunks = noffsets - 1;
+  const unsigned maxlen = tr->cfg.maxlen ? tr->cfg.maxlen : 214u;
+  tr->have_corpus = false;
+  if (tr->d_tokens) FV_CUDA(cudaFree(tr->d_tokens));
+  if (tr->d_wstart) FV_CUDA(cudaFree(tr->d_wstart));
+  if (tr->d_perm) FV_CUDA(cudaFree(tr->d_perm));
+  tr->d_tokens = nullptr;
+  tr->d_wstart = nullptr;
+  tr->d_perm = nullptr;
+  unsigned long long *d_off = nullptr, *d_wbase = nullptr, *d_btot = nullptr, *d_counts = nullptr;
+  uint32_t *d_nwin = nullptr, *d_err = nullptr;
+  const unsigned long long nblocks = (nchunks + SCAN_BLOCK - 1) / SCAN_BLOCK;
+  int rc = FV_OK;
+  auto cleanup = [&]() {
+    cudaFree(d_off); cudaFree(d_wbase); cudaFree(d_btot); cudaFree(d_counts); cudaFree(d_nwin); cudaFree(d_err);
+  };
+#define FV_PREP(expr)                                  \
+  do {                                                 \
+    rc = (expr);                                       \
+    if (rc != FV_OK) { cleanup(); return rc; }         \
+  } while (0)
+#define FV_PREP_CUDA(call)                                                                                    \
+  do {                                                                                                        \
+    cudaError_t e_ = (call);                                                                                  \
+    if (e_ != cudaSuccess) {                                                                                  \
+      cleanup();                                                                                              \
+      return fv::fail(FV_ERR_CUDA, "%s:%d: %s failed: %s", __FILE__, __LINE__, #call, cudaGetErrorString(e_)); \
+    }                                                                                                         \
+  } while (0)
+  FV_PREP(dev_alloc(&tr->d_tokens, ntok));
+  FV_PREP(dev_alloc(&d_off, noffsets));
+  FV_PREP(dev_alloc(&d_nwin, nchunks));
+  FV_PREP(dev_alloc(&d_wbase, nchunks + 1));
+  FV_PREP(dev_alloc(&d_btot, 2 * nblocks));
+  FV_PREP(dev_alloc(&d_counts, (size_t)d.V));
+  FV_PREP(dev_alloc(&d_err, 1));
+  FV_PREP_CUDA(cudaMemcpyAsync(tr->d_tokens, enc, ntok * sizeof(int32_t), cudaMemcpyHostToDevice, tr->stream));
+  FV_PREP_CUDA(cudaMemcpyAsync(d_off, offsets, noffsets * sizeof(uint64_t), cudaMemcpyHostToDevice, tr->stream));
+  FV_PREP_CUDA(cudaMemsetAsync(d_counts, 0, (size_t)d.V * sizeof(unsigned long long), tr->stream));
+  FV_PREP_CUDA(cudaMemsetAsync(d_err, 0, sizeof(uint32_t), tr->stream));
+  const int wide = tr->num_sms * 8;
+  k_chunk_windows<<<wide, 256, 0, tr->stream>>>(d_off, nchunks, (unsigned)d.W, maxlen, d_nwin, d_err);
+  k_block_scan<<<(unsigned)nblocks, SCAN_BLOCK, 0, tr->stream>>>(d_nwin, nchunks, nullptr, nullptr, d_btot);
+  std::vector<unsigned long long> btot(nblocks), bbase(nblocks);
+  FV_PREP_CUDA(cudaMemcpyAsync(btot.data(), d_btot, nblocks * sizeof(unsigned long long), cudaMemcpyDeviceToHost, tr->stream));
+  FV_PREP_CUDA(cudaStreamSynchronize(tr->stream));
+  unsigned long long ns = 0;
+  for (unsigned long long b = 0; b < nblocks; ++b) {
+    bbase[b] = ns;
+    ns += btot[b];
+  }
+  FV_PREP_CUDA(cudaMemcpyAsync(d_btot + nblocks, bbase.data(), nblocks * sizeof(unsigned long long), cudaMemcpyHostToDevice, tr->stream));
+  k_block_scan<<<(unsigned)nblocks, SCAN_BLOCK, 0, tr->stream>>>(d_nwin, nchunks, d_btot + nblocks, d_wbase, nullptr);
+  FV_PREP(dev_alloc(&tr->d_wstart, ns));
+  FV_PREP(dev_alloc(&tr->d_perm, ns));
+  if (ns) {
+    k_fill_starts<<<wide, 256, 0, tr->stream>>>(d_off, d_wbase, nchunks, ns, tr->d_wstart);
+    k_iota<<<tr->num_sms * 4, 256, 0, tr->stream>>>(tr->d_perm, ns);
+  }
+  const size_t hist_smem = (size_t)d.V * sizeof(uint32_t);
+  const int use_smem = hist_smem <= 200 * 1024;
+  if (use_smem) FV_PREP_CUDA(cudaFuncSetAttribute(k_count_tokens, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_smem));
+  k_count_tokens<<<tr->num_sms, 512, use_smem ? hist_smem : 0, tr->stream>>>(tr->d_tokens, ntok, d.V, use_smem, d_counts, d_err);
+  k_inverse_counts<<<64, 256, 0, tr->stream>>>(d_counts, d.V, (d.flags & FV_FLAG_COUNT_FP32) != 0, tr->d_f);
+  FV_PREP_CUDA(cudaGetLastError());
+  uint32_t err = 0;
+  FV_PREP_CUDA(cudaMemcpyAsync(&err, d_err, sizeof(err), cudaMemcpyDeviceToHost, tr->stream));
+  FV_PREP_CUDA(cudaStreamSynchronize(tr->stream));
+  cleanup();
+#undef FV_PREP
+#undef FV_PREP_CUDA
+  if (err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "a token id is >= vocab (%d)", d.V);
+  if (err & FV_DEVERR_WINDOW_RANGE) return fv::fail(FV_ERR_DATA, "offsets decrease somewhere: chunk boundaries must not go backwards");
+  d.tokens = tr->d_tokens;
+  d.wstart = tr->d_wstart;
+  d.perm = tr->d_perm;
+  d.Ns = ns;
+  d.ntok = ntok;
+  tr->have_corpus = true;
+  return FV_OK;
+}
+
 static int upload_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* starts, uint64_t ns) {
   Dev& d = tr->d;
   std::vector<float> f(d.V);
@@ -1973,11 +2165,7 @@ int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, con
              (unsigned long long)offsets[noffsets - 1], (unsigned long long)ntok);
   fv::DeviceGuard guard(tr->device);
   FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
-  uint64_t ns = 0;
-  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, tr->d.W, tr->cfg.maxlen, &ns, nullptr));
-  std::vector<uint64_t> starts(ns);
-  FV_TRY(fv_enumerate_windows(offsets, noffsets - 1, tr->d.W, tr->cfg.maxlen, &ns, starts.data()));
-  return upload_corpus(tr, enc, ntok, starts.data(), ns);
+  return prepare_corpus_on_device(tr, enc, ntok, offsets, noffsets);
 }
 
 int fv_trainer_set_corpus_windows(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* starts,
@@ -1989,6 +2177,14 @@ int fv_trainer_set_corpus_windows(fv_trainer* tr, const int32_t* enc, uint64_t n
   fv::DeviceGuard guard(tr->device);
   FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
   return upload_corpus(tr, enc, ntok, starts, nwindows);
+}
+
+int fv_trainer_get_window_starts(fv_trainer* tr, uint64_t* starts) {
+  FV_REQUIRE(tr && starts, FV_ERR_INVALID, "fv_trainer_get_window_starts: NULL argument");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  fv::DeviceGuard guard(tr->device);
+  FV_CUDA(cudaMemcpy(starts, tr->d_wstart, tr->d.Ns * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  return FV_OK;
 }
 
 int fv_trainer_num_windows(fv_trainer* tr, uint64_t* count) {

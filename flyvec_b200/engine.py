@@ -55,6 +55,11 @@ class Trainer:
         check(_lib.lib().fv_trainer_num_windows(self._h, C.byref(n)))
         return n.value
 
+    def window_starts(self) -> np.ndarray:
+        st = np.empty(self.num_windows, np.uint64)
+        check(_lib.lib().fv_trainer_get_window_starts(self._h, ptr(st)))
+        return st
+
     @property
     def steps_per_epoch(self) -> int:
         per = self.G * self.B

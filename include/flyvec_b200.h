@@ -113,7 +113,7 @@ int fv_trainer_destroy(fv_trainer* tr);
 
 /* Stands in for the pinned INPUT buffer, set_up_INPUT_pointer and
  * compute_inverse_word_frequency (train_flyvec.py:155-185, 223-229): copies the
- * token ids to the GPU, enumerates the windows and computes 1/count. */
+ * token ids and chunk boundaries to the GPU and builds the window table and 1/count there. */
 int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
                           uint64_t noffsets);
 /* The same with the window table already made (what compute_offset_phrases produced,
@@ -121,6 +121,8 @@ int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, con
 int fv_trainer_set_corpus_windows(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* starts,
                                   uint64_t nwindows);
 int fv_trainer_num_windows(fv_trainer* tr, uint64_t* count);
+/* The window table as built on the GPU (what compute_offset_phrases writes, prune_input.cpp:87-122). */
+int fv_trainer_get_window_starts(fv_trainer* tr, uint64_t* starts /* [num_windows] */);
 int fv_trainer_get_inverse_frequency(fv_trainer* tr, float* inv_freq /* [V] */);
 int fv_trainer_set_inverse_frequency(fv_trainer* tr, const float* inv_freq /* [V] */);
 

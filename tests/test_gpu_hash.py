@@ -130,3 +130,9 @@ def test_flyvec_api_matches_reference_shapes(built_lib, tmp_path):
     np.testing.assert_array_equal(m.get_dense_embedding("w7")["embedding"], syn[:, V + 7])
     vecs = m.simple_word_vectors(k=10)
     assert len(vecs) == V and vecs["w3"].sum() == 10
+    import json
+
+    assert m.save_simple_word_vectors(tmp_path / "simple.json", k=12) == V
+    dumped = json.loads((tmp_path / "simple.json").read_text())
+    assert sorted(dumped) == sorted(words) and sum(dumped["w3"]) == 12 and len(dumped["w3"]) == K
+    assert dumped["<UNK>"] == [0] * K

@@ -32,6 +32,49 @@ def test_corpus_tables_match_oracle(built_lib):
     np.testing.assert_array_equal(tr.inverse_frequency(), p["f"])
     np.testing.assert_array_equal(tr.get_permutation(), p["perm"])
     np.testing.assert_array_equal(tr.get_weights(), p["W0"])
+    np.testing.assert_array_equal(tr.window_starts(), p["starts"])
+    tr.close()
+
+
+@pytest.mark.parametrize("V,W,nchunks,maxlen", [(300, 11, 5000, 0), (70000, 5, 3000, 40), (50, 3, 1, 0), (1000, 11, 2500, 12)])
+def test_corpus_tables_built_on_gpu(built_lib, V, W, nchunks, maxlen):
+    """Window table and 1/count come from GPU kernels; both must equal the oracle's (T1, T2) exactly,
+    over empty chunks, chunks shorter than a window, chunks at and over the length limit, negative
+    (padding) ids, and a vocabulary too large for the shared-memory histogram."""
+    from flyvec_b200.engine import enumerate_windows
+    rng = np.random.default_rng(V + W)
+    lim = maxlen or orc.MAXLEN
+    lens = rng.integers(0, lim + 8, nchunks)
+    lens[rng.random(nchunks) < 0.1] = 0
+    lens[rng.random(nchunks) < 0.05] = lim - 1
+    lens[rng.random(nchunks) < 0.05] = lim
+    lens[rng.random(nchunks) < 0.05] = W
+    lens[rng.random(nchunks) < 0.05] = max(W - 1, 0)
+    off = np.concatenate(([0], np.cumsum(lens))).astype(np.uint64)
+    ntok = int(off[-1]) + 17
+    enc = (rng.zipf(1.3, ntok) % V).astype(np.int32)
+    enc[rng.random(ntok) < 0.01] = -1
+    tr = Trainer(hid=8, vocab=V, window=W, batch=4, maxlen=maxlen)
+    ns = tr.set_corpus(enc, off)
+    want = orc.enumerate_windows(off, W, lim)
+    assert ns == want.size
+    np.testing.assert_array_equal(tr.window_starts(), want)
+    np.testing.assert_array_equal(tr.window_starts(), enumerate_windows(off, W, maxlen))
+    np.testing.assert_array_equal(tr.inverse_frequency(), orc.inverse_word_frequency(enc, V, saturate_fp32=False))
+    np.testing.assert_array_equal(tr.get_permutation(), np.arange(ns, dtype=np.uint64))
+    tr.close()
+
+
+def test_corpus_errors_found_on_gpu(built_lib):
+    tr = Trainer(hid=8, vocab=100, window=3, batch=4)
+    enc = np.arange(60, dtype=np.int32)
+    with pytest.raises(_lib.FlyvecError, match="backwards"):
+        tr.set_corpus(enc, np.array([0, 30, 20, 60], np.uint64))
+    bad = enc.copy()
+    bad[41] = 100
+    with pytest.raises(_lib.FlyvecError, match=">= vocab"):
+        tr.set_corpus(bad, np.array([0, 30, 60], np.uint64))
+    assert tr.set_corpus(enc, np.array([0, 30, 60], np.uint64)) == 56
     tr.close()
 
 
