@@ -59,11 +59,20 @@ struct StepCtl {
   uint32_t pad;
   uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
   unsigned long long stamp[8];  // %globaltimer at phase boundaries of the last step (diagnostics)
+  // Device-side phase clock: every step kernel's first thread charges the time since the previous
+  // mark to the phase that was running and names its own.  No events, so the launches stay chained.
+  unsigned long long t_mark;
+  unsigned long long phase_ns[8];
+  uint32_t phase_now;
+  uint32_t pad2;
 };
+enum Phase { PH_OTHER = 0, PH_FORWARD = 1, PH_XX = 2, PH_WAIT = 3, PH_TAG = 4, PH_SCAN = 5, PH_APPLY = 6, PH_FOLD = 7 };
 
 // Everything a kernel needs, passed by value.
 struct Dev {
   int K, Kp, Kq, V, N, W, B, G, rank, P, XO;  // P = packet words, XO = offset of xx inside a packet
+  // exact n / divisor for n < 2^31 as (n * m) >> s (64-bit product): m = ceil(2^s / divisor), s = 31 + ceil(log2 divisor)
+  uint32_t mW, sW, mB, sB, mKp, sKp, mG, sG;
   int MO;          // offset of the second winners inside a packet (only with delta != 0)
   int has_delta;   // the anti-Hebbian term is on: every window also names its m-th (second) winner
   unsigned long long Ns, ntok;
@@ -96,11 +105,12 @@ struct Dev {
 // Mailbox header (words).  Everything is indexed [parity][sender]; a flag holds the sequence number
 // (tick + local + 1) of the step whose data is complete.
 constexpr int MAX_RANKS = 16;
-constexpr int FLAG_PKT = 0;                    // packets (winners + xx) delivered
+constexpr int FLAG_PKT = 0;                    // the xx part of the packet delivered (the whole packet when it travels at once)
 // The partial normaliser and the outbox count travel inside their flag: one 64-bit word
 // (sequence number in the high half, payload in the low half) written with a single store.
 constexpr int WORD_NC = 2 * MAX_RANKS;         // u64 [2][MAX_RANKS]: seq | float bits of sender's partial nc
 constexpr int WORD_OUT = 6 * MAX_RANKS;        // u64 [2][MAX_RANKS]: seq | entries in sender's outbox
+constexpr int FLAG_WIN = 10 * MAX_RANKS;       // u32 [2][MAX_RANKS]: the winners part of the packet delivered
 constexpr int MAIL_HDR = 10 * MAX_RANKS + 96;  // 256 words, keeps the packets 1 KiB aligned
 // Packet of rank r for the step of the given parity: B winners, then (at XO) Kp floats of xx.
 __device__ __forceinline__ uint32_t* packet(const Dev& d, int parity, int r) {
@@ -110,10 +120,19 @@ __device__ __forceinline__ uint32_t* packet(const Dev& d, int parity, int r) {
 __device__ __forceinline__ uint2* outbox(const Dev& d, const uint32_t* mail, int parity) {
   return reinterpret_cast<uint2*>(const_cast<uint32_t*>(mail) + d.outbox_off) + (size_t)parity * d.G * d.B * d.W * (1 + d.has_delta);
 }
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, uint32_t m, uint32_t s) {
+  return (uint32_t)(((unsigned long long)n * m) >> s);
+}
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+__device__ __forceinline__ void phase_mark(StepCtl* c, uint32_t next) {
+  const unsigned long long now = global_timer();
+  c->phase_ns[c->phase_now & 7u] += now - c->t_mark;
+  c->t_mark = now;
+  c->phase_now = next;
 }
 // Message passing between GPUs.  Producer: payload stores, ONE system-scope fence by one thread,
 // then relaxed flag stores.  Consumer: relaxed polls of the flag (they are served by the local L2,
@@ -193,9 +212,13 @@ __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps, floa
   ctl->delta = delta;
   ctl->fwd_next[0] = ctl->fwd_next[1] = 0u;
   ctl->xx_ticket = 0u;
+  for (int i = 0; i < 8; ++i) ctl->phase_ns[i] = 0ull;
+  ctl->t_mark = global_timer();
+  ctl->phase_now = PH_OTHER;
 }
 __global__ void k_advance(StepCtl* ctl, unsigned long long n) {
   grid_dependency_wait();
+  phase_mark(ctl, PH_OTHER);
   ctl->base += n;
   ctl->tick += n;
 }
@@ -370,6 +393,7 @@ __device__ __forceinline__ float weighted_activation(const Dev& d, const double*
 template <int NT>
 __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const int32_t* __restrict__ idx) {
   grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_FORWARD);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char fwd_smem[];
   float* s_alpha = reinterpret_cast<float*>(fwd_smem);  // [Kp] the units' scales as floats
@@ -547,19 +571,27 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
 // lane order into the warp's private bin array.  Bins are added warp by warp, CTA
 // partials CTA by CTA (by the CTA that finishes last), and xx lands behind the
 // winners in the outgoing packet.
+//
+// A unit that won windows but whose activations add up to exactly zero counts as
+// inactive on this rank (cu_special_reduction.cu:42-66 tests xx != 0), yet its windows
+// exist; it is published as -0.0f so that consumers, which tag every window without
+// knowing xx, can take this rank's windows out again (k_scan).  Units that won nothing
+// are +0.0f.
 // ---------------------------------------------------------------------------
+constexpr uint32_t XX_WON_ZERO = 0x80000000u;
 constexpr int XX_THREADS = 512;
 constexpr int XX_WARPS = XX_THREADS / 32;
 constexpr int TAG_TABLE_LOG2 = 11;
 constexpr int TAG_TABLE = 1 << TAG_TABLE_LOG2;  // shared-memory hash table, at most half full
 __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nctas, unsigned char* xx_smem) {
   float* bins = reinterpret_cast<float*>(xx_smem);  // [XX_WARPS][Kp]
+  int* s_won = reinterpret_cast<int*>(bins + XX_WARPS * d.Kp);  // [Kp] the unit won a window of this CTA's block
   __shared__ unsigned s_ticket;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
   const int parity = (int)((d.ctl->tick + local) & 1);
   uint32_t* __restrict__ mine = packet(d, parity, d.rank);
   const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(mine);
-  for (int i = threadIdx.x; i < XX_WARPS * d.Kp; i += XX_THREADS) bins[i] = 0.f;
+  for (int i = threadIdx.x; i < (XX_WARPS + 1) * d.Kp; i += XX_THREADS) bins[i] = 0.f;  // s_won included
   __syncthreads();
   const int per_cta = (d.B + nctas - 1) / nctas;
   const int per_warp = (per_cta + XX_WARPS - 1) / XX_WARPS;
@@ -598,7 +630,10 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
           m &= m - 1;
         }
       }
-      if (leader && w >= 0) mybins[w] += sum;
+      if (leader && w >= 0) {
+        mybins[w] += sum;
+        s_won[w] = 1;
+      }
       __syncwarp();
     }
   }
@@ -608,6 +643,7 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
     float p = 0.f;
 #pragma unroll
     for (int w = 0; w < XX_WARPS; ++w) p += bins[w * d.Kp + mu];
+    if (p == 0.f) p = __uint_as_float(s_won[mu] ? XX_WON_ZERO : 0u);
     d.xx_part[(size_t)cta * d.Kp + mu] = p;
   }
   __threadfence();
@@ -623,9 +659,14 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
         float part[8];  // nctas <= 8: fetch all partials, then add them in CTA order
 #pragma unroll
         for (int c = 0; c < 8; ++c) part[c] = (c < nctas) ? __ldcg(d.xx_part + (size_t)c * d.Kp + mu) : 0.f;
+        bool won = false;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          if (c < nctas) acc += part[c];
+          if (c < nctas) {
+            acc += part[c];
+            won = won || (__float_as_uint(part[c]) != 0u);
+          }
+        if (acc == 0.f) acc = __uint_as_float(won ? XX_WON_ZERO : 0u);
       }
       xx_out[mu] = acc;
     }
@@ -634,17 +675,18 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
       d.ctl->fwd_next[parity] = 0u;  // rank emulation runs several forward passes per step
     }
     if (d.peers != nullptr && d.G > 1) {
-      // Exchange fused into the producer: push the finished packet (winners + xx) into every
+      // Exchange fused into the producer: push xx (the winners went ahead, push_winners) into every
       // peer's mailbox over NVLink with plain stores, make the stores visible system-wide, then
-      // publish the step's sequence number in the peer's flag word.  The peers' k_tag polls it.
+      // publish the step's sequence number in the peer's flag word.  The peers' k_scan polls it.
       __syncthreads();
       const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
-      const uint4* __restrict__ src4 = reinterpret_cast<const uint4*>(mine);
-      const int n4 = d.P >> 2;
-      for (int r = 0; r < d.G; ++r) {
+      const uint4* __restrict__ src4 = reinterpret_cast<const uint4*>(mine + d.XO);
+      const int n4 = d.Kp >> 2;
+      for (int i = threadIdx.x; i < n4 * d.G; i += XX_THREADS) {
+        const int r = i / n4;
         if (r == d.rank) continue;
-        uint4* dst4 = reinterpret_cast<uint4*>(d.peers[r] + MAIL_HDR + ((size_t)parity * d.G + d.rank) * d.P);
-        for (int i = threadIdx.x; i < n4; i += XX_THREADS) dst4[i] = __ldcg(src4 + i);
+        uint4* dst4 = reinterpret_cast<uint4*>(d.peers[r] + MAIL_HDR + ((size_t)parity * d.G + d.rank) * d.P + d.XO);
+        dst4[i - r * n4] = __ldcg(src4 + (i - r * n4));
       }
       __syncthreads();
       if (threadIdx.x == 0) __threadfence_system();
@@ -654,8 +696,28 @@ __device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nc
     }
   }
 }
+// The winners of this rank's windows are final when k_forward ends.  xx CTA c copies them into the
+// mailboxes of peers c, c + nctas, ... (plain stores over NVLink), makes them visible with one
+// system-scope fence and raises the peers' FLAG_WIN word; the peers' tagging CTAs poll it.
+__device__ __forceinline__ void push_winners(const Dev& d, int local, int parity, int cta, int nctas) {
+  const uint4* __restrict__ src4 = reinterpret_cast<const uint4*>(packet(d, parity, d.rank));
+  const int n4 = d.XO >> 2;  // first and (with delta) second winners
+  for (int r = cta; r < d.G; r += nctas) {
+    if (r == d.rank) continue;
+    uint4* dst4 = reinterpret_cast<uint4*>(d.peers[r] + MAIL_HDR + ((size_t)parity * d.G + d.rank) * d.P);
+    for (int i = threadIdx.x; i < n4; i += XX_THREADS) dst4[i] = __ldcg(src4 + i);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
+    for (int r = cta; r < d.G; r += nctas)
+      if (r != d.rank) store_relaxed_sys(d.peers[r] + FLAG_WIN + parity * MAX_RANKS + d.rank, seq);
+  }
+}
 __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
   grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_XX);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char xx_smem[];
   xx_body(d, local, blockIdx.x, gridDim.x, xx_smem);
@@ -671,214 +733,196 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
 // skipped when its rank's xx[winner] is zero: the reference drops a replica's whole
 // row from the combine in that case (cu_special_reduction.cu:42-66).
 // ---------------------------------------------------------------------------
-// With xx_ctas > 0 (single rank) the first xx_ctas CTAs compute xx instead, side by
-// side with the tagging; tagging then cannot ask whether the rank was active for a
-// unit and tags every slot -- a unit that turns out inactive simply gets its parked
-// weights back unchanged in k_apply.
+// The first xx_ctas CTAs do not tag: they compute xx (xx_body) side by side with the tagging and,
+// with peer mailboxes, first send this rank's winners to the peers.  Tagging needs the winners of
+// all ranks but not xx, so it tags every (window, position); a unit that turns out inactive on all
+// ranks gets its parked weights back unchanged in k_apply, and the windows of a rank on which the
+// unit's xx cancelled to exactly zero are taken out of the counts again by k_scan.
+constexpr int TAG_CLAIMS = 2;  // compacted positions a thread claims per block round (UN == 2)
+__device__ __forceinline__ void claim_position(const Dev& d, uint32_t pos, uint32_t c, uint32_t slot, uint32_t mult, uint32_t EV) {
+  uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
+  const uint32_t tag = TAG_BASE | (slot + 1u);
+  for (;;) {
+    if ((c & ABS_MASK) > TAG_BASE) {
+      const uint32_t owner = (c & 0x007fffffu) - 1u;
+      if ((c >> 31) || owner >= EV) {
+        atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+      } else {
+        if (mult & 0xffffu) atomicAdd(&d.cnt[owner], (int)(mult & 0xffffu));
+        if (mult >> 16) atomicAdd(&d.cntn[owner], (int)(mult >> 16));
+      }
+      return;
+    }
+    const uint32_t prev = atomicCAS(addr, c, tag);
+    if (prev == c) {
+      // the claimant's own multiplicities travel in the record (first-winner kind in the low half,
+      // second-winner kind above); cnt[] only collects later comers, so a position touched from one
+      // block costs no counter atomic at all
+      const int irow = (int)fdiv(pos, d.mKp, d.sKp);
+      d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (irow >= d.V ? irow - d.V : irow))), mult);
+      return;
+    }
+    c = prev;
+  }
+}
 template <int UN>  // slots per thread and block round: a CTA deduplicates UN * XX_THREADS slots together
-__global__ void __launch_bounds__(XX_THREADS) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas) {
+__global__ void __launch_bounds__(XX_THREADS, UN == 2 ? 3 : 1) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas) {
   grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char tag_smem[];
+  const int parity = (int)((d.ctl->tick + local) & 1);
+  const bool mailbox = d.peers != nullptr && d.G > 1;
   if ((int)blockIdx.x < xx_ctas) {
+    if (mailbox) push_winners(d, local, parity, blockIdx.x, xx_ctas);
     xx_body(d, local, blockIdx.x, xx_ctas, tag_smem);
     return;
   }
-  const int parity = (int)((d.ctl->tick + local) & 1);
-  if (d.peers != nullptr && d.G > 1) {
-    // wait (bounded) until every peer has published this step's packet in our mailbox
+  const bool marker = (int)blockIdx.x == xx_ctas && threadIdx.x == 0;
+  if (marker) phase_mark(d.ctl, mailbox ? PH_WAIT : PH_TAG);
+  if (mailbox) {
+    // wait (bounded) until every peer's winners of this step are in our mailbox
     __shared__ int s_fail;
     if (threadIdx.x == 0) s_fail = 0;
     __syncthreads();
     if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
       const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
-      if (!wait_flag(d, d.mail + FLAG_PKT + parity * MAX_RANKS + threadIdx.x, seq)) s_fail = 1;
+      if (!wait_flag(d, d.mail + FLAG_WIN + parity * MAX_RANKS + threadIdx.x, seq)) s_fail = 1;
     }
     __syncthreads();
+    if (marker) phase_mark(d.ctl, PH_TAG);
     if (s_fail) return;
   }
   // Stage 1: a block of TAG_BLOCK slots is deduplicated in a shared-memory hash table keyed by the
   // matrix position, so a (unit, token) pair that occurs many times in the block -- frequent tokens
   // do -- reaches global memory once, with its multiplicity.  Same-address global atomics complete
   // at about one per nanosecond, which made the duplicates of the hottest pairs the bottleneck.
-  // Stage 2: every distinct position gets a record slot (one counter bump per block) and is claimed
-  // with one CAS; the winner of the claim writes the record, the others add their multiplicity to
-  // the claimant's count.
-  __shared__ uint32_t s_key[TAG_TABLE];
-  __shared__ int s_cnt[TAG_TABLE];
-  __shared__ uint32_t s_scan[XX_THREADS / 32 + 1];
+  // Stage 2: the distinct positions are compacted, get record slots (one counter bump per block) and
+  // are claimed with one CAS each, the loads of a thread's claims issued together; the winner of a
+  // claim writes the record, the others add their multiplicity to the claimant's count.
+  __shared__ uint32_t s_scan[XX_WARPS];
+  __shared__ uint32_t s_gbase;
   // With delta != 0 every (window, position) contributes twice: +f_i to the first winner's row and
   // -delta*f_i to the second winner's row (cuda_funcs.cu:665-668).  Virtual slot ev = kind * E + e.
   const int E = d.G * d.B * d.W;
   const int EV = E * (1 + d.has_delta);
-  const bool check_active = (xx_ctas == 0);
   constexpr int TAG_BLOCK = UN * XX_THREADS;
   const int nblocks = (EV + TAG_BLOCK - 1) / TAG_BLOCK;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  // winner of virtual slot ev (which must be < EV)
+  auto winner_of = [&](int ev) -> int {
+    const int kind = (ev >= E) ? 1 : 0;
+    const uint32_t q = fdiv((uint32_t)(ev - kind * E), d.mW, d.sW);  // window of the global step
+    const uint32_t r = fdiv(q, d.mB, d.sB);                          // its rank
+    return (int)packet(d, parity, (int)r)[kind * d.MO + (int)(q - r * (uint32_t)d.B)];
+  };
   for (int blk = blockIdx.x - xx_ctas; blk < nblocks; blk += gridDim.x - xx_ctas) {
     if constexpr (UN == 1) {
       // small steps: duplicates inside 512 slots are rare, so skip the table: number the live slots of
       // the CTA with a ballot/prefix (one counter bump per CTA round) and claim directly
       const int ev = blk * TAG_BLOCK + threadIdx.x;
-      const int kind = (ev >= E) ? 1 : 0;
-      const int e = ev - kind * E;
-      const int i0 = (ev < EV) ? idx[e] : -1;
-      bool go0 = i0 >= 0 && !(d.shard && (i0 % d.G) != d.rank);
+      const int i0 = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
+      bool go0 = i0 >= 0 && !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
       int mu0 = -1;
       if (go0) {
-        const int q = e / d.W;
-        const int r = q / d.B, j = q - r * d.B;
-        const uint32_t* __restrict__ pkt = packet(d, parity, r);
-        mu0 = (int)pkt[kind * d.MO + j];
-        go0 = mu0 >= 0 && !(check_active && __uint_as_float(pkt[d.XO + mu0]) == 0.f);
+        mu0 = winner_of(ev);
+        go0 = mu0 >= 0;
       }
+      const uint32_t pos = (uint32_t)((size_t)(go0 ? i0 : 0) * d.Kp + (go0 ? mu0 : 0));
       uint32_t c0 = 0u;
-      if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt + (size_t)i0 * d.Kp + mu0));
+      if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos);
       const unsigned live = __ballot_sync(FULL, go0);
       if (lane == 0) s_scan[wic] = (uint32_t)__popc(live);
       __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t tot = 0;
-        for (int w = 0; w < XX_THREADS / 32; ++w) {
-          const uint32_t c = s_scan[w];
-          s_scan[w] = tot;
-          tot += c;
-        }
-        s_scan[XX_THREADS / 32] = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
+      uint32_t before = 0u, tot = 0u;
+#pragma unroll
+      for (int w = 0; w < XX_WARPS; ++w) {
+        const uint32_t c = s_scan[w];
+        before += (w < wic) ? c : 0u;
+        tot += c;
       }
+      if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
       __syncthreads();
-      if (go0) {
-        const uint32_t slot = s_scan[XX_THREADS / 32] + s_scan[wic] + (uint32_t)__popc(live & ((1u << lane) - 1u));
-        const uint32_t pos = (uint32_t)((size_t)i0 * d.Kp + mu0);
-        uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
-        const uint32_t tag = TAG_BASE | (slot + 1u);
-        uint32_t c = c0;
-        for (;;) {
-          if ((c & ABS_MASK) > TAG_BASE) {
-            const uint32_t owner = (c & 0x007fffffu) - 1u;
-            if ((c >> 31) || owner >= (uint32_t)EV) {
-              atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
-            } else {
-              atomicAdd(kind ? &d.cntn[owner] : &d.cnt[owner], 1);
-            }
-            break;
-          }
-          const uint32_t prev = atomicCAS(addr, c, tag);
-          if (prev == c) {
-            // .w: the claimant's own multiplicities, first-winner kind in the low half, second-winner kind above
-            d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (i0 % d.V))), kind ? 0x10000u : 1u);
-            break;
-          }
-          c = prev;
-        }
-      }
-      __syncthreads();
+      if (go0) claim_position(d, pos, c0, s_gbase + before + (uint32_t)__popc(live & ((1u << lane) - 1u)), ev >= E ? 0x10000u : 1u, (uint32_t)EV);
     } else {
-    for (int t = threadIdx.x; t < TAG_TABLE; t += XX_THREADS) {
-      s_key[t] = 0u;
-      s_cnt[t] = 0;
-    }
-    __syncthreads();
-    int i[UN], mu[UN];
-    bool go[UN];
+      uint32_t* s_key = reinterpret_cast<uint32_t*>(tag_smem);           // [TAG_TABLE] position + 1, 0 = free
+      uint32_t* s_cnt = s_key + TAG_TABLE;                               // [TAG_TABLE] two 16-bit multiplicities
+      uint32_t* s_ckey = s_cnt + TAG_TABLE;                              // [TAG_BLOCK] compacted keys
+      uint32_t* s_cmult = s_ckey + TAG_BLOCK;                            // [TAG_BLOCK] and their multiplicities
+      constexpr int PER = TAG_TABLE / XX_THREADS;
+      static_assert(PER == 4, "a thread owns one uint4 of the table");
+      reinterpret_cast<uint4*>(s_key)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+      reinterpret_cast<uint4*>(s_cnt)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+      __syncthreads();
+      int i[UN], mu[UN];
 #pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-      i[u] = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
-    }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-      const int kind = (ev >= E) ? 1 : 0;
-      const int e = ev - kind * E;
-      go[u] = i[u] >= 0 && !(d.shard && (i[u] % d.G) != d.rank);  // sharded: another rank owns this row
-      mu[u] = -1;
-      if (go[u]) {
-        const int q = e / d.W;
-        const int r = q / d.B, j = q - r * d.B;
-        mu[u] = (int)packet(d, parity, r)[kind * d.MO + j];
+      for (int u = 0; u < UN; ++u) {
+        const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+        i[u] = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
       }
-    }
 #pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      go[u] = go[u] && mu[u] >= 0;
-      const int evu = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-      if (go[u] && check_active) {
-        const int e = evu >= E ? evu - E : evu;
-        const int r = (e / d.W) / d.B;
-        go[u] = __uint_as_float(packet(d, parity, r)[d.XO + mu[u]]) != 0.f;
+      for (int u = 0; u < UN; ++u) {
+        const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+        // sharded: another rank may own this row
+        const bool go = i[u] >= 0 && !(d.shard && (int)((uint32_t)i[u] - fdiv((uint32_t)i[u], d.mG, d.sG) * (uint32_t)d.G) != d.rank);
+        mu[u] = go ? winner_of(ev) : -1;
       }
-      if (go[u]) {
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (mu[u] < 0) continue;
+        const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
         const uint32_t key = (uint32_t)((size_t)i[u] * d.Kp + mu[u]) + 1u;
         uint32_t h = (key * 2654435761u) >> (32 - TAG_TABLE_LOG2);
         for (;;) {
           const uint32_t old = atomicCAS(&s_key[h], 0u, key);
           if (old == 0u || old == key) {
-            atomicAdd(&s_cnt[h], evu >= E ? 0x10000 : 1);  // two 16-bit multiplicities (a block has <= 1024 slots)
+            atomicAdd(&s_cnt[h], ev >= E ? 0x10000u : 1u);  // a block has <= 1024 slots: 16 bits each suffice
             break;
           }
           h = (h + 1) & (TAG_TABLE - 1);
         }
       }
-    }
-    __syncthreads();
-    // compact numbering of the occupied table slots (each thread owns TAG_TABLE / XX_THREADS of them)
-    constexpr int PER = TAG_TABLE / XX_THREADS;
-    int occ = 0;
+      __syncthreads();
+      // compaction: every thread owns PER consecutive table slots
+      const uint4 k4 = reinterpret_cast<const uint4*>(s_key)[threadIdx.x];
+      const uint4 c4 = reinterpret_cast<const uint4*>(s_cnt)[threadIdx.x];
+      const int occ = (k4.x != 0u) + (k4.y != 0u) + (k4.z != 0u) + (k4.w != 0u);
+      int incl = occ;
 #pragma unroll
-    for (int k = 0; k < PER; ++k) occ += (s_key[threadIdx.x * PER + k] != 0u);
-    int incl = occ;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(FULL, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (lane == 31) s_scan[wic] = (uint32_t)incl;
+      __syncthreads();
+      uint32_t before = 0u, tot = 0u;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(FULL, incl, o);
-      if (lane >= o) incl += v;
-    }
-    if (lane == 31) s_scan[wic] = (uint32_t)incl;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      uint32_t tot = 0;
-      for (int w = 0; w < XX_THREADS / 32; ++w) {
+      for (int w = 0; w < XX_WARPS; ++w) {
         const uint32_t c = s_scan[w];
-        s_scan[w] = tot;
+        before += (w < wic) ? c : 0u;
         tot += c;
       }
-      s_scan[XX_THREADS / 32] = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
-    }
-    __syncthreads();
-    uint32_t slot = s_scan[XX_THREADS / 32] + s_scan[wic] + (uint32_t)(incl - occ);
+      if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
+      uint32_t at = before + (uint32_t)(incl - occ);
+      if (k4.x) { s_ckey[at] = k4.x; s_cmult[at] = c4.x; ++at; }
+      if (k4.y) { s_ckey[at] = k4.y; s_cmult[at] = c4.y; ++at; }
+      if (k4.z) { s_ckey[at] = k4.z; s_cmult[at] = c4.z; ++at; }
+      if (k4.w) { s_ckey[at] = k4.w; s_cmult[at] = c4.w; ++at; }
+      __syncthreads();
+      // claims: position tot is at most TAG_BLOCK = TAG_CLAIMS * XX_THREADS
+      static_assert(TAG_CLAIMS * XX_THREADS >= TAG_BLOCK, "every compacted position needs a claimant");
+      uint32_t key[TAG_CLAIMS], cur[TAG_CLAIMS];
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      const uint32_t key = s_key[threadIdx.x * PER + k];
-      if (key == 0u) continue;
-      const int mult = s_cnt[threadIdx.x * PER + k];
-      const uint32_t pos = key - 1u;
-      uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
-      const uint32_t tag = TAG_BASE | (slot + 1u);
-      uint32_t c = __ldcg(addr);
-      for (;;) {
-        if ((c & ABS_MASK) > TAG_BASE) {
-          const uint32_t owner = (c & 0x007fffffu) - 1u;
-          if ((c >> 31) || owner >= (uint32_t)EV) {
-            atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
-          } else {
-            if (mult & 0xffff) atomicAdd(&d.cnt[owner], mult & 0xffff);
-            if (mult >> 16) atomicAdd(&d.cntn[owner], mult >> 16);
-          }
-          break;
-        }
-        const uint32_t prev = atomicCAS(addr, c, tag);
-        if (prev == c) {
-          const int irow = (int)(pos / (uint32_t)d.Kp);
-          // the claimant's own multiplicity travels in the record; cnt[] only collects later comers,
-          // so a position touched from one block costs no counter atomic at all
-          d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (irow % d.V))), (uint32_t)mult);
-          break;
-        }
-        c = prev;
+      for (int u = 0; u < TAG_CLAIMS; ++u) {
+        const uint32_t cidx = (uint32_t)(u * XX_THREADS + threadIdx.x);
+        key[u] = (cidx < tot) ? s_ckey[cidx] : 0u;
+        cur[u] = key[u] ? __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + (key[u] - 1u)) : 0u;
       }
-      ++slot;
+#pragma unroll
+      for (int u = 0; u < TAG_CLAIMS; ++u) {
+        const uint32_t cidx = (uint32_t)(u * XX_THREADS + threadIdx.x);
+        if (key[u]) claim_position(d, key[u] - 1u, cur[u], s_gbase + cidx, s_cmult[cidx], (uint32_t)EV);
+      }
     }
-    __syncthreads();
-    }  // table path
+    __syncthreads();  // the tables are reused by the next round
   }
 }
 
@@ -899,6 +943,39 @@ __device__ __forceinline__ void unit_stats(const Dev& d, int parity, int mu, dou
   *X = cnt ? sum / (double)cnt : 0.0;
 }
 
+// Ranks (bit r) on which unit mu won windows although its xx is exactly zero: their windows were
+// tagged like all others and have to leave the counts again.
+__device__ __forceinline__ uint32_t unit_cancelled(const Dev& d, int parity, int mu) {
+  uint32_t bad = 0u;
+  for (int r = 0; r < d.G; ++r)
+    if (packet(d, parity, r)[d.XO + mu] == XX_WON_ZERO) bad |= 1u << r;
+  return bad;
+}
+// How often the windows of the ranks in `bad` asked for matrix row `irow` of unit mu, as first
+// winner (*np) and as second winner (*nn).  A plain search over those ranks' windows: this only
+// runs when activations cancel exactly on one rank while another rank is active for the unit.
+// (Scalars instead of the parameter block: a call by reference would put the block on the stack.)
+__device__ __noinline__ int2 cancelled_multiplicity(const uint32_t* __restrict__ packet0, int P, int G, int B, int W, int MO,
+                                                    int has_delta, const int32_t* __restrict__ idx, int irow, int mu, uint32_t bad) {
+  int a = 0, b = 0;
+  for (int r = 0; r < G; ++r) {
+    if (!((bad >> r) & 1u)) continue;
+    const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(packet0 + (size_t)r * P);
+    for (int j = 0; j < B; ++j) {
+      const bool first = win[j] == mu;
+      const bool second = has_delta && win[MO + j] == mu;
+      if (!first && !second) continue;
+      const int32_t* __restrict__ ids = idx + ((size_t)r * B + j) * W;
+      for (int t = 0; t < W; ++t)
+        if (ids[t] == irow) {
+          a += first;
+          b += second;
+        }
+    }
+  }
+  return make_int2(a, b);
+}
+
 // ---------------------------------------------------------------------------
 // T11.  nc = max |D| with D = -X*W + S.
 //   part 1: owners evaluate D at their (touched) position -> ncb (scalar max);
@@ -916,14 +993,34 @@ constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_UNROLL = 8;
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, const int32_t* __restrict__ idx) {
   grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_SCAN);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
   int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
   uint32_t* sMax = reinterpret_cast<uint32_t*>(sN + d.Kp); // CTA column maxima
+  uint32_t* sBad = sMax + d.Kp;                            // ranks whose windows must leave the counts (unit_cancelled)
   const int p = (int)((d.ctl->tick + local) & 1);
   const int lane = threadIdx.x & 31;
   const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  __shared__ int s_any_bad;
+  if (threadIdx.x == 0) s_any_bad = 0;
+  __syncthreads();
+  if (d.peers != nullptr && d.G > 1) {
+    // wait (bounded) until every peer's xx of this step is in our mailbox
+    const bool marker = blockIdx.x == 0 && threadIdx.x == 0;
+    if (marker) phase_mark(d.ctl, PH_WAIT);
+    __shared__ int s_fail;
+    if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
+      const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
+      if (!wait_flag(d, d.mail + FLAG_PKT + p * MAX_RANKS + threadIdx.x, seq)) s_fail = 1;
+    }
+    __syncthreads();
+    if (marker) phase_mark(d.ctl, PH_SCAN);
+    if (s_fail) return;
+  }
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
@@ -931,15 +1028,33 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     sC[mu] = X * alpha[mu];
     sN[mu] = n;
     sMax[mu] = 0u;
+    const uint32_t bad = (mu < d.K && n > 0) ? unit_cancelled(d, p, mu) : 0u;
+    sBad[mu] = bad;
+    if (bad) s_any_bad = 1;
   }
   __syncthreads();
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nthreads = gridDim.x * blockDim.x;
+  const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s_any_bad) {
+    // some rank's windows for a unit do not count although the unit is active elsewhere: take them
+    // out of this thread's records before anybody (here or in k_apply) reads the counts
+    const uint32_t* packet0 = packet(d, p, 0);
+    for (int k = e0; k < nrec; k += nthreads) {
+      const uint4 r = d.rec[k];
+      if (r.w == 0u) continue;
+      const int irow = (int)fdiv(r.x, d.mKp, d.sKp);
+      const int mu = (int)r.x - irow * d.Kp;
+      if (!sBad[mu]) continue;
+      const int2 c = cancelled_multiplicity(packet0, d.P, d.G, d.B, d.W, d.MO, d.has_delta, idx, irow, mu, sBad[mu]);
+      if (c.x) d.cnt[k] -= c.x;
+      if (c.y) d.cntn[k] -= c.y;
+    }
+  }
 
   // part 1, first half: counts and records of this thread's share of the touched-position list
   // (coalesced loads, issued before the row stream so that their latency hides behind it)
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
   const float delta = d.ctl->delta;
-  const int nthreads = gridDim.x * blockDim.x;
-  const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
   constexpr int TS = 4;
   float cs[TS];  // net multiplicity of the scatter term: (+1 kind) - delta * (-delta kind)
   uint4 rc[TS];
@@ -999,8 +1114,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   uint32_t tmax = 0u;
   auto touched = [&](float c, const uint4& r) {
     if (r.w == 0u) return;  // a reserved record nobody claimed
-    const int mu = (int)(r.x % (uint32_t)d.Kp);
-    if (sN[mu] == 0) return;  // tagged before the unit proved inactive: no update there
+    const int mu = (int)(r.x - fdiv(r.x, d.mKp, d.sKp) * (uint32_t)d.Kp);
+    if (sN[mu] == 0) return;  // the unit proved inactive on every rank: no update there
     const double D = -sC[mu] * (double)__uint_as_float(r.y) + (double)c * (double)__uint_as_float(r.z) / (double)sN[mu];
     tmax = max(tmax, __float_as_uint(fabsf((float)D)));
   };
@@ -1064,6 +1179,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* __restrict__ idx) {
   grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_APPLY);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sX = reinterpret_cast<double*>(smem_raw);  // mean xx over active ranks, later s / (n * alpha')
@@ -1281,6 +1397,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
   grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_FOLD);
   // `local` = steps already launched in this call: the buffer the next step would read
   const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
   const size_t total = (size_t)d.N * d.Kq;
@@ -1548,7 +1665,6 @@ struct fv_trainer {
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   cudaEvent_t ev_copy[2] = {nullptr, nullptr}, ev_used[2] = {nullptr, nullptr};
-  std::vector<cudaEvent_t> phase_events;
   bool have_corpus = false, have_weights = false;
   void* comm = nullptr;
   // owned device buffers
@@ -1586,7 +1702,6 @@ struct fv_trainer {
 namespace {
 
 constexpr unsigned long long FOLD_EVERY = 32;  // steps between folds of alpha into wt
-constexpr int PHASE_SAMPLE = 16;               // every 16th step carries phase events
 constexpr int STAGE_STEPS = 32;                // steps per upload chunk in streaming mode
 
 #define FV_TRY(expr)                    \
@@ -1659,11 +1774,10 @@ int fold_weights(fv_trainer* tr, int local) {
 
 // One global step on tr->stream.  `idx` holds this step's input ids (all ranks' windows).
 // Adds the kernels launched to *launches.
-int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, cudaEvent_t* marks, uint64_t* launches) {
+int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, uint64_t* launches) {
   const Dev& d = tr->d;
   const bool emulate = (d.flags & FV_FLAG_EMULATE_RANKS) != 0;
   const bool single = (d.G == 1);
-  if (marks) FV_CUDA(cudaEventRecord(marks[0], tr->stream));
   if (emulate && !single) {
     // every rank's block in turn, each into its own packet slot
     const int own_rank = tr->d.rank;
@@ -1674,32 +1788,28 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, cudaEvent_t* mar
       *launches += 2;
     }
     tr->d.rank = own_rank;
-    if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
   } else {
     FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
     *launches += 1;
-    if (marks) FV_CUDA(cudaEventRecord(marks[1], tr->stream));
-    if (!single) {
-      // k_xx finishes the packet; with mailboxes its last CTA also pushes it to the peers
+    if (tr->comm_mode == 1) {
+      // k_xx finishes the packet, one all-gather delivers everybody's
       launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local);
       *launches += 1;
-      if (tr->comm_mode == 1) {
-        const int parity = (int)((tr->ticks + (unsigned long long)local) & 1);
-        uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P;
-        const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P, base, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
-        if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
-      }
+      const int parity = (int)((tr->ticks + (unsigned long long)local) & 1);
+      uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P;
+      const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P, base, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
+      if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
     }
   }
-  if (marks) FV_CUDA(cudaEventRecord(marks[2], tr->stream));
-  if (single)  // xx is computed by the first CTAs of the tagging kernel
-    launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local, idx,
-               tr->xx_grid);
-  else
-    launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, 0);
+  // One rank, or peer mailboxes: the first CTAs of the tagging kernel compute xx beside the tagging
+  // (and, with mailboxes, push winners first and xx last); otherwise xx is complete already.
+  const bool fused = single || (tr->comm_mode == 2 && !emulate);
+  const size_t table_smem = tr->tag_un == 2 ? (size_t)(2 * TAG_TABLE + 2 * 2 * XX_THREADS) * sizeof(uint32_t) : 0;
+  const size_t tag_smem = (fused && tr->xx_smem > table_smem) ? tr->xx_smem : table_smem;
+  launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + (fused ? tr->xx_grid : 0), XX_THREADS, tag_smem, tr->stream, d, local,
+             idx, fused ? tr->xx_grid : 0);
   launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
   launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
-  if (marks) FV_CUDA(cudaEventRecord(marks[3], tr->stream));
   FV_CUDA(cudaGetLastError());
   *launches += 3;
   tr->steps_since_fold += 1;
@@ -1715,14 +1825,6 @@ int ensure_log(fv_trainer* tr, size_t nsteps) {
   tr->log_cap = nsteps;
   tr->d.nc_log = tr->d_log;
   tr->d.s_log = tr->d_log + nsteps;
-  return FV_OK;
-}
-
-int read_device_error(fv_trainer* tr, uint32_t* out) {
-  StepCtl h;
-  FV_CUDA(cudaMemcpyAsync(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost, tr->stream));
-  FV_CUDA(cudaStreamSynchronize(tr->stream));
-  *out = h.error;
   return FV_OK;
 }
 
@@ -1745,12 +1847,6 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   const unsigned long long fold_every = (d.flags & FV_FLAG_FOLD_EVERY_STEP) ? 1 : FOLD_EVERY;
   const size_t step_ids = (size_t)d.G * d.B * d.W;
 
-  const size_t nsamples = (size_t)((nsteps + PHASE_SAMPLE - 1) / PHASE_SAMPLE);
-  while (tr->phase_events.size() < nsamples * 4) {
-    cudaEvent_t e;
-    FV_CUDA(cudaEventCreate(&e));
-    tr->phase_events.push_back(e);
-  }
   for (int b = 0; b < 2; ++b)
     if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
 
@@ -1782,8 +1878,7 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
       }
     }
     const int32_t* idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * step_ids;
-    cudaEvent_t* marks = (k % PHASE_SAMPLE == 0) ? &tr->phase_events[(k / PHASE_SAMPLE) * 4] : nullptr;
-    FV_TRY(enqueue_step(tr, (int)k, idx, marks, &launches));
+    FV_TRY(enqueue_step(tr, (int)k, idx, &launches));
     if ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps) {
       FV_CUDA(cudaEventRecord(tr->ev_used[chunk_id & 1], tr->stream));
       ++chunk_id;
@@ -1805,14 +1900,14 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   if (nc_out) memcpy(nc_out, log.data(), nsteps * sizeof(float));
   if (scale_out) memcpy(scale_out, log.data() + nsteps, nsteps * sizeof(float));
 
-  uint32_t dev_err = 0;
-  FV_TRY(read_device_error(tr, &dev_err));
+  StepCtl h;
+  FV_CUDA(cudaMemcpy(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost));
+  const uint32_t dev_err = h.error;
   if (getenv("FV_STAMPS")) {
-    StepCtl h;
-    FV_CUDA(cudaMemcpy(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost));
-    fprintf(stderr, "[rank %d] apply: start->nc %.1f us, own slots %.1f us, ->lists %.1f us, merge %.1f us; scan end->apply start %.1f us\n",
-            tr->d.rank, (h.stamp[1] - h.stamp[0]) * 1e-3, (h.stamp[2] - h.stamp[1]) * 1e-3, (h.stamp[3] - h.stamp[2]) * 1e-3,
-            (h.stamp[4] - h.stamp[3]) * 1e-3, ((double)h.stamp[0] - (double)h.stamp[6]) * 1e-3);
+    fprintf(stderr, "[rank %d] per step (us): other %.1f forward %.1f xx %.1f wait %.1f tag %.1f scan %.1f apply %.1f fold %.1f\n", tr->d.rank,
+            h.phase_ns[PH_OTHER] * 1e-3 / nsteps, h.phase_ns[PH_FORWARD] * 1e-3 / nsteps, h.phase_ns[PH_XX] * 1e-3 / nsteps,
+            h.phase_ns[PH_WAIT] * 1e-3 / nsteps, h.phase_ns[PH_TAG] * 1e-3 / nsteps, h.phase_ns[PH_SCAN] * 1e-3 / nsteps,
+            h.phase_ns[PH_APPLY] * 1e-3 / nsteps, h.phase_ns[PH_FOLD] * 1e-3 / nsteps);
   }
   if (stats) {
     float ms = 0.f;
@@ -1830,19 +1925,11 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
     }
     stats->windows = mine;
     stats->seconds = ms * 1e-3;
-    double ph[3] = {0, 0, 0};
-    for (size_t smp = 0; smp < nsamples; ++smp) {
-      cudaEvent_t* m = &tr->phase_events[smp * 4];
-      for (int i = 0; i < 3; ++i) {
-        float t = 0.f;
-        FV_CUDA(cudaEventElapsedTime(&t, m[i], m[i + 1]));
-        ph[i] += t * 1e-3;
-      }
-    }
-    const double scale = (double)nsteps / (double)nsamples;
-    stats->fwd_seconds = ph[0] * scale;
-    stats->exch_seconds = ph[1] * scale;
-    stats->upd_seconds = ph[2] * scale;
+    // from the device-side phase clock (whole run, no sampling): forward; xx + waiting for the peers;
+    // tag + scan + apply.  Folding and the gaps between steps make up the rest of `seconds`.
+    stats->fwd_seconds = h.phase_ns[PH_FORWARD] * 1e-9;
+    stats->exch_seconds = (h.phase_ns[PH_XX] + h.phase_ns[PH_WAIT]) * 1e-9;
+    stats->upd_seconds = (h.phase_ns[PH_TAG] + h.phase_ns[PH_SCAN] + h.phase_ns[PH_APPLY]) * 1e-9;
     stats->kernel_launches = launches;
     stats->last_nc = log[nsteps - 1];
     stats->last_scale = log[2 * nsteps - 1];
@@ -1868,7 +1955,6 @@ void free_all(fv_trainer* tr) {
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
-  for (cudaEvent_t e : tr->phase_events) cudaEventDestroy(e);
   cudaEvent_t evs[] = {tr->ev_begin, tr->ev_end, tr->ev_copy[0], tr->ev_copy[1], tr->ev_used[0], tr->ev_used[1]};
   for (cudaEvent_t e : evs)
     if (e) cudaEventDestroy(e);
@@ -1910,6 +1996,18 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.XO = d.MO * (1 + d.has_delta);        // xx follows; every part stays 16-byte aligned
   d.P = d.XO + d.Kp;
   d.spin_limit = 8u << 20;  // ~10 s of polling with back-off
+  {
+    auto magic = [](uint32_t divisor, uint32_t* m, uint32_t* s) {
+      uint32_t l = 0;
+      while ((1ull << l) < divisor) ++l;
+      *s = 31 + l;
+      *m = (uint32_t)(((1ull << *s) + divisor - 1) / divisor);
+    };
+    magic((uint32_t)d.W, &d.mW, &d.sW);
+    magic((uint32_t)d.B, &d.mB, &d.sB);
+    magic((uint32_t)d.Kp, &d.mKp, &d.sKp);
+    magic((uint32_t)d.G, &d.mG, &d.sG);
+  }
   d.prec = cfg->prec;
   d.flags = cfg->flags;
   tr->NT = (d.Kq + 31) / 32;
@@ -1954,12 +2052,16 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
 
   // launch geometry: whole multiples of the SM count
   tr->fwd_smem = (size_t)d.Kp * sizeof(float);
-  tr->xx_smem = (size_t)XX_WARPS * d.Kp * sizeof(float);
-  tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + sizeof(uint32_t));
+  tr->xx_smem = (size_t)(XX_WARPS + 1) * d.Kp * sizeof(float);
+  tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + 2 * sizeof(uint32_t));
   tr->apply_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int));
   FV_CUDA(cudaFuncSetAttribute(k_xx, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
-  FV_CUDA(cudaFuncSetAttribute(k_tag<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
-  FV_CUDA(cudaFuncSetAttribute(k_tag<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
+  {
+    const size_t table_smem = (size_t)(2 * TAG_TABLE + 2 * 2 * XX_THREADS) * sizeof(uint32_t);
+    FV_CUDA(cudaFuncSetAttribute(k_tag<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
+    FV_CUDA(cudaFuncSetAttribute(k_tag<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(tr->xx_smem > table_smem ? tr->xx_smem : table_smem)));
+  }
   int fwd_bps = 0;
   cudaError_t oerr = cudaSuccess;
   FV_DISPATCH_NT(tr->NT, forward_occupancy, &fwd_bps, tr->fwd_smem, &oerr);
@@ -1980,7 +2082,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
     if (apply_bps > 4) apply_bps = 4;
     tr->apply_grid = grid_for(E, 256, tr->num_sms * apply_bps);
   }
-  FV_TRY(dev_alloc(&tr->d_xx_part, (size_t)tr->xx_grid * d.Kp));
+  FV_TRY(dev_alloc(&tr->d_xx_part, (size_t)8 * d.Kp));  // up to 8 xx CTAs
   FV_TRY(dev_alloc(&tr->d_aw, (size_t)d.B));
   d.xx_part = tr->d_xx_part;
   d.aw = tr->d_aw;
@@ -2002,6 +2104,8 @@ int fv_trainer_create(const fv_config* cfg, fv_trainer** out) {
   FV_REQUIRE(cfg->vocab >= 1 && cfg->vocab <= (1u << 29), FV_ERR_INVALID, "vocab out of range: %u", cfg->vocab);
   FV_REQUIRE(cfg->window >= 1 && cfg->window <= 32, FV_ERR_INVALID, "window must be in [1, 32], got %u", cfg->window);
   FV_REQUIRE(cfg->batch >= 1, FV_ERR_INVALID, "batch must be >= 1");
+  FV_REQUIRE((2ull * cfg->vocab + 1) * ((cfg->hid + 3ull) & ~3ull) < (1ull << 31), FV_ERR_INVALID,
+             "(2*vocab+1)*hid = %llu does not fit the 31-bit matrix position", (2ull * cfg->vocab + 1) * ((cfg->hid + 3ull) & ~3ull));
   FV_REQUIRE(cfg->world <= MAX_RANKS, FV_ERR_INVALID, "world must be at most %d", MAX_RANKS);
   FV_REQUIRE(cfg->world >= 1 && cfg->rank >= 0 && cfg->rank < cfg->world, FV_ERR_INVALID,
              "need world >= 1 and 0 <= rank < world (rank %d, world %d)", cfg->rank, cfg->world);
@@ -2464,6 +2568,7 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
     tr->d.peers = tr->d_peer_table;
     tr->d.shard = getenv("FV_SHARD") ? 1 : 0;  // sharded update: opt-in (see the mode table in the header)
     tr->comm_mode = 2;
+    tr->xx_grid = 8;  // the xx CTAs also carry the winners to the peers: one CTA per peer up to 8 ranks
   } else {
     for (int r = 0; r < G; ++r) {
       if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);

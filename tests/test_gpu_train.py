@@ -224,6 +224,45 @@ def test_inactive_rank_rows_are_dropped(built_lib):
     tr.close()
 
 
+@pytest.mark.parametrize("delta", [0.0, 0.5])
+def test_cancelled_unit_on_one_rank_leaves_the_counts(built_lib, delta):
+    """A unit that wins windows on a rank while its activations there add up to exactly zero is
+    inactive on that rank (cu_special_reduction.cu:42-66 tests xx != 0), so that rank's windows must
+    not count in the scatter term although another rank, active for the same unit, touches the same
+    matrix positions.  Rank 0 sees only tokens on which every weight is zero (unit 0 wins all ties
+    with activation 0, unit 1 comes second); rank 1 mixes them with tokens units 0 and 1 respond to."""
+    K, V, W, B = 8, 40, 3, 16
+    zs = np.arange(10, 28, dtype=np.int32)                      # 18 tokens -> 16 windows of silent tokens
+    mixed = np.empty(18, np.int32)
+    mixed[0::2] = 1 + np.arange(9) % 5                          # tokens units 0 and 1 respond to
+    mixed[1::2] = zs[:9]                                        # the same silent tokens as rank 0
+    enc = np.concatenate([zs, mixed])
+    off = np.array([0, 18, 36], np.uint64)
+    W0 = np.zeros((K, 2 * V), np.float32)
+    for blk in (0, V):
+        W0[0, blk + 1:blk + 6] = 1.0
+        W0[1, blk + 1:blk + 6] = 0.5
+    tr = Trainer(hid=K, vocab=V, window=W, batch=B, lr0=2e-4, delta=delta, world=2, flags=_lib.FV_FLAG_EMULATE_RANKS)
+    assert tr.set_corpus(enc, off) == 2 * B
+    tr.set_weights(W0)
+    eps = np.float32(2e-4)
+    win, xx, nc, s = tr.step_debug(0, eps)
+    starts = orc.enumerate_windows(off, W)
+    f = orc.inverse_word_frequency(enc, V, saturate_fp32=False)
+    idxs = [orc.build_idx(enc, starts, np.arange(g * B, (g + 1) * B, dtype=np.uint64), W, V) for g in range(2)]
+    Wref, info = orc.train_step(W0, idxs, f, V, eps, delta=delta)
+    assert info["xx"][0][0] == 0 and info["xx"][1][0] != 0 and (info["win"][0] == 0).all()
+    for g in range(2):
+        np.testing.assert_array_equal(win[g], info["win"][g])
+        np.testing.assert_allclose(xx[g], info["xx"][g], rtol=2e-5, atol=1e-9)
+    np.testing.assert_allclose(nc, info["nc"], rtol=1e-5)
+    assert rel_err(tr.get_weights(), Wref) < STEP_TOL
+    # the silent tokens of rank 0 must matter for the check: counting them changes the result
+    both, _ = orc.train_step(W0, [np.concatenate(idxs)], f, V, eps, delta=delta)
+    assert rel_err(both, Wref) > 5 * STEP_TOL
+    tr.close()
+
+
 @pytest.mark.parametrize("world", [1, 2])
 def test_anti_hebbian_second_winner(built_lib, world):
     """delta != 0: the second-largest unit gets -delta times the Hebbian terms
