@@ -51,7 +51,7 @@ struct StepCtl {
   uint32_t error;
   uint32_t wabsmax;       // bit pattern of an upper bound of max |wt|
   uint32_t wabsmax_fold;  // the same, collected while folding
-  uint32_t xx_ticket;     // CTAs of the running k_xx that have finished
+  int32_t xx_kexp;        // xx is accumulated in units of 2^-xx_kexp this step (written by k_forward)
   uint32_t fwd_next[2];   // window tickets k_forward hands out beyond the first round, by step parity
   uint32_t scan_ticket;   // CTAs of the running k_scan that have finished
   uint32_t apply_ticket;  // CTAs of the running k_apply that have finished their own slots
@@ -89,11 +89,14 @@ struct Dev {
   unsigned spin_limit;     // polls before a wait on a peer's flag gives up
   int shard;               // 1: rows i with i % G == rank are updated here, the rest arrives from their owners
   size_t outbox_off;       // word offset of the outbox [2][G*B*W] of (position, value) pairs inside the mailbox
-  float* aw;       // [B] weighted activation of each window's winner
-  float* xx_part;  // [k_xx CTAs][Kp] partial sums of xx
+  // xx accumulators [Kp]: fixed-point sums (high and low 32-bit digits, each in a 64-bit word) and the
+  // number of windows won; filled by k_forward, turned into floats and cleared by xx_finish
+  unsigned long long* xx_hi;
+  unsigned long long* xx_lo;
+  uint32_t* xx_wins;
+  float fmax;      // upper bound of the inverse frequencies (scales the fixed-point unit)
   int32_t* cnt;    // per record: later comers that add +f_i (first winner's row)
   int32_t* cntn;   // per record: later comers that add -delta*f_i (second winner's row); null without delta
-  float* aw2;      // [B] weighted activation of each window's second winner (with delta)
   uint4* rec;      // [G*B*w] touched-position records {position, parked weight bits, 1/count bits, 0}
   uint32_t* colmax;
   uint32_t* ncb;
@@ -102,19 +105,28 @@ struct Dev {
   float* s_log;
 };
 
-// Mailbox header (words).  Everything is indexed [parity][sender]; a flag holds the sequence number
-// (tick + local + 1) of the step whose data is complete.
+// Mailbox header (32-bit words).  Everything is indexed [parity][sender]; a flag holds the sequence
+// number (tick + local + 1) of the step whose data is complete.
 constexpr int MAX_RANKS = 16;
-constexpr int FLAG_PKT = 0;                    // the xx part of the packet delivered (the whole packet when it travels at once)
 // The partial normaliser and the outbox count travel inside their flag: one 64-bit word
 // (sequence number in the high half, payload in the low half) written with a single store.
 constexpr int WORD_NC = 2 * MAX_RANKS;         // u64 [2][MAX_RANKS]: seq | float bits of sender's partial nc
 constexpr int WORD_OUT = 6 * MAX_RANKS;        // u64 [2][MAX_RANKS]: seq | entries in sender's outbox
-constexpr int FLAG_WIN = 10 * MAX_RANKS;       // u32 [2][MAX_RANKS]: the winners part of the packet delivered
-constexpr int MAIL_HDR = 10 * MAX_RANKS + 96;  // 256 words, keeps the packets 1 KiB aligned
-// Packet of rank r for the step of the given parity: B winners, then (at XO) Kp floats of xx.
-__device__ __forceinline__ uint32_t* packet(const Dev& d, int parity, int r) {
-  return d.mail + MAIL_HDR + ((size_t)parity * d.G + r) * d.P;
+constexpr int MAIL_HDR = 512;                  // words; keeps the packets 2 KiB aligned
+// Packet of rank r for the step of the given parity: P 64-bit words -- B winners, (with delta) B
+// second winners at MO, Kp floats of xx at XO.  Every word carries its own flag: payload in the low
+// half, the step's sequence number in the high half, written with ONE 8-byte store, which arrives
+// whole.  A producer therefore stores a word straight into every peer's copy of its packet the
+// moment the value exists and never fences; a consumer reads the word and knows from the sequence
+// number whether it is this step's.
+__device__ __forceinline__ unsigned long long* packet(const Dev& d, int parity, int r) {
+  return reinterpret_cast<unsigned long long*>(d.mail + MAIL_HDR) + ((size_t)parity * d.G + r) * d.P;
+}
+__device__ __forceinline__ unsigned long long* peer_packet(const Dev& d, int peer, int parity, int r) {
+  return reinterpret_cast<unsigned long long*>(d.peers[peer] + MAIL_HDR) + ((size_t)parity * d.G + r) * d.P;
+}
+__device__ __forceinline__ unsigned long long pk_word(uint32_t payload, uint32_t seq) {
+  return ((unsigned long long)seq << 32) | payload;
 }
 
 __device__ __forceinline__ uint2* outbox(const Dev& d, const uint32_t* mail, int parity) {
@@ -137,16 +149,8 @@ __device__ __forceinline__ void phase_mark(StepCtl* c, uint32_t next) {
 // Message passing between GPUs.  Producer: payload stores, ONE system-scope fence by one thread,
 // then relaxed flag stores.  Consumer: relaxed polls of the flag (they are served by the local L2,
 // where a peer's store over NVLink lands), one acquire load once the flag matches.
-__device__ __forceinline__ void store_relaxed_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void store_relaxed_sys64(unsigned long long* p, unsigned long long v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t load_relaxed_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
 }
 __device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -166,14 +170,8 @@ __device__ __forceinline__ bool wait_expired(const Dev& d, unsigned& polls) {
   if (polls > 64) __nanosleep(128);
   return false;
 }
-// Bounded wait until flag == seq.  Returns false (and raises FV_DEVERR_TIMEOUT) when the limit
-// is reached or another wait already failed; no wait in this library spins without a limit.
-__device__ __forceinline__ bool wait_flag(const Dev& d, const uint32_t* flag, uint32_t seq) {
-  unsigned polls = 0;
-  while (load_relaxed_sys(flag) != seq)
-    if (wait_expired(d, polls)) return false;
-  return load_acquire_sys(flag) == seq;
-}
+// Bounded waits: they return false (and raise FV_DEVERR_TIMEOUT) when the limit is reached or another
+// wait already failed; no wait in this library spins without a limit.
 // Bounded wait for a {seq, payload} word; the payload needs no further ordering.
 __device__ __forceinline__ bool wait_word(const Dev& d, const unsigned long long* word, uint32_t seq, uint32_t* payload) {
   unsigned polls = 0;
@@ -185,6 +183,15 @@ __device__ __forceinline__ bool wait_word(const Dev& d, const unsigned long long
     }
     if (wait_expired(d, polls)) return false;
   }
+}
+
+// Payload of a packet word once it carries the step's sequence number (bounded wait; `fallback`
+// after a timeout, which also raises FV_DEVERR_TIMEOUT).  Words of this rank, and all words when
+// the packets travel by all-gather, are complete before the reading kernel starts.
+__device__ __forceinline__ uint32_t pk_read(const Dev& d, const unsigned long long* word, uint32_t seq, uint32_t fallback) {
+  uint32_t payload = fallback;
+  if (!wait_word(d, word, seq, &payload)) return fallback;
+  return payload;
 }
 
 // Programmatic dependent launch: a kernel launched with the stream-serialization
@@ -211,7 +218,6 @@ __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps, floa
   ctl->eps = eps;
   ctl->delta = delta;
   ctl->fwd_next[0] = ctl->fwd_next[1] = 0u;
-  ctl->xx_ticket = 0u;
   for (int i = 0; i < 8; ++i) ctl->phase_ns[i] = 0ull;
   ctl->t_mark = global_timer();
   ctl->phase_now = PH_OTHER;
@@ -422,8 +428,35 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   // with xmax replaced by the bound on |alpha * wt| kept in the control word.
   const float theta = 4.0f * (float)(d.W * d.W + 2 * d.W + 4) * 5.9604645e-8f * amax * __uint_as_float(d.ctl->wabsmax);
   const bool force64 = (d.flags & FV_FLAG_ACC_FP64) != 0;
+  // xx[mu] = sum of the winners' weighted activations (cuda_funcs.cu:722-744 adds them with float
+  // atomics in arbitrary order).  Here every window adds its term as a fixed-point number in units
+  // of 2^-kexp, two 32-bit digits in two 64-bit accumulators: integer addition commutes, so the sum
+  // does not depend on the order the windows finish in and repeats from run to run, and it is
+  // exact to 2^-32 of the unit.  The unit comes from a bound on any term,
+  // |term| <= max|alpha| * max|wt| * w * max f * max(1, |delta|), so that 2*B terms cannot overflow.
+  int kexp;
+  {
+    const double bound = (double)amax * (double)__uint_as_float(d.ctl->wabsmax) * (double)d.W * (double)d.fmax *
+                         fmax(1.0, fabs((double)d.ctl->delta)) * 2.0 * (double)d.B;
+    int e = (bound > 0.0 && bound < 1e300) ? ilogb(bound) + 1 : 0;  // bound < 2^e
+    e = max(-200, min(e, 200));
+    kexp = 92 - e;
+  }
+  const double xx_unit = ldexp(1.0, kexp);
+  if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->xx_kexp = kexp;
+  auto xx_add = [&](int mu, float term) {
+    const double q = (double)term * xx_unit;  // exact: the unit is a power of two
+    const double hi = floor(q * 2.3283064365386963e-10);  // q / 2^32
+    const long long lo = __double2ll_rn(q - hi * 4294967296.0);  // in [0, 2^32]
+    atomicAdd(d.xx_hi + mu, (unsigned long long)__double2ll_rn(hi));
+    atomicAdd(d.xx_lo + mu, (unsigned long long)lo);
+    atomicAdd(d.xx_wins + mu, 1u);
+  };
 
-  int32_t* __restrict__ win_out = reinterpret_cast<int32_t*>(packet(d, (int)((d.ctl->tick + local) & 1), d.rank));
+  // winners go into this rank's packet as flagged words; the tagging kernel forwards them to the peers
+  // (remote stores issued here would have to drain before this kernel can end)
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  unsigned long long* win_out = (lane == 0) ? packet(d, par, d.rank) : nullptr;
   const int zrow = d.N;  // the all-zero row
   const int nbatch = (d.W + 3) >> 2;
   int qc[NT];
@@ -542,185 +575,96 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
           second = exact_winner(d.wt, alpha, d.Kp, Kq, d.K, d.W, zrow, my, lane, winner);
         }
         const float aw2 = weighted_activation(d, alpha, my, second, lane);
-        if (lane == 0) {
-          win_out[d.MO + j] = second;
-          d.aw2[j] = aw2;
-        }
+        if (win_out) win_out[d.MO + j] = pk_word((uint32_t)second, seq);
+        if (lane == 0 && second >= 0) xx_add(second, -d.ctl->delta * aw2);  // cuda_funcs.cu:726-735
       }
     } else {
       jn = __shfl_sync(FULL, jn, 0);
       if (need_ticket) jlast = jn + 1;
       if (jn < d.B && lane < d.W) n_my = idx_own[(size_t)jn * d.W + lane];
     }
-    if (lane == 0) {
-      win_out[j] = winner;
-      d.aw[j] = awv;
-      if (d.has_delta && winner < 0) win_out[d.MO + j] = -1;
+    if (win_out) {
+      win_out[j] = pk_word((uint32_t)winner, seq);
+      if (d.has_delta && winner < 0) win_out[d.MO + j] = pk_word((uint32_t)-1, seq);
     }
+    if (lane == 0 && winner >= 0) xx_add(winner, awv);
     j = jn;
     my = n_my;
   }
 }
 
 // ---------------------------------------------------------------------------
-// xx[mu] = sum over this rank's windows won by mu of the weighted activation
-// (cuda_funcs.cu:722-744 does this with float atomics in arbitrary order; any order
-// is admissible, this one repeats from run to run).  CTA b takes a contiguous block
-// of windows, warp w of it a contiguous sub-block, 32 windows at a time: lanes with
-// the same winner are found with match.any, the lowest adds their activations in
-// lane order into the warp's private bin array.  Bins are added warp by warp, CTA
-// partials CTA by CTA (by the CTA that finishes last), and xx lands behind the
-// winners in the outgoing packet.
+// xx of this rank: one CTA turns the fixed-point sums k_forward left behind into floats, clears
+// the accumulators for the next step and puts xx behind the winners in this rank's packet -- and,
+// with peer mailboxes, straight into every peer's copy of it.
 //
-// A unit that won windows but whose activations add up to exactly zero counts as
-// inactive on this rank (cu_special_reduction.cu:42-66 tests xx != 0), yet its windows
-// exist; it is published as -0.0f so that consumers, which tag every window without
-// knowing xx, can take this rank's windows out again (k_scan).  Units that won nothing
-// are +0.0f.
+// A unit that won windows but whose activations add up to exactly zero counts as inactive on
+// this rank (cu_special_reduction.cu:42-66 tests xx != 0), yet its windows exist; it is published
+// as -0.0f so that consumers, which tag every window without knowing xx, can take this rank's
+// windows out again (k_scan).  Units that won nothing are +0.0f.
 // ---------------------------------------------------------------------------
 constexpr uint32_t XX_WON_ZERO = 0x80000000u;
 constexpr int XX_THREADS = 512;
 constexpr int XX_WARPS = XX_THREADS / 32;
 constexpr int TAG_TABLE_LOG2 = 11;
 constexpr int TAG_TABLE = 1 << TAG_TABLE_LOG2;  // shared-memory hash table, at most half full
-__device__ __forceinline__ void xx_body(const Dev& d, int local, int cta, int nctas, unsigned char* xx_smem) {
-  float* bins = reinterpret_cast<float*>(xx_smem);  // [XX_WARPS][Kp]
-  int* s_won = reinterpret_cast<int*>(bins + XX_WARPS * d.Kp);  // [Kp] the unit won a window of this CTA's block
-  __shared__ unsigned s_ticket;
-  const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+__device__ __forceinline__ void xx_finish(const Dev& d, int local) {
   const int parity = (int)((d.ctl->tick + local) & 1);
-  uint32_t* __restrict__ mine = packet(d, parity, d.rank);
-  const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(mine);
-  for (int i = threadIdx.x; i < (XX_WARPS + 1) * d.Kp; i += XX_THREADS) bins[i] = 0.f;  // s_won included
-  __syncthreads();
-  const int per_cta = (d.B + nctas - 1) / nctas;
-  const int per_warp = (per_cta + XX_WARPS - 1) / XX_WARPS;
-  const int lo = cta * per_cta + wic * per_warp;
-  const int hi = min(min(lo + per_warp, (cta + 1) * per_cta), d.B);
-  float* mybins = bins + wic * d.Kp;
-  constexpr int XX_PRE = 4;  // chunks of 32 windows whose loads are issued together
-  const float delta = d.ctl->delta;
-  for (int pass = 0; pass < 1 + d.has_delta; ++pass) {  // pass 1: the second winners, weighted by -delta (cuda_funcs.cu:726-735)
-  const int32_t* __restrict__ wsrc = pass ? win + d.MO : win;
-  const float* __restrict__ asrc = pass ? d.aw2 : d.aw;
-  for (int base0 = lo; base0 < hi; base0 += 32 * XX_PRE) {
-    int wv[XX_PRE];
-    float av[XX_PRE];
-#pragma unroll
-    for (int u = 0; u < XX_PRE; ++u) {
-      const int jw = base0 + 32 * u + lane;
-      wv[u] = (jw < hi) ? wsrc[jw] : -1;
-      av[u] = (jw < hi) ? asrc[jw] : 0.f;
-      if (pass) av[u] = -delta * av[u];
-    }
-#pragma unroll
-    for (int u = 0; u < XX_PRE; ++u) {
-      if (base0 + 32 * u >= hi) break;
-      const int w = wv[u];
-      const float a = av[u];
-      unsigned m = __match_any_sync(FULL, w);
-      const bool leader = (__ffs(m) - 1) == lane;
-      const int rounds = __reduce_max_sync(FULL, __popc(m));
-      float sum = 0.f;
-      for (int it = 0; it < rounds; ++it) {
-        const int src = m ? (__ffs(m) - 1) : 0;
-        const float v = __shfl_sync(FULL, a, src);
-        if (m) {
-          sum += v;
-          m &= m - 1;
-        }
-      }
-      if (leader && w >= 0) {
-        mybins[w] += sum;
-        s_won[w] = 1;
-      }
-      __syncwarp();
-    }
-  }
-  }  // pass
-  __syncthreads();
+  const bool mailbox = d.peers != nullptr && d.G > 1;
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const int kexp = d.ctl->xx_kexp;
   for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
-    float p = 0.f;
-#pragma unroll
-    for (int w = 0; w < XX_WARPS; ++w) p += bins[w * d.Kp + mu];
-    if (p == 0.f) p = __uint_as_float(s_won[mu] ? XX_WON_ZERO : 0u);
-    d.xx_part[(size_t)cta * d.Kp + mu] = p;
-  }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(&d.ctl->xx_ticket, 1u);
-  __syncthreads();
-  if (s_ticket == (unsigned)nctas - 1) {
-    __threadfence();
-    float* __restrict__ xx_out = reinterpret_cast<float*>(mine) + d.XO;
-    for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
-      float acc = 0.f;
-      if (mu < d.K) {
-        float part[8];  // nctas <= 8: fetch all partials, then add them in CTA order
-#pragma unroll
-        for (int c = 0; c < 8; ++c) part[c] = (c < nctas) ? __ldcg(d.xx_part + (size_t)c * d.Kp + mu) : 0.f;
-        bool won = false;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c < nctas) {
-            acc += part[c];
-            won = won || (__float_as_uint(part[c]) != 0u);
-          }
-        if (acc == 0.f) acc = __uint_as_float(won ? XX_WON_ZERO : 0u);
+    float x = 0.f;
+    if (mu < d.K) {
+      const long long hi = (long long)__ldcg(d.xx_hi + mu);
+      const unsigned long long lo = __ldcg(d.xx_lo + mu);
+      const uint32_t wins = __ldcg(d.xx_wins + mu);
+      if (wins) {
+        x = (float)(ldexp((double)hi, 32 - kexp) + ldexp((double)lo, -kexp));
+        if (x == 0.f) x = __uint_as_float(XX_WON_ZERO);
+        d.xx_hi[mu] = 0ull;
+        d.xx_lo[mu] = 0ull;
+        d.xx_wins[mu] = 0u;
       }
-      xx_out[mu] = acc;
     }
-    if (threadIdx.x == 0) {
-      d.ctl->xx_ticket = 0u;
-      d.ctl->fwd_next[parity] = 0u;  // rank emulation runs several forward passes per step
-    }
-    if (d.peers != nullptr && d.G > 1) {
-      // Exchange fused into the producer: push xx (the winners went ahead, push_winners) into every
-      // peer's mailbox over NVLink with plain stores, make the stores visible system-wide, then
-      // publish the step's sequence number in the peer's flag word.  The peers' k_scan polls it.
-      __syncthreads();
-      const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
-      const uint4* __restrict__ src4 = reinterpret_cast<const uint4*>(mine + d.XO);
-      const int n4 = d.Kp >> 2;
-      for (int i = threadIdx.x; i < n4 * d.G; i += XX_THREADS) {
-        const int r = i / n4;
-        if (r == d.rank) continue;
-        uint4* dst4 = reinterpret_cast<uint4*>(d.peers[r] + MAIL_HDR + ((size_t)parity * d.G + d.rank) * d.P + d.XO);
-        dst4[i - r * n4] = __ldcg(src4 + (i - r * n4));
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x < d.G && (int)threadIdx.x != d.rank)
-        store_relaxed_sys(d.peers[threadIdx.x] + FLAG_PKT + parity * MAX_RANKS + d.rank, seq);
+    const unsigned long long word = pk_word(__float_as_uint(x), seq);
+    if (mailbox) {
+      for (int r = 0; r < d.G; ++r) store_relaxed_sys64(peer_packet(d, r, parity, d.rank) + d.XO + mu, word);
+    } else {
+      packet(d, parity, d.rank)[d.XO + mu] = word;
     }
   }
+  if (threadIdx.x == 0) d.ctl->fwd_next[parity] = 0u;  // rank emulation runs several forward passes per step
 }
-// The winners of this rank's windows are final when k_forward ends.  xx CTA c copies them into the
-// mailboxes of peers c, c + nctas, ... (plain stores over NVLink), makes them visible with one
-// system-scope fence and raises the peers' FLAG_WIN word; the peers' tagging CTAs poll it.
-__device__ __forceinline__ void push_winners(const Dev& d, int local, int parity, int cta, int nctas) {
-  const uint4* __restrict__ src4 = reinterpret_cast<const uint4*>(packet(d, parity, d.rank));
-  const int n4 = d.XO >> 2;  // first and (with delta) second winners
-  for (int r = cta; r < d.G; r += nctas) {
-    if (r == d.rank) continue;
-    uint4* dst4 = reinterpret_cast<uint4*>(d.peers[r] + MAIL_HDR + ((size_t)parity * d.G + d.rank) * d.P);
-    for (int i = threadIdx.x; i < n4; i += XX_THREADS) dst4[i] = __ldcg(src4 + i);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
-    for (int r = cta; r < d.G; r += nctas)
-      if (r != d.rank) store_relaxed_sys(d.peers[r] + FLAG_WIN + parity * MAX_RANKS + d.rank, seq);
+// The winners of this rank's windows are final when k_forward ends.  Push CTA c of n copies its
+// slice of the flagged words into every peer's copy of this rank's packet: plain 8-byte stores over
+// NVLink, no fence and no separate flag -- every word announces itself.
+constexpr int PUSH_CTAS = 8;
+__device__ __forceinline__ void push_winners(const Dev& d, int parity, int cta, int nctas) {
+  const ulonglong2* __restrict__ src2 = reinterpret_cast<const ulonglong2*>(packet(d, parity, d.rank));
+  const int n2 = d.XO >> 1;  // first and (with delta) second winners, two words at a time
+  const int per = (n2 + nctas - 1) / nctas;
+  const int hi = min((cta + 1) * per, n2);
+  constexpr int PUSH_UNROLL = 4;  // loads of a thread in flight together
+  for (int i0 = cta * per + threadIdx.x; i0 < hi; i0 += PUSH_UNROLL * XX_THREADS) {
+    ulonglong2 v[PUSH_UNROLL];
+#pragma unroll
+    for (int u = 0; u < PUSH_UNROLL; ++u)
+      if (i0 + u * XX_THREADS < hi) v[u] = __ldcg(src2 + i0 + u * XX_THREADS);
+    for (int r = 0; r < d.G; ++r) {
+      if (r == d.rank) continue;
+      ulonglong2* dst2 = reinterpret_cast<ulonglong2*>(peer_packet(d, r, parity, d.rank));
+#pragma unroll
+      for (int u = 0; u < PUSH_UNROLL; ++u)
+        if (i0 + u * XX_THREADS < hi) dst2[i0 + u * XX_THREADS] = v[u];
+    }
   }
 }
 __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
   grid_dependency_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_XX);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
-  extern __shared__ __align__(16) unsigned char xx_smem[];
-  xx_body(d, local, blockIdx.x, gridDim.x, xx_smem);
+  xx_finish(d, local);
 }
 
 // ---------------------------------------------------------------------------
@@ -733,9 +677,9 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
 // skipped when its rank's xx[winner] is zero: the reference drops a replica's whole
 // row from the combine in that case (cu_special_reduction.cu:42-66).
 // ---------------------------------------------------------------------------
-// The first xx_ctas CTAs do not tag: they compute xx (xx_body) side by side with the tagging and,
-// with peer mailboxes, first send this rank's winners to the peers.  Tagging needs the winners of
-// all ranks but not xx, so it tags every (window, position); a unit that turns out inactive on all
+// The first xx_ctas CTAs (one) do not tag: they finish xx (xx_finish) side by side with the tagging;
+// with peer mailboxes the next push_ctas CTAs send this rank's winners to the peers.  Tagging needs
+// the winners of all ranks (a peer's arrive word by word once its forward pass has ended) but not xx, so it tags every (window, position); a unit that turns out inactive on all
 // ranks gets its parked weights back unchanged in k_apply, and the windows of a rank on which the
 // unit's xx cancelled to exactly zero are taken out of the counts again by k_scan.
 constexpr int TAG_CLAIMS = 2;  // compacted positions a thread claims per block round (UN == 2)
@@ -766,31 +710,21 @@ __device__ __forceinline__ void claim_position(const Dev& d, uint32_t pos, uint3
   }
 }
 template <int UN>  // slots per thread and block round: a CTA deduplicates UN * XX_THREADS slots together
-__global__ void __launch_bounds__(XX_THREADS, UN == 2 ? 3 : 1) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas) {
+__global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
   grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char tag_smem[];
   const int parity = (int)((d.ctl->tick + local) & 1);
-  const bool mailbox = d.peers != nullptr && d.G > 1;
   if ((int)blockIdx.x < xx_ctas) {
-    if (mailbox) push_winners(d, local, parity, blockIdx.x, xx_ctas);
-    xx_body(d, local, blockIdx.x, xx_ctas, tag_smem);
+    xx_finish(d, local);
     return;
   }
-  const bool marker = (int)blockIdx.x == xx_ctas && threadIdx.x == 0;
-  if (marker) phase_mark(d.ctl, mailbox ? PH_WAIT : PH_TAG);
-  if (mailbox) {
-    // wait (bounded) until every peer's winners of this step are in our mailbox
-    __shared__ int s_fail;
-    if (threadIdx.x == 0) s_fail = 0;
-    __syncthreads();
-    if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
-      const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
-      if (!wait_flag(d, d.mail + FLAG_WIN + parity * MAX_RANKS + threadIdx.x, seq)) s_fail = 1;
-    }
-    __syncthreads();
-    if (marker) phase_mark(d.ctl, PH_TAG);
-    if (s_fail) return;
+  const int svc = xx_ctas + push_ctas;  // CTAs that serve the exchange instead of tagging
+  if ((int)blockIdx.x < svc) {
+    push_winners(d, parity, blockIdx.x - xx_ctas, push_ctas);
+    return;
   }
+  if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
   // Stage 1: a block of TAG_BLOCK slots is deduplicated in a shared-memory hash table keyed by the
   // matrix position, so a (unit, token) pair that occurs many times in the block -- frequent tokens
   // do -- reaches global memory once, with its multiplicity.  Same-address global atomics complete
@@ -812,20 +746,22 @@ __global__ void __launch_bounds__(XX_THREADS, UN == 2 ? 3 : 1) k_tag(Dev d, int 
     const int kind = (ev >= E) ? 1 : 0;
     const uint32_t q = fdiv((uint32_t)(ev - kind * E), d.mW, d.sW);  // window of the global step
     const uint32_t r = fdiv(q, d.mB, d.sB);                          // its rank
-    return (int)packet(d, parity, (int)r)[kind * d.MO + (int)(q - r * (uint32_t)d.B)];
+    // a peer's winner may still be on its way: the word says so (bounded wait; -1 after a timeout)
+    return (int)pk_read(d, packet(d, parity, (int)r) + kind * d.MO + (int)(q - r * (uint32_t)d.B), seq, (uint32_t)-1);
   };
-  for (int blk = blockIdx.x - xx_ctas; blk < nblocks; blk += gridDim.x - xx_ctas) {
+  // every rank begins with the blocks of its own windows, whose winners are here already
+  const int first_blk = (int)(((long long)nblocks * d.rank) / d.G);
+  for (int b0 = blockIdx.x - svc; b0 < nblocks; b0 += gridDim.x - svc) {
+    const int blk = (b0 + first_blk) % nblocks;
     if constexpr (UN == 1) {
       // small steps: duplicates inside 512 slots are rare, so skip the table: number the live slots of
       // the CTA with a ballot/prefix (one counter bump per CTA round) and claim directly
+      // the winner's address does not depend on the id: both loads leave together
       const int ev = blk * TAG_BLOCK + threadIdx.x;
       const int i0 = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
-      bool go0 = i0 >= 0 && !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
-      int mu0 = -1;
-      if (go0) {
-        mu0 = winner_of(ev);
-        go0 = mu0 >= 0;
-      }
+      const int mu0 = (ev < EV) ? winner_of(ev) : -1;
+      const bool go0 = i0 >= 0 && mu0 >= 0 &&
+                       !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
       const uint32_t pos = (uint32_t)((size_t)(go0 ? i0 : 0) * d.Kp + (go0 ? mu0 : 0));
       uint32_t c0 = 0u;
       if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos);
@@ -859,11 +795,15 @@ __global__ void __launch_bounds__(XX_THREADS, UN == 2 ? 3 : 1) k_tag(Dev d, int 
         i[u] = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
       }
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
+      for (int u = 0; u < UN; ++u) {  // the winner's address does not depend on the id: all loads leave together
         const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+        mu[u] = (ev < EV) ? winner_of(ev) : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
         // sharded: another rank may own this row
         const bool go = i[u] >= 0 && !(d.shard && (int)((uint32_t)i[u] - fdiv((uint32_t)i[u], d.mG, d.sG) * (uint32_t)d.G) != d.rank);
-        mu[u] = go ? winner_of(ev) : -1;
+        if (!go) mu[u] = -1;
       }
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
@@ -929,11 +869,11 @@ __global__ void __launch_bounds__(XX_THREADS, UN == 2 ? 3 : 1) k_tag(Dev d, int 
 // Per-unit combine over ranks: n = number of ranks with xx != 0, X = mean of xx
 // over those ranks (the closed form of cu_special_reduction.cu:42-67 applied to
 // the -xx*W term).
-__device__ __forceinline__ void unit_stats(const Dev& d, int parity, int mu, double* X, int* n) {
+__device__ __forceinline__ void unit_stats(const Dev& d, int parity, uint32_t seq, int mu, double* X, int* n) {
   double sum = 0.0;
   int cnt = 0;
   for (int r = 0; r < d.G; ++r) {
-    const float x = __uint_as_float(packet(d, parity, r)[d.XO + mu]);
+    const float x = __uint_as_float(pk_read(d, packet(d, parity, r) + d.XO + mu, seq, 0u));
     if (x != 0.f) {
       sum += (double)x;
       ++cnt;
@@ -948,22 +888,22 @@ __device__ __forceinline__ void unit_stats(const Dev& d, int parity, int mu, dou
 __device__ __forceinline__ uint32_t unit_cancelled(const Dev& d, int parity, int mu) {
   uint32_t bad = 0u;
   for (int r = 0; r < d.G; ++r)
-    if (packet(d, parity, r)[d.XO + mu] == XX_WON_ZERO) bad |= 1u << r;
+    if ((uint32_t)packet(d, parity, r)[d.XO + mu] == XX_WON_ZERO) bad |= 1u << r;  // read after unit_stats: the word is there
   return bad;
 }
 // How often the windows of the ranks in `bad` asked for matrix row `irow` of unit mu, as first
 // winner (*np) and as second winner (*nn).  A plain search over those ranks' windows: this only
 // runs when activations cancel exactly on one rank while another rank is active for the unit.
 // (Scalars instead of the parameter block: a call by reference would put the block on the stack.)
-__device__ __noinline__ int2 cancelled_multiplicity(const uint32_t* __restrict__ packet0, int P, int G, int B, int W, int MO,
+__device__ __noinline__ int2 cancelled_multiplicity(const unsigned long long* __restrict__ packet0, int P, int G, int B, int W, int MO,
                                                     int has_delta, const int32_t* __restrict__ idx, int irow, int mu, uint32_t bad) {
   int a = 0, b = 0;
   for (int r = 0; r < G; ++r) {
     if (!((bad >> r) & 1u)) continue;
-    const int32_t* __restrict__ win = reinterpret_cast<const int32_t*>(packet0 + (size_t)r * P);
+    const unsigned long long* __restrict__ win = packet0 + (size_t)r * P;
     for (int j = 0; j < B; ++j) {
-      const bool first = win[j] == mu;
-      const bool second = has_delta && win[MO + j] == mu;
+      const bool first = (int)(uint32_t)win[j] == mu;
+      const bool second = has_delta && (int)(uint32_t)win[MO + j] == mu;
       if (!first && !second) continue;
       const int32_t* __restrict__ ids = idx + ((size_t)r * B + j) * W;
       for (int t = 0; t < W; ++t)
@@ -1006,25 +946,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   __shared__ int s_any_bad;
   if (threadIdx.x == 0) s_any_bad = 0;
   __syncthreads();
-  if (d.peers != nullptr && d.G > 1) {
-    // wait (bounded) until every peer's xx of this step is in our mailbox
-    const bool marker = blockIdx.x == 0 && threadIdx.x == 0;
-    if (marker) phase_mark(d.ctl, PH_WAIT);
-    __shared__ int s_fail;
-    if (threadIdx.x == 0) s_fail = 0;
-    __syncthreads();
-    if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
-      const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
-      if (!wait_flag(d, d.mail + FLAG_PKT + p * MAX_RANKS + threadIdx.x, seq)) s_fail = 1;
-    }
-    __syncthreads();
-    if (marker) phase_mark(d.ctl, PH_SCAN);
-    if (s_fail) return;
-  }
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
-    if (mu < d.K) unit_stats(d, p, mu, &X, &n);
+    if (mu < d.K) unit_stats(d, p, seq, mu, &X, &n);  // waits (bounded) for a peer's xx still on its way
     sC[mu] = X * alpha[mu];
     sN[mu] = n;
     sMax[mu] = 0u;
@@ -1039,7 +965,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   if (s_any_bad) {
     // some rank's windows for a unit do not count although the unit is active elsewhere: take them
     // out of this thread's records before anybody (here or in k_apply) reads the counts
-    const uint32_t* packet0 = packet(d, p, 0);
+    const unsigned long long* packet0 = packet(d, p, 0);
     for (int k = e0; k < nrec; k += nthreads) {
       const uint4 r = d.rec[k];
       if (r.w == 0u) continue;
@@ -1194,7 +1120,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
-    if (mu < d.K) unit_stats(d, p, mu, &X, &n);
+    if (mu < d.K) unit_stats(d, p, (uint32_t)(d.ctl->tick + local + 1), mu, &X, &n);
     sX[mu] = X;
     sN[mu] = n;
     if (n > 0) dense = fmaxf(dense, (float)(fabs(X * alpha[mu]) * (double)__uint_as_float(d.colmax[p * d.Kp + mu])));
@@ -1680,11 +1606,10 @@ struct fv_trainer {
   uint32_t* peer_mail[16] = {nullptr};      // peers' mailboxes mapped into this process
   uint32_t** d_peer_table = nullptr;
   int comm_mode = 0;                         // 0 none, 1 NCCL all-gather per step, 2 peer-memory mailboxes
-  float* d_xx_part = nullptr;
-  float* d_aw = nullptr;
+  unsigned long long* d_xx_acc = nullptr;  // xx_hi [Kp], xx_lo [Kp]
+  uint32_t* d_xx_wins = nullptr;
   int32_t* d_cnt = nullptr;
   int32_t* d_cntn = nullptr;
-  float* d_aw2 = nullptr;
   uint4* d_rec = nullptr;
   uint32_t* d_colmax = nullptr;
   uint32_t* d_ncb = nullptr;
@@ -1695,8 +1620,8 @@ struct fv_trainer {
   unsigned long long ticks = 0;  // host copy of StepCtl::tick
   float delta_now = 0.f;         // anti-Hebbian strength used by the next run_* call
   int tag_un = 1;
-  int fwd_grid = 0, xx_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
-  size_t fwd_smem = 0, xx_smem = 0, scan_smem = 0, apply_smem = 0;
+  int fwd_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
+  size_t fwd_smem = 0, scan_smem = 0, apply_smem = 0;
 };
 
 namespace {
@@ -1784,7 +1709,7 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, uint64_t* launch
     for (int r = 0; r < d.G; ++r) {
       tr->d.rank = r;
       FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
-      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, tr->d, local);
+      launch_pdl(k_xx, 1, XX_THREADS, (size_t)0, tr->stream, tr->d, local);
       *launches += 2;
     }
     tr->d.rank = own_rank;
@@ -1793,11 +1718,11 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, uint64_t* launch
     *launches += 1;
     if (tr->comm_mode == 1) {
       // k_xx finishes the packet, one all-gather delivers everybody's
-      launch_pdl(k_xx, tr->xx_grid, XX_THREADS, tr->xx_smem, tr->stream, d, local);
+      launch_pdl(k_xx, 1, XX_THREADS, (size_t)0, tr->stream, d, local);
       *launches += 1;
       const int parity = (int)((tr->ticks + (unsigned long long)local) & 1);
-      uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P;
-      const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P, base, (size_t)d.P, NCCL_UINT32, tr->comm, tr->stream);
+      uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P * 2;  // packets are P 64-bit words
+      const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P * 2, base, (size_t)d.P * 2, NCCL_UINT32, tr->comm, tr->stream);
       if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
     }
   }
@@ -1805,9 +1730,9 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, uint64_t* launch
   // (and, with mailboxes, push winners first and xx last); otherwise xx is complete already.
   const bool fused = single || (tr->comm_mode == 2 && !emulate);
   const size_t table_smem = tr->tag_un == 2 ? (size_t)(2 * TAG_TABLE + 2 * 2 * XX_THREADS) * sizeof(uint32_t) : 0;
-  const size_t tag_smem = (fused && tr->xx_smem > table_smem) ? tr->xx_smem : table_smem;
-  launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + (fused ? tr->xx_grid : 0), XX_THREADS, tag_smem, tr->stream, d, local,
-             idx, fused ? tr->xx_grid : 0);
+  const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
+  launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx,
+             xx_ctas, push_ctas);
   launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
   launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
   FV_CUDA(cudaGetLastError());
@@ -1951,7 +1876,7 @@ void free_all(fv_trainer* tr) {
     if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
-                  tr->d_mail, tr->d_peer_table, tr->d_xx_part, tr->d_aw, tr->d_aw2, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+                  tr->d_mail, tr->d_peer_table, tr->d_xx_acc, tr->d_xx_wins, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -1992,8 +1917,8 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.G = cfg->world;
   d.rank = cfg->rank;
   d.has_delta = (cfg->delta != 0.0f) ? 1 : 0;
-  d.MO = (d.B + 3) & ~3;                  // second winners (with delta) start here
-  d.XO = d.MO * (1 + d.has_delta);        // xx follows; every part stays 16-byte aligned
+  d.MO = (d.B + 3) & ~3;                  // second winners (with delta) start here (64-bit words)
+  d.XO = d.MO * (1 + d.has_delta);        // xx follows
   d.P = d.XO + d.Kp;
   d.spin_limit = 8u << 20;  // ~10 s of polling with back-off
   {
@@ -2016,13 +1941,12 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_TRY(dev_alloc(&tr->d_wt, ((size_t)d.N + 1) * d.Kp));  // one extra all-zero row for padding positions
   FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
-  d.outbox_off = (MAIL_HDR + 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
+  d.outbox_off = (MAIL_HDR + 2 * 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
   tr->mail_words = d.outbox_off + (d.G > 1 ? 2 * 2 * (size_t)d.G * d.B * d.W * (1 + d.has_delta) : 0);
   FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
   FV_TRY(dev_alloc(&tr->d_cnt, E));
   if (cfg->delta != 0.0f) {
     FV_TRY(dev_alloc(&tr->d_cntn, E));
-    FV_TRY(dev_alloc(&tr->d_aw2, (size_t)cfg->batch));
     FV_CUDA(cudaMemsetAsync(tr->d_cntn, 0, E * sizeof(int32_t), tr->stream));
   }
   FV_TRY(dev_alloc(&tr->d_rec, E));
@@ -2042,7 +1966,6 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.peers = nullptr;
   d.cnt = tr->d_cnt;
   d.cntn = tr->d_cntn;
-  d.aw2 = tr->d_aw2;
   d.rec = tr->d_rec;
   d.colmax = tr->d_colmax;
   d.ncb = tr->d_ncb;
@@ -2052,23 +1975,14 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
 
   // launch geometry: whole multiples of the SM count
   tr->fwd_smem = (size_t)d.Kp * sizeof(float);
-  tr->xx_smem = (size_t)(XX_WARPS + 1) * d.Kp * sizeof(float);
   tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + 2 * sizeof(uint32_t));
   tr->apply_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int));
-  FV_CUDA(cudaFuncSetAttribute(k_xx, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
-  {
-    const size_t table_smem = (size_t)(2 * TAG_TABLE + 2 * 2 * XX_THREADS) * sizeof(uint32_t);
-    FV_CUDA(cudaFuncSetAttribute(k_tag<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tr->xx_smem));
-    FV_CUDA(cudaFuncSetAttribute(k_tag<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)(tr->xx_smem > table_smem ? tr->xx_smem : table_smem)));
-  }
   int fwd_bps = 0;
   cudaError_t oerr = cudaSuccess;
   FV_DISPATCH_NT(tr->NT, forward_occupancy, &fwd_bps, tr->fwd_smem, &oerr);
   FV_CUDA(oerr);
   if (fwd_bps < 1) fwd_bps = 1;
   tr->fwd_grid = grid_for((size_t)d.B * 32, FWD_THREADS, tr->num_sms * fwd_bps);
-  tr->xx_grid = grid_for((size_t)d.B, 2048, 8);
   tr->scan_grid = tr->num_sms * 2;
   // small steps: one slot per thread keeps enough CTAs busy; large steps deduplicate 1024 slots per CTA
   tr->tag_un = (E >= (size_t)tr->num_sms * 4 * XX_THREADS) ? 2 : 1;
@@ -2082,10 +1996,14 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
     if (apply_bps > 4) apply_bps = 4;
     tr->apply_grid = grid_for(E, 256, tr->num_sms * apply_bps);
   }
-  FV_TRY(dev_alloc(&tr->d_xx_part, (size_t)8 * d.Kp));  // up to 8 xx CTAs
-  FV_TRY(dev_alloc(&tr->d_aw, (size_t)d.B));
-  d.xx_part = tr->d_xx_part;
-  d.aw = tr->d_aw;
+  FV_TRY(dev_alloc(&tr->d_xx_acc, 2 * (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_xx_wins, (size_t)d.Kp));
+  FV_CUDA(cudaMemsetAsync(tr->d_xx_acc, 0, 2 * (size_t)d.Kp * sizeof(unsigned long long), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_xx_wins, 0, (size_t)d.Kp * sizeof(uint32_t), tr->stream));
+  d.xx_hi = tr->d_xx_acc;
+  d.xx_lo = tr->d_xx_acc + d.Kp;
+  d.xx_wins = tr->d_xx_wins;
+  d.fmax = 1.0f;
   FV_CUDA(cudaMemsetAsync(tr->d_wt, 0, ((size_t)d.N + 1) * d.Kp * sizeof(float), tr->stream));
   FV_CUDA(cudaStreamSynchronize(tr->stream));
   return FV_OK;
@@ -2309,6 +2227,12 @@ int fv_trainer_set_inverse_frequency(fv_trainer* tr, const float* inv_freq) {
   FV_REQUIRE(tr && inv_freq, FV_ERR_INVALID, "fv_trainer_set_inverse_frequency: NULL argument");
   fv::DeviceGuard guard(tr->device);
   FV_CUDA(cudaMemcpy(tr->d_f, inv_freq, (size_t)tr->d.V * sizeof(float), cudaMemcpyHostToDevice));
+  float fmax = 0.f;
+  for (int v = 0; v < tr->d.V; ++v) {
+    FV_REQUIRE(std::isfinite(inv_freq[v]), FV_ERR_DATA, "inverse frequency %d is not finite", v);
+    fmax = std::max(fmax, std::fabs(inv_freq[v]));
+  }
+  tr->d.fmax = fmax;  // bounds the terms of xx (k_forward's fixed-point unit)
   return FV_OK;
 }
 
@@ -2429,12 +2353,17 @@ int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* win
   const Dev& d = tr->d;
   // the step just run had parity (ticks - 1) & 1
   const int parity = (int)((tr->ticks - 1) & 1);
-  std::vector<uint32_t> pkt((size_t)d.G * d.P);
-  FV_CUDA(cudaMemcpy(pkt.data(), tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P, pkt.size() * sizeof(uint32_t),
+  std::vector<unsigned long long> pkt((size_t)d.G * d.P);  // words: payload low, sequence number high
+  FV_CUDA(cudaMemcpy(pkt.data(), tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P * 2, pkt.size() * sizeof(unsigned long long),
                      cudaMemcpyDeviceToHost));
   for (int r = 0; r < d.G; ++r) {
-    if (winners) memcpy(winners + (size_t)r * d.B, pkt.data() + (size_t)r * d.P, (size_t)d.B * sizeof(int32_t));
-    if (xx) memcpy(xx + (size_t)r * d.K, pkt.data() + (size_t)r * d.P + d.XO, (size_t)d.K * sizeof(float));
+    if (winners)
+      for (int j = 0; j < d.B; ++j) winners[(size_t)r * d.B + j] = (int32_t)(uint32_t)pkt[(size_t)r * d.P + j];
+    if (xx)
+      for (int mu = 0; mu < d.K; ++mu) {
+        const uint32_t bits = (uint32_t)pkt[(size_t)r * d.P + d.XO + mu];
+        memcpy(xx + (size_t)r * d.K + mu, &bits, sizeof(float));
+      }
   }
   if (nc) *nc = nc1;
   if (scale) *scale = s1;
@@ -2451,12 +2380,19 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
   if (!tr->d_idx_stage[0]) FV_TRY(dev_alloc(&tr->d_idx_stage[0], step_ids * STAGE_STEPS));
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, step, 0.f, tr->delta_now);
   k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->stream>>>(d, step, 1, tr->d_idx_stage[0]);
-  // the kernel only writes winners and activations, so it can be repeated on the same step;
-  // alternating the parity lets each launch clear the ticket counter of the next
+  // the kernel only writes winners and adds to the xx accumulators, so it can be repeated on the same
+  // step; alternating the parity lets each launch clear the ticket counter of the next.  The launches
+  // keep their winners to this rank: a peer must not find words of a step that never ran.
+  uint32_t* const* const peers = tr->d.peers;
+  tr->d.peers = nullptr;
   for (uint32_t r = 0; r < 3; ++r) FV_DISPATCH_NT(tr->NT, launch_forward, tr, (int)(r & 1), tr->d_idx_stage[0]);
   FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   for (uint32_t r = 0; r < reps; ++r) FV_DISPATCH_NT(tr->NT, launch_forward, tr, (int)((r + 1) & 1), tr->d_idx_stage[0]);
   FV_CUDA(cudaEventRecord(tr->ev_end, tr->stream));
+  tr->d.peers = peers;
+  // no xx_finish ran: clear what the launches added to the accumulators
+  FV_CUDA(cudaMemsetAsync(tr->d_xx_acc, 0, 2 * (size_t)d.Kp * sizeof(unsigned long long), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_xx_wins, 0, (size_t)d.Kp * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaGetLastError());
   FV_CUDA(cudaStreamSynchronize(tr->stream));
   float ms = 0.f;
@@ -2568,7 +2504,6 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
     tr->d.peers = tr->d_peer_table;
     tr->d.shard = getenv("FV_SHARD") ? 1 : 0;  // sharded update: opt-in (see the mode table in the header)
     tr->comm_mode = 2;
-    tr->xx_grid = 8;  // the xx CTAs also carry the winners to the peers: one CTA per peer up to 8 ranks
   } else {
     for (int r = 0; r < G; ++r) {
       if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
