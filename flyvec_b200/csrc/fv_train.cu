@@ -741,13 +741,18 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
   constexpr int TAG_BLOCK = UN * XX_THREADS;
   const int nblocks = (EV + TAG_BLOCK - 1) / TAG_BLOCK;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
-  // winner of virtual slot ev (which must be < EV)
-  auto winner_of = [&](int ev) -> int {
+  // packet word with the winner of virtual slot ev (which must be < EV)
+  auto winner_word = [&](int ev) -> const unsigned long long* {
     const int kind = (ev >= E) ? 1 : 0;
     const uint32_t q = fdiv((uint32_t)(ev - kind * E), d.mW, d.sW);  // window of the global step
     const uint32_t r = fdiv(q, d.mB, d.sB);                          // its rank
-    // a peer's winner may still be on its way: the word says so (bounded wait; -1 after a timeout)
-    return (int)pk_read(d, packet(d, parity, (int)r) + kind * d.MO + (int)(q - r * (uint32_t)d.B), seq, (uint32_t)-1);
+    return packet(d, parity, (int)r) + kind * d.MO + (int)(q - r * (uint32_t)d.B);
+  };
+  // a peer's winner may still be on its way: the word says so (bounded wait; -1 after a timeout).
+  // `first` is the word as a plain load found it, so that several loads can be in flight together.
+  auto winner_from = [&](const unsigned long long* word, unsigned long long first) -> int {
+    if ((uint32_t)(first >> 32) == seq) return (int)(uint32_t)first;
+    return (int)pk_read(d, word, seq, (uint32_t)-1);
   };
   // every rank begins with the blocks of its own windows, whose winners are here already
   const int first_blk = (int)(((long long)nblocks * d.rank) / d.G);
@@ -759,7 +764,9 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       // the winner's address does not depend on the id: both loads leave together
       const int ev = blk * TAG_BLOCK + threadIdx.x;
       const int i0 = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
-      const int mu0 = (ev < EV) ? winner_of(ev) : -1;
+      const unsigned long long* ww = winner_word(ev < EV ? ev : 0);
+      const unsigned long long w0 = load_relaxed_sys64(ww);
+      const int mu0 = (ev < EV) ? winner_from(ww, w0) : -1;
       const bool go0 = i0 >= 0 && mu0 >= 0 &&
                        !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
       const uint32_t pos = (uint32_t)((size_t)(go0 ? i0 : 0) * d.Kp + (go0 ? mu0 : 0));
@@ -794,10 +801,18 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
         const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
         i[u] = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
       }
+      const unsigned long long* ww[UN];
+      unsigned long long w0[UN];
 #pragma unroll
       for (int u = 0; u < UN; ++u) {  // the winner's address does not depend on the id: all loads leave together
         const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-        mu[u] = (ev < EV) ? winner_of(ev) : -1;
+        ww[u] = winner_word(ev < EV ? ev : 0);
+        w0[u] = load_relaxed_sys64(ww[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+        mu[u] = (ev < EV) ? winner_from(ww[u], w0[u]) : -1;
       }
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
@@ -872,17 +887,28 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
 __device__ __forceinline__ void unit_stats(const Dev& d, int parity, uint32_t seq, int mu, double* X, int* n) {
   double sum = 0.0;
   int cnt = 0;
-  for (int r = 0; r < d.G; ++r) {
-    const float x = __uint_as_float(pk_read(d, packet(d, parity, r) + d.XO + mu, seq, 0u));
-    if (x != 0.f) {
-      sum += (double)x;
-      ++cnt;
+  constexpr int RB = 8;  // ranks whose words are fetched together
+  for (int r0 = 0; r0 < d.G; r0 += RB) {
+    unsigned long long w[RB];
+#pragma unroll
+    for (int u = 0; u < RB; ++u)
+      if (r0 + u < d.G) w[u] = load_relaxed_sys64(packet(d, parity, r0 + u) + d.XO + mu);
+#pragma unroll
+    for (int u = 0; u < RB; ++u) {
+      if (r0 + u >= d.G) break;
+      uint32_t bits = (uint32_t)w[u];
+      // a peer's xx may still be on its way: the word says so (bounded wait; 0 after a timeout)
+      if ((uint32_t)(w[u] >> 32) != seq) bits = pk_read(d, packet(d, parity, r0 + u) + d.XO + mu, seq, 0u);
+      const float x = __uint_as_float(bits);
+      if (x != 0.f) {
+        sum += (double)x;
+        ++cnt;
+      }
     }
   }
   *n = cnt;
   *X = cnt ? sum / (double)cnt : 0.0;
 }
-
 // Ranks (bit r) on which unit mu won windows although its xx is exactly zero: their windows were
 // tagged like all others and have to leave the counts again.
 __device__ __forceinline__ uint32_t unit_cancelled(const Dev& d, int parity, int mu) {
@@ -1986,7 +2012,9 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->scan_grid = tr->num_sms * 2;
   // small steps: one slot per thread keeps enough CTAs busy; large steps deduplicate 1024 slots per CTA
   tr->tag_un = (E >= (size_t)tr->num_sms * 4 * XX_THREADS) ? 2 : 1;
-  tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, tr->num_sms * 4);
+  // three CTAs fit an SM (registers); the grid stays resident together with the 1 + PUSH_CTAS CTAs that
+  // serve the exchange, so every CTA walks the same number of block rounds
+  tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, tr->num_sms * 3 - 1 - PUSH_CTAS);
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
   {
     // k_apply waits on peers inside the kernel (sharded update), so its grid must be fully resident
