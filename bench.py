@@ -267,7 +267,7 @@ def bench_train(args):
         "config": {"workload": "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000/GPU lr=2e-4 W0~N(0,1)",
                    "corpus_tokens": int(ntok), "windows": int(ns), "global_batch": world * B,
                    "parallelism": f"dp{world}",
-                   "exchange": {0: "none", 1: "nccl all-gather per step", 2: "peer-memory mailboxes"}[tr.comm_mode],
+                   "exchange": {0: "none", 1: "nccl all-gather per step", 2: "peer-memory mailboxes, flag-in-word packets"}[tr.comm_mode],
                    "l2": "inputs larger than L2: corpus + window tables (>0.6 GB) stream through; the 64 MB synapse "
                          "matrix is re-read every step by design"},
         "wall_ms_per_step": wall / steps * 1e3,
@@ -281,7 +281,7 @@ def bench_train(args):
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": FWD_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": fwd_bytes, "avg_launch_ms": fwd_avg * 1e3,
                      "note": "rows are gathered from the L2-resident matrix, so achieved can exceed the HBM figure"},
-        "phases_ms_per_step": {"forward": fwd_s / steps * 1e3, "xx+exchange": dist.max(st["exch_seconds"]) / steps * 1e3,
+        "phases_ms_per_step": {"forward": fwd_s / steps * 1e3, "xx kernel + all-gather (NCCL mode only; mailbox waits fall into update)": dist.max(st["exch_seconds"]) / steps * 1e3,
                                "update": dist.max(st["upd_seconds"]) / steps * 1e3},
         "step_algorithmic_gbs": step_bytes / (sec / steps) / 1e9,
         "last_nc": st["last_nc"],

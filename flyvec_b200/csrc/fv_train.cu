@@ -606,8 +606,8 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
 constexpr uint32_t XX_WON_ZERO = 0x80000000u;
 constexpr int XX_THREADS = 512;
 constexpr int XX_WARPS = XX_THREADS / 32;
-constexpr int TAG_TABLE_LOG2 = 11;
-constexpr int TAG_TABLE = 1 << TAG_TABLE_LOG2;  // shared-memory hash table, at most half full
+// shared-memory hash table of the tagging kernel: 2 * UN * XX_THREADS slots, at most half full
+constexpr size_t tag_table_bytes(int un) { return un > 1 ? (size_t)(2 * 2 * un + 2 * un) * XX_THREADS * sizeof(uint32_t) : 0; }
 __device__ __forceinline__ void xx_finish(const Dev& d, int local) {
   const int parity = (int)((d.ctl->tick + local) & 1);
   const bool mailbox = d.peers != nullptr && d.G > 1;
@@ -682,7 +682,6 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
 // the winners of all ranks (a peer's arrive word by word once its forward pass has ended) but not xx, so it tags every (window, position); a unit that turns out inactive on all
 // ranks gets its parked weights back unchanged in k_apply, and the windows of a rank on which the
 // unit's xx cancelled to exactly zero are taken out of the counts again by k_scan.
-constexpr int TAG_CLAIMS = 2;  // compacted positions a thread claims per block round (UN == 2)
 __device__ __forceinline__ void claim_position(const Dev& d, uint32_t pos, uint32_t c, uint32_t slot, uint32_t mult, uint32_t EV) {
   uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
   const uint32_t tag = TAG_BASE | (slot + 1u);
@@ -786,14 +785,20 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       __syncthreads();
       if (go0) claim_position(d, pos, c0, s_gbase + before + (uint32_t)__popc(live & ((1u << lane) - 1u)), ev >= E ? 0x10000u : 1u, (uint32_t)EV);
     } else {
+      constexpr int TAG_TABLE = 2 * TAG_BLOCK;
+      constexpr int TAG_TABLE_LOG2 = (UN == 2) ? 11 : 12;
+      static_assert(UN == 2 || UN == 4, "table sizes are worked out for 1024 and 2048 slots per block");
+      static_assert((1 << TAG_TABLE_LOG2) == TAG_TABLE, "table size");
       uint32_t* s_key = reinterpret_cast<uint32_t*>(tag_smem);           // [TAG_TABLE] position + 1, 0 = free
       uint32_t* s_cnt = s_key + TAG_TABLE;                               // [TAG_TABLE] two 16-bit multiplicities
       uint32_t* s_ckey = s_cnt + TAG_TABLE;                              // [TAG_BLOCK] compacted keys
       uint32_t* s_cmult = s_ckey + TAG_BLOCK;                            // [TAG_BLOCK] and their multiplicities
-      constexpr int PER = TAG_TABLE / XX_THREADS;
-      static_assert(PER == 4, "a thread owns one uint4 of the table");
-      reinterpret_cast<uint4*>(s_key)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
-      reinterpret_cast<uint4*>(s_cnt)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+      constexpr int NQ = TAG_TABLE / XX_THREADS / 4;  // uint4 groups of the table a thread owns
+#pragma unroll
+      for (int g = 0; g < NQ; ++g) {
+        reinterpret_cast<uint4*>(s_key)[threadIdx.x * NQ + g] = make_uint4(0u, 0u, 0u, 0u);
+        reinterpret_cast<uint4*>(s_cnt)[threadIdx.x * NQ + g] = make_uint4(0u, 0u, 0u, 0u);
+      }
       __syncthreads();
       int i[UN], mu[UN];
 #pragma unroll
@@ -829,17 +834,22 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
         for (;;) {
           const uint32_t old = atomicCAS(&s_key[h], 0u, key);
           if (old == 0u || old == key) {
-            atomicAdd(&s_cnt[h], ev >= E ? 0x10000u : 1u);  // a block has <= 1024 slots: 16 bits each suffice
+            atomicAdd(&s_cnt[h], ev >= E ? 0x10000u : 1u);  // a block has <= 2048 slots: 16 bits each suffice
             break;
           }
           h = (h + 1) & (TAG_TABLE - 1);
         }
       }
       __syncthreads();
-      // compaction: every thread owns PER consecutive table slots
-      const uint4 k4 = reinterpret_cast<const uint4*>(s_key)[threadIdx.x];
-      const uint4 c4 = reinterpret_cast<const uint4*>(s_cnt)[threadIdx.x];
-      const int occ = (k4.x != 0u) + (k4.y != 0u) + (k4.z != 0u) + (k4.w != 0u);
+      // compaction: every thread owns 4 * NQ consecutive table slots
+      uint4 k4[NQ], c4[NQ];
+      int occ = 0;
+#pragma unroll
+      for (int g = 0; g < NQ; ++g) {
+        k4[g] = reinterpret_cast<const uint4*>(s_key)[threadIdx.x * NQ + g];
+        c4[g] = reinterpret_cast<const uint4*>(s_cnt)[threadIdx.x * NQ + g];
+        occ += (k4[g].x != 0u) + (k4[g].y != 0u) + (k4[g].z != 0u) + (k4[g].w != 0u);
+      }
       int incl = occ;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -857,22 +867,24 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       }
       if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
       uint32_t at = before + (uint32_t)(incl - occ);
-      if (k4.x) { s_ckey[at] = k4.x; s_cmult[at] = c4.x; ++at; }
-      if (k4.y) { s_ckey[at] = k4.y; s_cmult[at] = c4.y; ++at; }
-      if (k4.z) { s_ckey[at] = k4.z; s_cmult[at] = c4.z; ++at; }
-      if (k4.w) { s_ckey[at] = k4.w; s_cmult[at] = c4.w; ++at; }
-      __syncthreads();
-      // claims: position tot is at most TAG_BLOCK = TAG_CLAIMS * XX_THREADS
-      static_assert(TAG_CLAIMS * XX_THREADS >= TAG_BLOCK, "every compacted position needs a claimant");
-      uint32_t key[TAG_CLAIMS], cur[TAG_CLAIMS];
 #pragma unroll
-      for (int u = 0; u < TAG_CLAIMS; ++u) {
+      for (int g = 0; g < NQ; ++g) {
+        if (k4[g].x) { s_ckey[at] = k4[g].x; s_cmult[at] = c4[g].x; ++at; }
+        if (k4[g].y) { s_ckey[at] = k4[g].y; s_cmult[at] = c4[g].y; ++at; }
+        if (k4[g].z) { s_ckey[at] = k4[g].z; s_cmult[at] = c4[g].z; ++at; }
+        if (k4[g].w) { s_ckey[at] = k4[g].w; s_cmult[at] = c4[g].w; ++at; }
+      }
+      __syncthreads();
+      // claims: at most TAG_BLOCK = UN * XX_THREADS compacted positions, UN per thread, loads together
+      uint32_t key[UN], cur[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
         const uint32_t cidx = (uint32_t)(u * XX_THREADS + threadIdx.x);
         key[u] = (cidx < tot) ? s_ckey[cidx] : 0u;
         cur[u] = key[u] ? __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + (key[u] - 1u)) : 0u;
       }
 #pragma unroll
-      for (int u = 0; u < TAG_CLAIMS; ++u) {
+      for (int u = 0; u < UN; ++u) {
         const uint32_t cidx = (uint32_t)(u * XX_THREADS + threadIdx.x);
         if (key[u]) claim_position(d, key[u] - 1u, cur[u], s_gbase + cidx, s_cmult[cidx], (uint32_t)EV);
       }
@@ -1755,7 +1767,7 @@ int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, uint64_t* launch
   // One rank, or peer mailboxes: the first CTAs of the tagging kernel compute xx beside the tagging
   // (and, with mailboxes, push winners first and xx last); otherwise xx is complete already.
   const bool fused = single || (tr->comm_mode == 2 && !emulate);
-  const size_t table_smem = tr->tag_un == 2 ? (size_t)(2 * TAG_TABLE + 2 * 2 * XX_THREADS) * sizeof(uint32_t) : 0;
+  const size_t table_smem = tag_table_bytes(tr->tag_un);
   const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
   launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx,
              xx_ctas, push_ctas);
@@ -2011,10 +2023,14 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->fwd_grid = grid_for((size_t)d.B * 32, FWD_THREADS, tr->num_sms * fwd_bps);
   tr->scan_grid = tr->num_sms * 2;
   // small steps: one slot per thread keeps enough CTAs busy; large steps deduplicate 1024 slots per CTA
-  tr->tag_un = (E >= (size_t)tr->num_sms * 4 * XX_THREADS) ? 2 : 1;
-  // three CTAs fit an SM (registers); the grid stays resident together with the 1 + PUSH_CTAS CTAs that
-  // serve the exchange, so every CTA walks the same number of block rounds
-  tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, tr->num_sms * 3 - 1 - PUSH_CTAS);
+  // Three CTAs fit an SM (registers); the grid stays resident together with the 1 + PUSH_CTAS CTAs that
+  // serve the exchange.  A CTA takes 512 slots per block round while one round covers the step, else
+  // 1024 deduplicated in shared memory (2048 per round measured no faster at 8 ranks).
+  {
+    const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS;
+    tr->tag_un = ((E + XX_THREADS - 1) / XX_THREADS > resident) ? 2 : 1;
+    tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, (int)resident);
+  }
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
   {
     // k_apply waits on peers inside the kernel (sharded update), so its grid must be fully resident
