@@ -71,9 +71,11 @@ typedef struct fv_run_stats {
   uint64_t steps;          /* global minibatch steps executed                  */
   uint64_t windows;        /* windows this rank processed                      */
   double seconds;          /* device time of the step loop (CUDA events)       */
-  double fwd_seconds;      /* time inside the fused gather/arg-max kernel      */
-  double exch_seconds;     /* xx build + cross-GPU exchange                    */
-  double upd_seconds;      /* scatter bookkeeping, abs-max scan, update        */
+  /* the next three come from a clock the kernels keep on the device (whole run) */
+  double fwd_seconds;      /* the fused gather/arg-max kernel                  */
+  double exch_seconds;     /* xx kernel + all-gather (comm mode 1 only)        */
+  double upd_seconds;      /* scatter bookkeeping (with any wait for a peer's
+                              words, comm mode 2), abs-max scan, update        */
   uint64_t kernel_launches;/* kernels of this library launched in the loop     */
   float last_nc;           /* normaliser of the last step                      */
   float last_scale;        /* eps / max(prec, nc) of the last step             */
@@ -160,7 +162,8 @@ int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* win
 
 /* Measurement aid: average duration of the fused gather/arg-max kernel (T4-T8 for this rank's block of
  * global step `step`) over `reps` back-to-back launches, timed with CUDA events on the trainer's stream.
- * The kernel only writes winners and activations, so repeating it leaves the weights untouched. */
+ * The kernel only writes winners and xx terms, so repeating it leaves the weights untouched; the launches keep
+ * their winners to this rank (nothing is sent to peers). */
 int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double* seconds_per_launch);
 
 /* Multi-GPU: one process per GPU.  Rank 0 draws an id, the caller ships the 128
@@ -169,11 +172,18 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
  * (cu_special_reduction.cu:61-66, 345-346). */
 int fv_comm_unique_id(uint8_t id[128]);
 int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
-/* How the ranks exchange their per-step packets: 0 = single rank / not initialised, 1 = one NCCL
- * all-gather per step, 2 = peer-memory mailboxes (the producing kernel stores its packet into every
- * peer's memory over NVLink and raises a flag; waits on those flags are bounded and end the call
- * with FV_ERR_TIMEOUT).  Mode 2 is chosen when every rank can map every other rank's mailbox;
- * the environment variable FV_COMM=nccl forces mode 1. */
+/* How the ranks exchange their per-step packets (B winners and K floats of xx per rank):
+ *   0  single rank / not initialised;
+ *   1  one NCCL all-gather per step;
+ *   2  peer-memory mailboxes: every packet word carries the step's sequence number beside its payload
+ *      and is written with one 8-byte store straight into every peer's memory over NVLink, so no
+ *      fence, flag or collective sits between the forward pass and the update; a consumer that finds
+ *      an old sequence number polls that word, every poll loop is bounded, and a peer that never
+ *      delivers ends the call with FV_ERR_TIMEOUT.
+ * Mode 2 is chosen when every rank can map every other rank's mailbox; the environment variable
+ * FV_COMM=nccl forces mode 1.  With FV_SHARD=1 (mode 2 only) each rank updates the matrix rows
+ * i % world == rank and pulls the other rows' new values from their owners; measured slower than the
+ * replicated update on 2 to 8 B200s, so it is off by default. */
 int fv_trainer_comm_mode(fv_trainer* tr, int* mode);
 /* Which windows of the current order rank `rank` owns in global step `step`
  * (cuda_funcs.cu:1667-1670); pure arithmetic, usable without a GPU. */
