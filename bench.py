@@ -311,11 +311,13 @@ def bench_hash(args, windows: bool):
         rng = np.random.default_rng(204)
         sel = rng.integers(0, len(starts), n)
         ids = build_idx_host(enc, starts, sel, W, V)
-        h.set_inverse_frequency(engine.inverse_frequency(enc, V))
+        inv_f = engine.inverse_frequency(enc, V)
+        h.set_inverse_frequency(inv_f)
         per_item = W * K * 4 + W * 4 + code_b
     else:
         n = args.items or 1_000_000
         ids = synth.make_hash_ids(n, V, seed=100)
+        inv_f = None
         # large batches go through the vocabulary table: an id in, a code gathered from the table and written out
         per_item = (4 + 2 * code_b) if n >= 4 * V else (K * 4 + code_b)
     d_in = engine.DeviceBuffer(ids.nbytes)
@@ -336,6 +338,10 @@ def bench_hash(args, windows: bool):
     else:
         h.hash_tokens(ids, hash_length=hl, packed=True)
     e2e = time.perf_counter() - t0
+    cpu = None
+    if not args.no_cpu_baseline:
+        cpu = cpu_hash_baseline(h.weights(), V, ids, hl, windows, h_f=inv_f,
+                                seconds_budget=args.cpu_seconds)
     out = {"metric": "hashed windows/sec" if windows else "hashed tokens/sec", "value": n / t,
            "unit": "windows/s" if windows else "tokens/s", "n_gpus": 1, "steps": len(times), "warmup": max(args.warmup, 3),
            "ms_per_step": t * 1e3, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
@@ -344,7 +350,38 @@ def bench_hash(args, windows: bool):
            "e2e": {"value": n / e2e, "unit": "items/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": n * code_b},
            "roofline": {"kernel": "k_hash", "bound": "hbm", "achieved": per_item * n / t / 1e9, "peak": peak,
                         "unit": "GB/s", "frac": per_item * n / t / 1e9 / peak, "traffic": None, "peak_source": peak_src}}
+    if cpu:
+        out["cpu_baseline"] = cpu
     print(json.dumps(out))
+
+
+def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_budget: float = 15.0):
+    """The oracle's numpy restatement of the reference's hashing rule on a bounded sample: for tokens the
+    per-token loop shaped like FlyVec.get_sparse_embedding (flyvec/core.py:139-163, one core) and its
+    vectorised form; for windows the weighted activation plus the same rule."""
+    from oracle import flyvec_oracle as orc
+
+    def timed(fn, items, first):
+        n, done, spent = first, 0, 0.0
+        while spent < seconds_budget / 2 and done < len(items):
+            part = items[done:done + n]
+            t0 = time.perf_counter()
+            fn(part)
+            spent += time.perf_counter() - t0
+            done += len(part)
+            n *= 2
+        return done / spent, done, spent
+
+    if windows:
+        rate, done, spent = timed(lambda part: orc.hash_windows(syn, V, part, h_f, hl), ids, 256)
+        return {"value": rate, "unit": "windows/s", "cores": 1, "kind": "port",
+                "sample": f"{done} windows of the same workload, numpy restatement, {spent:.1f} s"}
+    rate, done, spent = timed(lambda part: orc.hash_tokens(syn, V, part, hl), ids, 1024)
+    fast, done_f, spent_f = timed(lambda part: orc.hash_tokens_fast(syn, V, part, hl), ids, 8192)
+    return {"value": rate, "unit": "tokens/s", "cores": 1, "kind": "port",
+            "sample": f"{done} tokens of the same workload, per-token numpy loop shaped like the reference's "
+                      f"get_sparse_embedding, {spent:.1f} s",
+            "vectorised_numpy_tokens_per_s": fast, "vectorised_sample": f"{done_f} tokens, {spent_f:.1f} s"}
 
 
 # ----------------------------------------------------------------------------

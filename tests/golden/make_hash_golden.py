@@ -3,6 +3,7 @@
 Run from the repository root in a container that has the reference checkout:
 
     python tests/golden/make_hash_golden.py /path/to/reference
+    python tests/golden/make_hash_golden.py /path/to/reference --time   # only times the reference's hashing
 
 The reference's ``flyvec/core.py`` is imported unchanged.  Its third-party
 imports that are not needed for hashing (cached_property, fastcore, gensim,
@@ -79,10 +80,31 @@ class FakeTokenizer:
         return self.V
 
 
+def time_reference(FlyVec, normalize_synapses, n_tokens: int = 20000):
+    """Throughput of the reference's own per-token hashing on config-0 shapes (K=400, V=20000, hash_length 50),
+    one core, wherever this script runs (the reference checkout does not travel to a GPU box)."""
+    import time
+    from flyvec_b200 import synth
+
+    K, V = 400, 20000
+    model = FlyVec("unused.npy", "unused.dict", normalize_synapses=True)
+    model.__dict__["synapses"] = normalize_synapses(synth.make_weights(K, 2 * V, seed=1))
+    model.__dict__["tokenizer"] = FakeTokenizer(V)
+    words = [f"t{t}" for t in synth.make_hash_ids(n_tokens, V, seed=100)]
+    t0 = time.perf_counter()
+    for w in words:
+        model.get_sparse_embedding(w, hash_length=50)
+    dt = time.perf_counter() - t0
+    print(f"reference FlyVec.get_sparse_embedding: {n_tokens} tokens in {dt:.2f} s = {n_tokens / dt:.0f} tokens/s (1 core)")
+
+
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else "/root/reference"
     FlyVec, normalize_synapses = import_reference(ref_root)
     from flyvec_b200 import synth
+
+    if "--time" in sys.argv:
+        return time_reference(FlyVec, normalize_synapses)
 
     K, V, seed = 128, 300, 4242
     hash_lengths = np.array([1, 8, 50], dtype=np.int32)
