@@ -43,6 +43,7 @@ constexpr uint32_t TAG_BASE = 0x7f800000u;  // exponent all ones: tag = TAG_BASE
 constexpr uint32_t ABS_MASK = 0x7fffffffu;
 constexpr int MAX_K = 1024;
 
+constexpr int XX_SLOTS = 8;  // copies of the xx accumulators (spread by window index)
 struct StepCtl {
   unsigned long long base;  // schedule index of the step launched with local == 0
   unsigned long long tick;  // steps executed since the weights were last folded (selects the alpha buffer)
@@ -89,7 +90,7 @@ struct Dev {
   unsigned spin_limit;     // polls before a wait on a peer's flag gives up
   int shard;               // 1: rows i with i % G == rank are updated here, the rest arrives from their owners
   size_t outbox_off;       // word offset of the outbox [2][G*B*W] of (position, value) pairs inside the mailbox
-  // xx accumulators [Kp]: fixed-point sums (high and low 32-bit digits, each in a 64-bit word) and the
+  // xx accumulators [XX_SLOTS][Kp]: fixed-point sums (high and low 32-bit digits, each in a 64-bit word) and the
   // number of windows won; filled by k_forward, turned into floats and cleared by xx_finish
   unsigned long long* xx_hi;
   unsigned long long* xx_lo;
@@ -434,23 +435,44 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   // does not depend on the order the windows finish in and repeats from run to run, and it is
   // exact to 2^-32 of the unit.  The unit comes from a bound on any term,
   // |term| <= max|alpha| * max|wt| * w * max f * max(1, |delta|), so that 2*B terms cannot overflow.
-  int kexp;
-  {
+  __shared__ int s_kexp;
+  if (threadIdx.x == 0) {
     const double bound = (double)amax * (double)__uint_as_float(d.ctl->wabsmax) * (double)d.W * (double)d.fmax *
                          fmax(1.0, fabs((double)d.ctl->delta)) * 2.0 * (double)d.B;
     int e = (bound > 0.0 && bound < 1e300) ? ilogb(bound) + 1 : 0;  // bound < 2^e
     e = max(-200, min(e, 200));
-    kexp = 92 - e;
+    s_kexp = 92 - e;
+    if (blockIdx.x == 0) d.ctl->xx_kexp = 92 - e;
   }
-  const double xx_unit = ldexp(1.0, kexp);
-  if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->xx_kexp = kexp;
-  auto xx_add = [&](int mu, float term) {
-    const double q = (double)term * xx_unit;  // exact: the unit is a power of two
-    const double hi = floor(q * 2.3283064365386963e-10);  // q / 2^32
-    const long long lo = __double2ll_rn(q - hi * 4294967296.0);  // in [0, 2^32]
-    atomicAdd(d.xx_hi + mu, (unsigned long long)__double2ll_rn(hi));
-    atomicAdd(d.xx_lo + mu, (unsigned long long)lo);
-    atomicAdd(d.xx_wins + mu, 1u);
+  __syncthreads();
+  const int kexp = s_kexp;
+  // term * 2^kexp as an integer (round to nearest), split at 2^32 with the low digit in [0, 2^32):
+  // |term| = m * 2^(E - 150) with the 24-bit m of the float, so the product is m shifted by E - 150 + kexp
+  auto xx_add = [&](int mu, float term, int j) {
+    const uint32_t bits = __float_as_uint(term);
+    const int E = (int)((bits >> 23) & 0xffu);
+    const unsigned long long m = (bits & 0x007fffffu) | (E ? 0x00800000u : 0u);
+    const int sh = (E ? E : 1) - 150 + kexp;
+    unsigned long long hi = 0ull, lo = 0ull;  // |product| = hi * 2^32 + lo
+    if (sh >= 32) {
+      hi = (sh < 32 + 40) ? (m << (sh - 32)) : 0ull;  // m < 2^24 and the bound keep the product below 2^93
+    } else if (sh >= 0) {
+      const unsigned long long v = m << sh;  // < 2^56
+      hi = v >> 32;
+      lo = v & 0xffffffffull;
+    } else if (sh > -25) {
+      lo = (m + (1ull << (-sh - 1))) >> (-sh);
+    }
+    if (bits >> 31) {  // negative: floor at the split keeps the low digit non-negative
+      hi = lo ? ~hi : (0ull - hi);
+      lo = lo ? (0x100000000ull - lo) : 0ull;
+    }
+    // a popular unit wins hundreds of windows per step: XX_SLOTS copies of the accumulators, chosen
+    // by the window index, keep the reductions from queueing on one address
+    const int at = (j & (XX_SLOTS - 1)) * d.Kp + mu;
+    if (hi) atomicAdd(d.xx_hi + at, hi);
+    if (lo) atomicAdd(d.xx_lo + at, lo);
+    d.xx_wins[mu] = 1u;  // "won a window": the same value from everybody, a plain store will do
   };
 
   // winners go into this rank's packet as flagged words; the tagging kernel forwards them to the peers
@@ -576,7 +598,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
         }
         const float aw2 = weighted_activation(d, alpha, my, second, lane);
         if (win_out) win_out[d.MO + j] = pk_word((uint32_t)second, seq);
-        if (lane == 0 && second >= 0) xx_add(second, -d.ctl->delta * aw2);  // cuda_funcs.cu:726-735
+        if (lane == 0 && second >= 0) xx_add(second, -d.ctl->delta * aw2, j);  // cuda_funcs.cu:726-735
       }
     } else {
       jn = __shfl_sync(FULL, jn, 0);
@@ -587,7 +609,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
       win_out[j] = pk_word((uint32_t)winner, seq);
       if (d.has_delta && winner < 0) win_out[d.MO + j] = pk_word((uint32_t)-1, seq);
     }
-    if (lane == 0 && winner >= 0) xx_add(winner, awv);
+    if (lane == 0 && winner >= 0) xx_add(winner, awv, j);
     j = jn;
     my = n_my;
   }
@@ -616,14 +638,24 @@ __device__ __forceinline__ void xx_finish(const Dev& d, int local) {
   for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
     float x = 0.f;
     if (mu < d.K) {
-      const long long hi = (long long)__ldcg(d.xx_hi + mu);
-      const unsigned long long lo = __ldcg(d.xx_lo + mu);
       const uint32_t wins = __ldcg(d.xx_wins + mu);
       if (wins) {
-        x = (float)(ldexp((double)hi, 32 - kexp) + ldexp((double)lo, -kexp));
+        unsigned long long h[XX_SLOTS], l[XX_SLOTS];
+#pragma unroll
+        for (int s = 0; s < XX_SLOTS; ++s) {
+          h[s] = __ldcg(d.xx_hi + s * d.Kp + mu);
+          l[s] = __ldcg(d.xx_lo + s * d.Kp + mu);
+        }
+        unsigned long long hi = 0ull, lo = 0ull;  // integer sums: any order gives the same result
+#pragma unroll
+        for (int s = 0; s < XX_SLOTS; ++s) {
+          hi += h[s];
+          lo += l[s];
+          d.xx_hi[s * d.Kp + mu] = 0ull;
+          d.xx_lo[s * d.Kp + mu] = 0ull;
+        }
+        x = (float)(ldexp((double)(long long)hi, 32 - kexp) + ldexp((double)lo, -kexp));
         if (x == 0.f) x = __uint_as_float(XX_WON_ZERO);
-        d.xx_hi[mu] = 0ull;
-        d.xx_lo[mu] = 0ull;
         d.xx_wins[mu] = 0u;
       }
     }
@@ -2040,12 +2072,12 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
     if (apply_bps > 4) apply_bps = 4;
     tr->apply_grid = grid_for(E, 256, tr->num_sms * apply_bps);
   }
-  FV_TRY(dev_alloc(&tr->d_xx_acc, 2 * (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_xx_acc, 2 * (size_t)XX_SLOTS * d.Kp));
   FV_TRY(dev_alloc(&tr->d_xx_wins, (size_t)d.Kp));
-  FV_CUDA(cudaMemsetAsync(tr->d_xx_acc, 0, 2 * (size_t)d.Kp * sizeof(unsigned long long), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_xx_acc, 0, 2 * (size_t)XX_SLOTS * d.Kp * sizeof(unsigned long long), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_xx_wins, 0, (size_t)d.Kp * sizeof(uint32_t), tr->stream));
   d.xx_hi = tr->d_xx_acc;
-  d.xx_lo = tr->d_xx_acc + d.Kp;
+  d.xx_lo = tr->d_xx_acc + (size_t)XX_SLOTS * d.Kp;
   d.xx_wins = tr->d_xx_wins;
   d.fmax = 1.0f;
   FV_CUDA(cudaMemsetAsync(tr->d_wt, 0, ((size_t)d.N + 1) * d.Kp * sizeof(float), tr->stream));
@@ -2435,7 +2467,7 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
   FV_CUDA(cudaEventRecord(tr->ev_end, tr->stream));
   tr->d.peers = peers;
   // no xx_finish ran: clear what the launches added to the accumulators
-  FV_CUDA(cudaMemsetAsync(tr->d_xx_acc, 0, 2 * (size_t)d.Kp * sizeof(unsigned long long), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_xx_acc, 0, 2 * (size_t)XX_SLOTS * d.Kp * sizeof(unsigned long long), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_xx_wins, 0, (size_t)d.Kp * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaGetLastError());
   FV_CUDA(cudaStreamSynchronize(tr->stream));
