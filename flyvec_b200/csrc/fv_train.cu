@@ -274,12 +274,16 @@ __global__ void __launch_bounds__(256) k_build_idx_block(Dev d, unsigned long lo
   }
 }
 
-// Checks host-supplied input ids (streaming mode) against [ -2, N ).
-__global__ void k_check_idx(Dev d, const int32_t* __restrict__ idx, size_t total) {
+// Checks host-supplied input ids (streaming mode) against [ -2, N ); an id outside is reported and
+// replaced by padding, so that no later kernel forms an address from it.
+__global__ void k_check_idx(Dev d, int32_t* __restrict__ idx, size_t total) {
   grid_dependency_wait();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
     const int v = idx[e];
-    if (v >= d.N || v < -2) atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
+    if (v >= d.N || v < -2) {
+      atomicOr(&d.ctl->error, FV_DEVERR_TOKEN_RANGE);
+      idx[e] = -1;
+    }
   }
 }
 
