@@ -294,6 +294,30 @@ def bench_train(args):
         print(json.dumps(out))
 
 
+def bench_update_emulated(args):
+    """The replicated update (count, scan, apply) of `--emulate-ranks G` ranks' windows on ONE GPU: every rank's
+    forward pass runs in turn, then one update over all G*B windows, exactly what each GPU of a G-GPU job does
+    after the exchange.  For profiling the update kernels at multi-GPU sizes without a multi-GPU box."""
+    from flyvec_b200 import _lib, engine, synth
+
+    K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
+    G = args.emulate_ranks
+    enc, off = synth.make_corpus(args.tokens or 12_000_000, V, s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=W,
+                                 seed=CORPUS_SEED)
+    tr = engine.Trainer(hid=K, vocab=V, window=W, batch=B, lr0=CFG["lr"], world=G,
+                        flags=_lib.FV_FLAG_EMULATE_RANKS if G > 1 else 0)
+    tr.set_corpus(enc, off)
+    tr.set_weights(synth.make_weights(K, 2 * V, seed=WEIGHT_SEED))
+    tr.shuffle(PERM_SEED)
+    eps = np.float32(CFG["lr"])
+    tr.run_steps(0, args.warmup, eps)
+    st = tr.run_steps(args.warmup, args.steps, eps)
+    print(json.dumps({"metric": "update of G ranks' windows on one GPU (emulated ranks)", "ranks": G, "steps": args.steps,
+                      "us_per_step": st["seconds"] / args.steps * 1e6, "update_us_per_step": st["upd_seconds"] / args.steps * 1e6,
+                      "forward_us_per_step_all_ranks": st["fwd_seconds"] / args.steps * 1e6,
+                      "config": {"workload": f"config 1 shapes, {G} x {B} windows per step"}}))
+
+
 def bench_hash(args, windows: bool):
     """Device-resident and end-to-end throughput of the token / window hasher."""
     from flyvec_b200 import engine, synth
@@ -448,6 +472,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["train", "hash_tokens", "hash_windows"], default="train")
+    ap.add_argument("--emulate-ranks", type=int, default=0,
+                    help="one GPU: time the update of this many ranks' windows (profiling aid, not a bench line)")
     ap.add_argument("--tokens", type=int, default=0, help="corpus size (default 50M per GPU, at most 400M)")
     ap.add_argument("--items", type=int, default=0, help="hash workloads: number of tokens / windows")
     ap.add_argument("--hash-length", type=int, default=50)
@@ -458,6 +484,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return bench_reference(args)
+    if args.emulate_ranks:
+        return bench_update_emulated(args)
     if args.workload == "train":
         return bench_train(args)
     return bench_hash(args, windows=(args.workload == "hash_windows"))
