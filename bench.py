@@ -34,7 +34,7 @@ CORPUS_SEED, WEIGHT_SEED, PERM_SEED = 101, 1, 201
 # DRAM bytes (read + write) of one k_forward launch at config-1 shapes inside the running step loop, from the
 # ncu capture summarised in profiles/train_step_config1.md (caches as the pipeline leaves them); with ncu's
 # cache flush before the launch the same kernel reads 27.4 MB.
-FWD_DRAM_TRAFFIC_BYTES = 1.8e6
+FWD_DRAM_TRAFFIC_BYTES = 2.0e6
 
 
 # ----------------------------------------------------------------------------
