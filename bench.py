@@ -239,14 +239,15 @@ def bench_train(args):
     first = (warmup + steps) * world * B
     if first + e2e_steps * world * B > ns:
         first = 0
-    sel = perm[first:first + e2e_steps * world * B]
-    pinned = _lib.pinned_empty((e2e_steps, world * B, W), np.int32)
-    pinned[...] = build_idx_host(enc, starts, sel, W, V).reshape(e2e_steps, world * B, W)
+    # every rank feeds only its own windows (rank r's block of each global step); the ranks' ids meet on the GPUs
+    sel = perm[first:first + e2e_steps * world * B].reshape(e2e_steps, world, B)[:, rank, :].reshape(-1)
+    pinned = _lib.pinned_empty((e2e_steps, B, W), np.int32)
+    pinned[...] = build_idx_host(enc, starts, sel, W, V).reshape(e2e_steps, B, W)
     nc_host = _lib.pinned_empty((e2e_steps,), np.float32)
-    tr.run_steps_host(pinned[:min(8, e2e_steps)], min(8, e2e_steps), eps)  # warm the staging buffers
+    tr.run_steps_host_local(pinned[:min(8, e2e_steps)], min(8, e2e_steps), eps)  # warm the staging buffers
     dist.barrier()
     t0 = time.perf_counter()
-    tr.run_steps_host(pinned, e2e_steps, eps, nc_out=nc_host)
+    tr.run_steps_host_local(pinned, e2e_steps, eps, nc_out=nc_host)
     e2e_wall = dist.max(time.perf_counter() - t0)
     e2e_value = e2e_steps * world * B / e2e_wall
 
@@ -274,8 +275,9 @@ def bench_train(args):
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "windows/s", "h2d_bytes_per_step": world * B * W * 4,
                 "d2h_bytes_per_step": 4, "steps": e2e_steps,
-                "what": "fv_trainer_run_steps_host: input ids uploaded from pinned host memory inside the call, "
-                        "per-step normaliser copied back"},
+                "what": "fv_trainer_run_steps_host_local: every rank uploads the input ids of its own windows from pinned host "
+                        "memory inside the call (all-gathered over NVLink when there are several ranks), per-step "
+                        "normaliser copied back"},
         "gpu_launches": int(st["kernel_launches"]),
         "roofline": {"kernel": "k_forward (fused gather-sum + arg-max)", "bound": "hbm", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": FWD_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,

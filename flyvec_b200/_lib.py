@@ -85,6 +85,7 @@ _PROTOTYPES = {
     "fv_trainer_run_epoch": ([_P, C.c_uint64, C.c_uint64, C.POINTER(FvRunStats)], C.c_int),
     "fv_trainer_run_steps": ([_P, C.c_uint64, C.c_uint64, C.c_float, _P, _P, C.POINTER(FvRunStats)], C.c_int),
     "fv_trainer_run_steps_host": ([_P, _P, C.c_uint64, C.c_float, _P, _P, C.POINTER(FvRunStats)], C.c_int),
+    "fv_trainer_run_steps_host_local": ([_P, _P, C.c_uint64, C.c_float, _P, _P, C.POINTER(FvRunStats)], C.c_int),
     "fv_trainer_step_debug": ([_P, C.c_uint64, C.c_float, _P, _P, C.POINTER(C.c_float), C.POINTER(C.c_float)],
                               C.c_int),
     "fv_trainer_time_forward": ([_P, C.c_uint64, C.c_uint32, C.POINTER(C.c_double)], C.c_int),

@@ -74,6 +74,7 @@ struct Dev {
   int K, Kp, Kq, V, N, W, B, G, rank, P, XO;  // P = packet words, XO = offset of xx inside a packet
   // exact n / divisor for n < 2^31 as (n * m) >> s (64-bit product): m = ceil(2^s / divisor), s = 31 + ceil(log2 divisor)
   uint32_t mW, sW, mB, sB, mKp, sKp, mG, sG;
+  int idx_rstride; // ids of a step: rank r's block of B*W ids starts r * idx_rstride elements into the step's buffer
   int MO;          // offset of the second winners inside a packet (only with delta != 0)
   int has_delta;   // the anti-Hebbian term is on: every window also names its m-th (second) winner
   unsigned long long Ns, ntok;
@@ -135,6 +136,11 @@ __device__ __forceinline__ uint2* outbox(const Dev& d, const uint32_t* mail, int
 }
 __device__ __forceinline__ uint32_t fdiv(uint32_t n, uint32_t m, uint32_t s) {
   return (uint32_t)(((unsigned long long)n * m) >> s);
+}
+// Input id of slot e = (rank, window, position) of a step whose ranks' blocks lie idx_rstride apart.
+__device__ __forceinline__ int step_id(const Dev& d, const int32_t* __restrict__ idx, int e) {
+  const uint32_t r = fdiv(fdiv((uint32_t)e, d.mW, d.sW), d.mB, d.sB);
+  return idx[(size_t)e + (size_t)r * (size_t)(d.idx_rstride - d.B * d.W)];
 }
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
@@ -414,7 +420,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   const int nwarps = gridDim.x * FWD_WARPS;
   const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
   const int Kq = d.Kq;
-  const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.B * d.W;
+  const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.idx_rstride;
 
   // tickets: this launch draws from the counter of its parity and clears the other one, so that
   // consecutive launches need nobody else to reset anything
@@ -798,7 +804,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       // the CTA with a ballot/prefix (one counter bump per CTA round) and claim directly
       // the winner's address does not depend on the id: both loads leave together
       const int ev = blk * TAG_BLOCK + threadIdx.x;
-      const int i0 = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
+      const int i0 = (ev < EV) ? step_id(d, idx, ev >= E ? ev - E : ev) : -1;
       const unsigned long long* ww = winner_word(ev < EV ? ev : 0);
       const unsigned long long w0 = load_relaxed_sys64(ww);
       const int mu0 = (ev < EV) ? winner_from(ww, w0) : -1;
@@ -840,7 +846,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
         const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-        i[u] = (ev < EV) ? idx[ev >= E ? ev - E : ev] : -1;
+        i[u] = (ev < EV) ? step_id(d, idx, ev >= E ? ev - E : ev) : -1;
       }
       const unsigned long long* ww[UN];
       unsigned long long w0[UN];
@@ -970,7 +976,8 @@ __device__ __forceinline__ uint32_t unit_cancelled(const Dev& d, int parity, int
 // runs when activations cancel exactly on one rank while another rank is active for the unit.
 // (Scalars instead of the parameter block: a call by reference would put the block on the stack.)
 __device__ __noinline__ int2 cancelled_multiplicity(const unsigned long long* __restrict__ packet0, int P, int G, int B, int W, int MO,
-                                                    int has_delta, const int32_t* __restrict__ idx, int irow, int mu, uint32_t bad) {
+                                                    int has_delta, const int32_t* __restrict__ idx, int rstride, int irow, int mu,
+                                                    uint32_t bad) {
   int a = 0, b = 0;
   for (int r = 0; r < G; ++r) {
     if (!((bad >> r) & 1u)) continue;
@@ -979,7 +986,7 @@ __device__ __noinline__ int2 cancelled_multiplicity(const unsigned long long* __
       const bool first = (int)(uint32_t)win[j] == mu;
       const bool second = has_delta && (int)(uint32_t)win[MO + j] == mu;
       if (!first && !second) continue;
-      const int32_t* __restrict__ ids = idx + ((size_t)r * B + j) * W;
+      const int32_t* __restrict__ ids = idx + (size_t)r * rstride + (size_t)j * W;
       for (int t = 0; t < W; ++t)
         if (ids[t] == irow) {
           a += first;
@@ -1046,7 +1053,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
       const int irow = (int)fdiv(r.x, d.mKp, d.sKp);
       const int mu = (int)r.x - irow * d.Kp;
       if (!sBad[mu]) continue;
-      const int2 c = cancelled_multiplicity(packet0, d.P, d.G, d.B, d.W, d.MO, d.has_delta, idx, irow, mu, sBad[mu]);
+      const int2 c = cancelled_multiplicity(packet0, d.P, d.G, d.B, d.W, d.MO, d.has_delta, idx, d.idx_rstride, irow, mu, sBad[mu]);
       if (c.x) d.cnt[k] -= c.x;
       if (c.y) d.cntn[k] -= c.y;
     }
@@ -1675,6 +1682,7 @@ struct fv_trainer {
   unsigned long long* d_perm = nullptr;
   float* d_f = nullptr;
   int32_t* d_idx_stage[2] = {nullptr, nullptr};
+  int32_t* d_idx_local[2] = {nullptr, nullptr};  // this rank's ids of a chunk before the all-gather (rank-local host feed)
   uint32_t* d_mail = nullptr;               // local mailbox (flags + packets)
   size_t mail_words = 0;
   uint32_t* peer_mail[16] = {nullptr};      // peers' mailboxes mapped into this process
@@ -1830,8 +1838,10 @@ int ensure_log(fv_trainer* tr, size_t nsteps) {
 // The step loop.  idx_host == nullptr: ids are built on the GPU from the corpus
 // and the current order.  Otherwise they are uploaded in chunks of STAGE_STEPS
 // steps on a second stream, two chunks in flight.
+// idx_local: idx_host holds only this rank's windows (nsteps * batch of them); the ranks' blocks of a
+// chunk are then all-gathered over NVLink on the second stream, so every rank uploads 1/world of the ids.
 int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long long nsteps, float eps,
-                   const int32_t* idx_host, float* nc_out, float* scale_out, fv_run_stats* stats) {
+                   const int32_t* idx_host, bool idx_local, float* nc_out, float* scale_out, fv_run_stats* stats) {
   FV_REQUIRE(tr->have_weights, FV_ERR_STATE, "trainer has no weights: call fv_trainer_set_weights first");
   if (!idx_host) FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus: call fv_trainer_set_corpus first");
   if (tr->d.G > 1 && !(tr->d.flags & FV_FLAG_EMULATE_RANKS))
@@ -1848,11 +1858,19 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
 
   for (int b = 0; b < 2; ++b)
     if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
+  const bool gather_ids = idx_host && idx_local && d.G > 1 && !(d.flags & FV_FLAG_EMULATE_RANKS);
+  if (idx_host && idx_local && d.G > 1 && !gather_ids)
+    return fv::fail(FV_ERR_INVALID, "rank-local ids need real ranks: with FV_FLAG_EMULATE_RANKS pass all ranks' ids");
+  const size_t own_ids = (size_t)d.B * d.W;
+  for (int b = 0; b < 2 && gather_ids; ++b)
+    if (!tr->d_idx_local[b]) FV_TRY(dev_alloc(&tr->d_idx_local[b], own_ids * STAGE_STEPS));
+  tr->d.idx_rstride = (int)own_ids;
 
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps, tr->delta_now);
   uint64_t launches = 1;
   FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   unsigned long long chunk_id = 0;
+  int chunk_rstride = (int)own_ids;
   for (unsigned long long k = 0; k < nsteps; ++k) {
     // Input ids arrive in chunks of STAGE_STEPS steps through two device buffers filled on a second
     // stream, one chunk ahead of the step loop: uploaded from the caller's host memory, or derived
@@ -1862,7 +1880,22 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
       const unsigned long long n = (nsteps - k < STAGE_STEPS) ? nsteps - k : STAGE_STEPS;
       // the buffer must no longer be read by the chunk that used it two chunks ago
       if (chunk_id >= 2) FV_CUDA(cudaStreamWaitEvent(tr->copy_stream, tr->ev_used[b], 0));
-      if (idx_host) {
+      if (gather_ids) {
+        // this rank's ids of the chunk go up, then one all-gather lays the ranks' blocks side by side:
+        // [rank][step of the chunk][B*w], i.e. the blocks of one step lie n * B*w apart
+        FV_CUDA(cudaMemcpyAsync(tr->d_idx_local[b], idx_host + k * own_ids, n * own_ids * sizeof(int32_t),
+                                cudaMemcpyHostToDevice, tr->copy_stream));
+        // comm mode 1 already uses the communicator on the step stream: keep NCCL calls in one order there
+        cudaStream_t gs = (tr->comm_mode == 1) ? tr->stream : tr->copy_stream;
+        if (gs != tr->copy_stream) {
+          FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
+          FV_CUDA(cudaStreamWaitEvent(gs, tr->ev_copy[b], 0));
+        }
+        const int rc = g_nccl.AllGather(tr->d_idx_local[b], tr->d_idx_stage[b], n * own_ids, NCCL_UINT32, tr->comm, gs);
+        if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather (ids) failed: %s", g_nccl.GetErrorString(rc));
+        chunk_rstride = (int)(n * own_ids);
+      } else if (idx_host) {
+        chunk_rstride = (int)own_ids;
         FV_CUDA(cudaMemcpyAsync(tr->d_idx_stage[b], idx_host + k * step_ids, n * step_ids * sizeof(int32_t),
                                 cudaMemcpyHostToDevice, tr->copy_stream));
       } else {
@@ -1876,7 +1909,8 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
         launches += 1;
       }
     }
-    const int32_t* idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * step_ids;
+    tr->d.idx_rstride = chunk_rstride;
+    const int32_t* idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * (gather_ids ? own_ids : step_ids);
     FV_TRY(enqueue_step(tr, (int)k, idx, &launches));
     if ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps) {
       FV_CUDA(cudaEventRecord(tr->ev_used[chunk_id & 1], tr->stream));
@@ -1887,6 +1921,7 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
       launches += 2;
     }
   }
+  tr->d.idx_rstride = (int)own_ids;
   k_advance<<<1, 1, 0, tr->stream>>>(tr->d_ctl, nsteps);
   tr->ticks += nsteps;
   launches += 1;
@@ -1951,7 +1986,7 @@ void free_all(fv_trainer* tr) {
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
                   tr->d_mail, tr->d_peer_table, tr->d_xx_acc, tr->d_xx_wins, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
-                  tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1]};
+                  tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1], tr->d_idx_local[0], tr->d_idx_local[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
   cudaEvent_t evs[] = {tr->ev_begin, tr->ev_end, tr->ev_copy[0], tr->ev_copy[1], tr->ev_used[0], tr->ev_used[1]};
@@ -1994,6 +2029,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.MO = (d.B + 3) & ~3;                  // second winners (with delta) start here (64-bit words)
   d.XO = d.MO * (1 + d.has_delta);        // xx follows
   d.P = d.XO + d.Kp;
+  d.idx_rstride = d.B * d.W;
   d.spin_limit = 8u << 20;  // ~10 s of polling with back-off
   {
     auto magic = [](uint32_t divisor, uint32_t* m, uint32_t* s) {
@@ -2401,13 +2437,19 @@ int fv_trainer_get_permutation(fv_trainer* tr, uint64_t* perm) {
 int fv_trainer_run_steps(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, float eps, float* nc_out,
                          float* scale_out, fv_run_stats* stats) {
   FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_run_steps: NULL trainer");
-  return run_steps_impl(tr, first_step, nsteps, eps, nullptr, nc_out, scale_out, stats);
+  return run_steps_impl(tr, first_step, nsteps, eps, nullptr, false, nc_out, scale_out, stats);
 }
 
 int fv_trainer_run_steps_host(fv_trainer* tr, const int32_t* idx_host, uint64_t nsteps, float eps, float* nc_out,
                               float* scale_out, fv_run_stats* stats) {
   FV_REQUIRE(tr && idx_host, FV_ERR_INVALID, "fv_trainer_run_steps_host: NULL argument");
-  return run_steps_impl(tr, 0, nsteps, eps, idx_host, nc_out, scale_out, stats);
+  return run_steps_impl(tr, 0, nsteps, eps, idx_host, false, nc_out, scale_out, stats);
+}
+
+int fv_trainer_run_steps_host_local(fv_trainer* tr, const int32_t* idx_host, uint64_t nsteps, float eps, float* nc_out,
+                                    float* scale_out, fv_run_stats* stats) {
+  FV_REQUIRE(tr && idx_host, FV_ERR_INVALID, "fv_trainer_run_steps_host_local: NULL argument");
+  return run_steps_impl(tr, 0, nsteps, eps, idx_host, true, nc_out, scale_out, stats);
 }
 
 int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_stats* stats) {
@@ -2421,14 +2463,14 @@ int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_st
   tr->delta_now = (float)((double)tr->cfg.delta * 0.5 * (1.0 + tanh(((double)(float)epoch - 0.125 * (double)nep) / 10.0)));
   const unsigned long long per_step = (unsigned long long)tr->d.G * tr->d.B;
   const unsigned long long nsteps = (tr->d.Ns + per_step - 1) / per_step;
-  return run_steps_impl(tr, 0, nsteps, eps, nullptr, nullptr, nullptr, stats);
+  return run_steps_impl(tr, 0, nsteps, eps, nullptr, false, nullptr, nullptr, stats);
 }
 
 int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* winners, float* xx, float* nc,
                           float* scale) {
   FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_step_debug: NULL trainer");
   float nc1 = 0.f, s1 = 0.f;
-  FV_TRY(run_steps_impl(tr, step, 1, eps, nullptr, &nc1, &s1, nullptr));
+  FV_TRY(run_steps_impl(tr, step, 1, eps, nullptr, false, &nc1, &s1, nullptr));
   fv::DeviceGuard guard(tr->device);
   const Dev& d = tr->d;
   // the step just run had parity (ticks - 1) & 1

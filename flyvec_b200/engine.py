@@ -125,6 +125,16 @@ class Trainer:
                                                    ptr(nc_out) if nc_out is not None else None, None, C.byref(st)))
         return st.as_dict()
 
+    def run_steps_host_local(self, idx_local: np.ndarray, nsteps: int, eps: float, nc_out: np.ndarray | None = None):
+        """``idx_local``: int32 ``[nsteps, batch, window]`` input ids of THIS rank's windows only; the ranks'
+        ids are all-gathered on the GPUs, a block of steps ahead of the step loop."""
+        assert idx_local.dtype == np.int32 and idx_local.flags.c_contiguous
+        assert idx_local.size == nsteps * self.B * self.W
+        st = FvRunStats()
+        check(_lib.lib().fv_trainer_run_steps_host_local(self._h, ptr(idx_local), nsteps, eps,
+                                                         ptr(nc_out) if nc_out is not None else None, None, C.byref(st)))
+        return st.as_dict()
+
     def step_debug(self, step: int, eps: float):
         win = np.empty(self.G * self.B, np.int32)
         xx = np.empty((self.G, self.K), np.float32)

@@ -155,6 +155,12 @@ int fv_trainer_run_steps(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, f
  * of the reference's zero-copy reads of pinned host tokens (cuda_funcs.cu:1679-1680). */
 int fv_trainer_run_steps_host(fv_trainer* tr, const int32_t* idx_host, uint64_t nsteps, float eps, float* nc_out,
                               float* scale_out, fv_run_stats* stats);
+/* The same with every rank passing only ITS OWN windows (nsteps*batch of them, in step order): the
+ * ranks' ids meet on the GPUs through an all-gather over NVLink that runs a block of steps ahead on a
+ * second stream, so a rank uploads 1/world of what fv_trainer_run_steps_host takes.  With one rank
+ * the two calls are the same. */
+int fv_trainer_run_steps_host_local(fv_trainer* tr, const int32_t* idx_host, uint64_t nsteps, float eps, float* nc_out,
+                                    float* scale_out, fv_run_stats* stats);
 /* One step with its intermediates copied out, for parity checks:
  * winners[world*batch] (-1 for absent windows), xx[world][K], nc, scale. */
 int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* winners, float* xx, float* nc,

@@ -36,8 +36,21 @@ def main():
         wins.append(win)
         ncs.append(nc)
     st = tr.run_steps(nsteps, 3, 2e-4)  # and a few more without the debug read-back
-    np.savez(out / f"rank{rank}.npz", W=tr.get_weights(), wins=np.stack(wins), ncs=np.array(ncs),
-             windows=st["windows"])
+    W_a = tr.get_weights()
+    # 40 more steps twice from the same weights: ids built on the GPU from the resident corpus, and ids of
+    # this rank's windows fed from host memory and all-gathered on the GPUs (two chunks, the second partial)
+    more, first = 40, nsteps + 3
+    tr.run_steps(first, more, 2e-4)
+    W_res = tr.get_weights()
+    tr.set_weights(W_a)
+    sel = p["perm"][first * world * batch:(first + more) * world * batch].reshape(more, world, batch)[:, rank, :].reshape(-1)
+    pos = p["starts"][sel].astype(np.int64)[:, None] + np.arange(p["W"], dtype=np.int64)[None, :]
+    ids = p["enc"][pos].astype(np.int32)
+    ids[:, p["W"] // 2] += p["V"]
+    tr.run_steps_host_local(np.ascontiguousarray(ids.reshape(more, batch, p["W"])), more, 2e-4)
+    W_loc = tr.get_weights()
+    np.savez(out / f"rank{rank}.npz", W=W_a, wins=np.stack(wins), ncs=np.array(ncs),
+             windows=st["windows"], W_res=W_res, W_loc=W_loc)
     tr.close()
     dist.barrier()
     dist.destroy_process_group()

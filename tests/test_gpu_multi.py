@@ -31,6 +31,11 @@ def test_two_ranks_match_oracle(built_lib, tmp_path):
     np.testing.assert_array_equal(r0["W"], r1["W"])       # replicas identical
     np.testing.assert_array_equal(r0["wins"], r1["wins"])  # both saw the same gathered winners
     assert int(r0["windows"]) == 3 * batch and int(r1["windows"]) == 3 * batch
+    # ids fed per rank from host memory and all-gathered on the GPUs give what the resident corpus gives
+    np.testing.assert_array_equal(r0["W_res"], r1["W_res"])
+    np.testing.assert_array_equal(r0["W_loc"], r0["W_res"])
+    np.testing.assert_array_equal(r1["W_loc"], r1["W_res"])
+    assert not np.array_equal(r0["W_res"], r0["W"])
 
     p = small_problem(K=64, V=512, W=11, ntok=30000, seed=21)
     Wref = p["W0"]

@@ -332,6 +332,16 @@ def test_streaming_mode_matches_resident_mode(built_lib):
     np.testing.assert_array_equal(Wa, Wb)
     np.testing.assert_array_equal(nc, sa["nc"])
     assert sb["windows"] == nsteps * batch
+    # with one rank the rank-local feed is the same call
+    c = make_trainer(p, batch)
+    c.run_steps_host_local(pinned, nsteps, 2e-4)
+    np.testing.assert_array_equal(c.get_weights(), Wa)
+    c.close()
+    # emulated ranks have no second process to gather from
+    e = make_trainer(p, 64, world=2, flags=_lib.FV_FLAG_EMULATE_RANKS)
+    with pytest.raises(_lib.FlyvecError, match="rank-local"):
+        e.run_steps_host_local(np.ascontiguousarray(pinned[:4, :64]), 4, 2e-4)
+    e.close()
 
 
 def test_seeded_shuffle_is_a_permutation(built_lib):
