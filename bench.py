@@ -289,7 +289,7 @@ def bench_train(args):
         "last_nc": st["last_nc"],
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_train_baseline(enc, off, seconds_budget=args.cpu_seconds)
+        out["cpu_baseline"] = cpu_train_baseline(enc, off, seconds_limit=args.cpu_seconds)
     tr.close()
     dist.close()
     if rank == 0:
@@ -369,7 +369,7 @@ def bench_hash(args, windows: bool):
     cpu = None
     if not args.no_cpu_baseline:
         cpu = cpu_hash_baseline(h.weights(), V, ids, hl, windows, h_f=inv_f,
-                                seconds_budget=args.cpu_seconds)
+                                seconds_limit=args.cpu_seconds)
     out = {"metric": "hashed windows/sec" if windows else "hashed tokens/sec", "value": n / t,
            "unit": "windows/s" if windows else "tokens/s", "n_gpus": 1, "steps": len(times), "warmup": max(args.warmup, 3),
            "ms_per_step": t * 1e3, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
@@ -383,7 +383,7 @@ def bench_hash(args, windows: bool):
     print(json.dumps(out))
 
 
-def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_budget: float = 15.0):
+def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_limit: float = 15.0):
     """The oracle's numpy restatement of the reference's hashing rule on a bounded sample: for tokens the
     per-token loop shaped like FlyVec.get_sparse_embedding (flyvec/core.py:139-163, one core) and its
     vectorised form; for windows the weighted activation plus the same rule."""
@@ -391,7 +391,7 @@ def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_budget: float = 15.
 
     def timed(fn, items, first):
         n, done, spent = first, 0, 0.0
-        while spent < seconds_budget / 2 and done < len(items):
+        while spent < seconds_limit / 2 and done < len(items):
             part = items[done:done + n]
             t0 = time.perf_counter()
             fn(part)
@@ -415,7 +415,7 @@ def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_budget: float = 15.
 # ----------------------------------------------------------------------------
 # CPU arm: the oracle's C restatement of the reference step on the host cores
 # ----------------------------------------------------------------------------
-def cpu_train_baseline(enc, off, seconds_budget: float = 20.0, max_steps: int = 10 ** 9):
+def cpu_train_baseline(enc, off, seconds_limit: float = 20.0, max_steps: int = 10 ** 9):
     """Times oracle/oracle_train.c (a literal restatement of the reference's step;
     the reference trainer itself is CUDA-only) on config-1 shapes."""
     from flyvec_b200 import synth
@@ -430,7 +430,7 @@ def cpu_train_baseline(enc, off, seconds_budget: float = 20.0, max_steps: int = 
     Wm = synth.make_weights(K, 2 * V, seed=WEIGHT_SEED)
     runner = c_oracle.StepRunner(K, 2 * V, V, W, B, 1)
     nsteps, t_total = 0, 0.0
-    while nsteps < max_steps and (nsteps < 2 or t_total < seconds_budget):
+    while nsteps < max_steps and (nsteps < 2 or t_total < seconds_limit):
         idx = orc.build_idx(np.asarray(enc), starts, perm[(nsteps * B) % (len(perm) - B):][:B], W, V)
         t0 = time.perf_counter()
         runner.step(Wm, idx[None], [B], f, np.float32(CFG["lr"]))
@@ -452,8 +452,8 @@ def bench_reference(args):
 
     K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
     enc, off = synth.make_corpus(5_000_000, V, s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=W, seed=CORPUS_SEED)
-    budget = args.cpu_seconds_reference
-    base = cpu_train_baseline(enc, off, seconds_budget=budget, max_steps=args.steps + 1)
+    limit = args.cpu_seconds_reference
+    base = cpu_train_baseline(enc, off, seconds_limit=limit, max_steps=args.steps + 1)
     timed = int(base["sample"].split()[0])
     out = {"impl": "reference", "metric": "train windows/sec (K=400,V=20k,w=11)", "value": base["value"],
            "unit": "windows/s", "n_gpus": args.gpus, "steps": timed, "warmup": 1,
