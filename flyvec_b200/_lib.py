@@ -29,6 +29,7 @@ FV_HASH_PACKED = 0
 FV_HASH_BYTES = 1
 FV_HASH_RAW = 2
 FV_HASH_NO_UNK = 4
+FV_HASH_EXACT = 8
 
 STATUS_NAMES = {1: "FV_ERR_INVALID", 2: "FV_ERR_CUDA", 3: "FV_ERR_COMM", 4: "FV_ERR_STATE", 5: "FV_ERR_DATA",
                 6: "FV_ERR_TIMEOUT"}

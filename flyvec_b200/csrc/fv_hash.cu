@@ -21,6 +21,8 @@ struct HDev {
   const float* wt;
   const float* f;  // 1/count per vocabulary id, may be null
   uint32_t* error;
+  float wabsmax;   // max |wt| (bounds the rounding error of the float window sums)
+  float fmax;      // max |f|
 };
 
 // ---- normalisation ---------------------------------------------------------
@@ -99,6 +101,15 @@ __global__ void k_row_norms(const float* __restrict__ w_kn, int K, long long N, 
   norm[mu] = __fadd_rn(__fsqrt_rn(ss), prec);
 }
 
+// max |x| over n floats as a bit pattern (non-negative floats order like their bits)
+__global__ void k_absmax_bits(const float* __restrict__ x, size_t n, uint32_t* __restrict__ out) {
+  uint32_t m = 0u;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    m = max(m, __float_as_uint(x[i]) & 0x7fffffffu);
+  m = __reduce_max_sync(FULL, m);
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
 // [K][N] -> [N][Kp], dividing by the unit's norm when norm != nullptr.
 __global__ void k_load_transposed(const float* __restrict__ w_kn, const float* __restrict__ norm,
                                   float* __restrict__ wt, int K, int Kp, int N) {
@@ -147,7 +158,7 @@ __device__ __forceinline__ float key2f(uint32_t k) {
 // MODE 0: token ids (activation = row V+id); MODE 1: windows, weighted by f;
 // MODE 2: windows, raw.
 template <int NT, int MODE>
-__global__ void __launch_bounds__(256) k_hash(HDev h, const int32_t* __restrict__ in, unsigned long long n, int W,
+__global__ void __launch_bounds__(256, (NT <= 4) ? 3 : 1) k_hash(HDev h, const int32_t* __restrict__ in, unsigned long long n, int W,
                                               int hash_len, uint32_t flags, uint8_t* __restrict__ out) {
   const int lane = threadIdx.x & 31;
   const unsigned long long warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -155,6 +166,12 @@ __global__ void __launch_bounds__(256) k_hash(HDev h, const int32_t* __restrict_
   const int Kq = h.Kq;
   const bool bytes_out = (flags & FV_HASH_BYTES) != 0;
   const size_t out_stride = bytes_out ? (size_t)h.K : (size_t)((h.K + 7) / 8);
+  // Bound on |float window sum - reference window sum| for a window whose terms are bounded by
+  // t_c = f_c * max|wt|: sequential float summation is off by at most (W-1) * 2^-24 * sum t_c, product
+  // rounding (one fused rounding here, a rounded product there) and the final float store add at most
+  // 3 * 2^-24 * sum t_c; times four for safety.  theta = theta_unit * sum f_c is formed per window.
+  const float theta_unit = 4.0f * (float)(W + 2) * 5.9604645e-8f * h.wabsmax;
+  const bool exact_only = (flags & FV_HASH_EXACT) != 0;
 
   for (unsigned long long item = warp; item < n; item += nwarps) {
     float a[NT][4];
@@ -175,78 +192,153 @@ __global__ void __launch_bounds__(256) k_hash(HDev h, const int32_t* __restrict_
         const float4 v = (q < Kq) ? __ldg(row + q) : make_float4(0.f, 0.f, 0.f, 0.f);
         a[t][0] = v.x; a[t][1] = v.y; a[t][2] = v.z; a[t][3] = v.w;
       }
-    } else {
-      // double sum over the window positions of the (float) weighted term, float store
-      // (flyvec/src/cuda_funcs.cu:289-305; 248-263 for the raw form)
-      const int my = (lane < W) ? in[item * (unsigned long long)W + lane] : -1;
-      if (my >= h.N) {
-        atomicOr(h.error, FV_DEVERR_TOKEN_RANGE);
-      }
-      double acc[NT][4];
+    }
+    // Window sums.  The reference adds the (float) terms in double and stores a float
+    // (flyvec/src/cuda_funcs.cu:289-305; 248-263 for the raw form).  Converting every term to double
+    // is what bounds this kernel, so the sums are first formed in float: they are off by at most theta
+    // from the reference's, and when the hash_len-th and the next largest of them lie more than
+    // 4 * theta apart, the units above the threshold are the same whichever sums are used -- the code
+    // is certified.  Otherwise (ties, close calls: well under 1 % of the windows) the warp redoes the
+    // window with the reference's arithmetic.
+    const int my = (MODE != 0 && lane < W) ? in[item * (unsigned long long)W + lane] : -1;
+    if (MODE != 0 && my >= h.N) atomicOr(h.error, FV_DEVERR_TOKEN_RANGE);
+    bool done = false;
+    uint32_t kh = 0u;
+    float thr = 0.f, theta = 0.f;
+    for (int pass = (MODE == 0 || exact_only) ? 1 : 0; pass < 2 && !done; ++pass) {
+      if (MODE != 0 && pass == 0) {
+        float acc[NT][4];
 #pragma unroll
-      for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0;
-      for (int c = 0; c < W; ++c) {
-        const int id = __shfl_sync(FULL, my, c);
-        if (id < 0 || id >= h.N) continue;
-        const float sc = (MODE == 1) ? __ldg(h.f + (id % h.V)) : 1.f;
-        const float4* __restrict__ row = reinterpret_cast<const float4*>(h.wt + (size_t)id * h.Kp);
+        for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+        for (int c0 = 0; c0 < W; c0 += 4) {  // four rows' loads in flight together
+          const float4* __restrict__ row[4];
+          float sc[4];
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          const int q = lane + 32 * t;
-          if (q < Kq) {
-            const float4 v = __ldg(row + q);
-            if (MODE == 1) {
-              acc[t][0] += (double)__fmul_rn(v.x, sc);
-              acc[t][1] += (double)__fmul_rn(v.y, sc);
-              acc[t][2] += (double)__fmul_rn(v.z, sc);
-              acc[t][3] += (double)__fmul_rn(v.w, sc);
-            } else {
-              acc[t][0] += (double)v.x;
-              acc[t][1] += (double)v.y;
-              acc[t][2] += (double)v.z;
-              acc[t][3] += (double)v.w;
+          for (int u = 0; u < 4; ++u) {
+            const int id = __shfl_sync(FULL, my, (c0 + u) & 31);
+            const bool ok = c0 + u < W && id >= 0 && id < h.N;
+            row[u] = reinterpret_cast<const float4*>(h.wt + (size_t)(ok ? id : 0) * h.Kp);
+            sc[u] = !ok ? 0.f : (MODE == 1) ? __ldg(h.f + (id % h.V)) : 1.f;  // an absent position adds 0 * (row 0)
+            theta += theta_unit * fabsf(sc[u]);
+          }
+          float4 v[4][NT];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) v[u][t] = __ldg(row[u] + min(lane + 32 * t, Kq - 1));
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+              acc[t][0] = fmaf(v[u][t].x, sc[u], acc[t][0]);
+              acc[t][1] = fmaf(v[u][t].y, sc[u], acc[t][1]);
+              acc[t][2] = fmaf(v[u][t].z, sc[u], acc[t][2]);
+              acc[t][3] = fmaf(v[u][t].w, sc[u], acc[t][3]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) a[t][k] = acc[t][k];
+      } else if (MODE != 0) {
+        double acc[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0;
+        for (int c = 0; c < W; ++c) {
+          const int id = __shfl_sync(FULL, my, c);
+          if (id < 0 || id >= h.N) continue;
+          const float sc = (MODE == 1) ? __ldg(h.f + (id % h.V)) : 1.f;
+          const float4* __restrict__ row = reinterpret_cast<const float4*>(h.wt + (size_t)id * h.Kp);
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const int q = lane + 32 * t;
+            if (q < Kq) {
+              const float4 v = __ldg(row + q);
+              if (MODE == 1) {
+                acc[t][0] += (double)__fmul_rn(v.x, sc);
+                acc[t][1] += (double)__fmul_rn(v.y, sc);
+                acc[t][2] += (double)__fmul_rn(v.z, sc);
+                acc[t][3] += (double)__fmul_rn(v.w, sc);
+              } else {
+                acc[t][0] += (double)v.x;
+                acc[t][1] += (double)v.y;
+                acc[t][2] += (double)v.z;
+                acc[t][3] += (double)v.w;
+              }
             }
           }
         }
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) a[t][k] = (float)acc[t][k];
       }
+
+      uint32_t key[NT][4];
+      uint32_t kand = 0xffffffffu, kor = 0u;
 #pragma unroll
       for (int t = 0; t < NT; ++t)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) a[t][k] = (float)acc[t][k];
-    }
-
-    uint32_t key[NT][4];
+        for (int k = 0; k < 4; ++k) {
+          const bool real = 4 * (lane + 32 * t) + k < h.K;
+          key[t][k] = real ? f2key(a[t][k]) : 0u;
+          if (real) {
+            kand &= key[t][k];
+            kor |= key[t][k];
+          }
+        }
+      // hash_len-th largest key: the largest v with #{key >= v} >= hash_len, found bit by bit; the
+      // leading bits all keys share (sign and most of the exponent, as a rule) need no search
+      kand = __reduce_and_sync(FULL, kand);
+      kor = __reduce_or_sync(FULL, kor);
+      const int shared_bits = __clz(kand ^ kor);  // 32 when all keys are equal
+      kh = shared_bits >= 32 ? kand : (kand & ~(0xffffffffu >> shared_bits));
+      bool split = false;  // a candidate with exactly hash_len keys at or above it separates the two order statistics
+      for (int bit = 31 - shared_bits; bit >= 0 && !split; --bit) {
+        const uint32_t cand = kh | (1u << bit);
+        int c = 0;
 #pragma unroll
-    for (int t = 0; t < NT; ++t)
+        for (int t = 0; t < NT; ++t)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) key[t][k] = (4 * (lane + 32 * t) + k < h.K) ? f2key(a[t][k]) : 0u;
-
-    // hash_len-th largest key: the largest v with #{key >= v} >= hash_len
-    uint32_t kh = 0u;
-    for (int bit = 31; bit >= 0; --bit) {
-      const uint32_t cand = kh | (1u << bit);
-      int c = 0;
-#pragma unroll
-      for (int t = 0; t < NT; ++t)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) c += (key[t][k] >= cand);
-      c = __reduce_add_sync(FULL, c);
-      if (c >= hash_len) kh = cand;
-    }
-    // the next one in sorted order: kh again if it occurs beyond rank hash_len, else the largest key below it
-    int cge = 0;
-    uint32_t below = 0u;
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        cge += (key[t][k] >= kh);
-        if (key[t][k] < kh) below = max(below, key[t][k]);
+          for (int k = 0; k < 4; ++k) c += (key[t][k] >= cand);
+        c = __reduce_add_sync(FULL, c);
+        if (c >= hash_len) kh = cand;
+        split = (c == hash_len);
       }
-    cge = __reduce_add_sync(FULL, cge);
-    below = __reduce_max_sync(FULL, below);
-    const uint32_t kn = (cge > hash_len) ? kh : below;
-    const float thr = __fmul_rn(__fadd_rn(key2f(kh), key2f(kn)), 0.5f);
+      uint32_t kn;
+      if (split) {
+        // kh is a lower bound with exactly hash_len keys at or above it: the hash_len-th largest is the
+        // smallest of those, the next one the largest below (the remaining bits need no search)
+        uint32_t above = 0xffffffffu, below = 0u;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (key[t][k] >= kh) above = min(above, key[t][k]);
+            else below = max(below, key[t][k]);
+          }
+        kh = __reduce_min_sync(FULL, above);
+        kn = __reduce_max_sync(FULL, below);
+      } else {
+        // ties at the hash_len-th value: kh is that value; the next one in sorted order is kh again if it
+        // occurs beyond rank hash_len, else the largest key below it
+        int cge = 0;
+        uint32_t below = 0u;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            cge += (key[t][k] >= kh);
+            if (key[t][k] < kh) below = max(below, key[t][k]);
+          }
+        cge = __reduce_add_sync(FULL, cge);
+        below = __reduce_max_sync(FULL, below);
+        kn = (cge > hash_len) ? kh : below;
+      }
+      thr = __fmul_rn(__fadd_rn(key2f(kh), key2f(kn)), 0.5f);
+      // pass 0 only stands when the two order statistics are clearly apart (NaN compares false)
+      done = (pass == 1) || (key2f(kh) - key2f(kn) > 4.0f * theta);
+    }
 
     uint8_t* __restrict__ dst = out + (size_t)item * out_stride;
 #pragma unroll
@@ -472,10 +564,20 @@ int create_hasher(fv_hasher* hs, const float* w_kn, int K, int N, int normalize,
     k_load_transposed<<<grid, block, 0, hs->stream>>>(tmp, norm, hs->d_wt, K, h.Kp, N);
     e = cudaGetLastError();
   }
+  uint32_t wmax_bits = 0u;
+  if (e == cudaSuccess) e = cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream);
+  if (e == cudaSuccess) {
+    k_absmax_bits<<<hs->num_sms * 4, 256, 0, hs->stream>>>(hs->d_wt, (size_t)N * h.Kp, hs->d_err);  // d_err as scratch
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&wmax_bits, hs->d_err, sizeof(uint32_t), cudaMemcpyDeviceToHost, hs->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(hs->stream);
   cudaFree(tmp);
   if (norm) cudaFree(norm);
   FV_CUDA(e);
+  memcpy(&h.wabsmax, &wmax_bits, sizeof(float));  // NaN or infinity here sends every window to the exact pass
+  h.fmax = 1.0f;
   return FV_OK;
 }
 
@@ -543,6 +645,9 @@ int fv_hasher_set_inverse_frequency(fv_hasher* hs, const float* inv_freq, uint32
   if (!hs->d_f) FV_CUDA(cudaMalloc((void**)&hs->d_f, (size_t)vocab * sizeof(float)));
   FV_CUDA(cudaMemcpy(hs->d_f, inv_freq, (size_t)vocab * sizeof(float), cudaMemcpyHostToDevice));
   hs->h.f = hs->d_f;
+  float fmax = 0.f;
+  for (uint32_t v = 0; v < vocab; ++v) fmax = std::fmax(fmax, std::fabs(inv_freq[v]));  // NaN-propagating enough: NaN f gives NaN sums
+  hs->h.fmax = fmax;
   return FV_OK;
 }
 

@@ -248,10 +248,13 @@ class Hasher:
         check(_lib.lib().fv_hash_tokens_static(self._h, ptr(ids), ids.size, hash_length, flags, ptr(out)))
         return out if packed else out.view(np.int8)
 
-    def hash_windows(self, idx, inv_freq=None, hash_length: int = 50, packed: bool = False) -> np.ndarray:
+    def hash_windows(self, idx, inv_freq=None, hash_length: int = 50, packed: bool = False,
+                     exact: bool = False) -> np.ndarray:
+        """``exact``: sum every window in double like the reference instead of certifying float sums
+        first (same codes, slower)."""
         idx = as_c(idx, np.int32)
         assert idx.ndim == 2
-        flags = _lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES
+        flags = (_lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES) | (_lib.FV_HASH_EXACT if exact else 0)
         f = None
         if inv_freq is None:
             flags |= _lib.FV_HASH_RAW

@@ -42,6 +42,8 @@ typedef enum fv_status {
 #define FV_HASH_BYTES 1u    /* output K bytes per item, each 0 or 1 (the reference's int8 layout) */
 #define FV_HASH_RAW 2u      /* window hashing: unweighted activation (the form training selects on) */
 #define FV_HASH_NO_UNK 4u   /* token hashing: do not zero the code of id 0 */
+#define FV_HASH_EXACT 8u    /* window hashing: sum every window in double like the reference, without the
+                               certified float pass (same codes, slower; for checks) */
 
 /*
  * Hyper-parameters of one trainer.  Stands in for the reference's

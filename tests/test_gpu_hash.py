@@ -76,6 +76,27 @@ def test_window_codes_bit_exact(built_lib, weighted, hash_length):
     h.close()
 
 
+def test_window_codes_certified_and_exact_pass_agree(built_lib):
+    """Float window sums are only trusted when the two order statistics around the threshold are far
+    enough apart; ties and close calls must fall back to the reference's double arithmetic.  Weights
+    quantised to a few levels make exact ties and near-ties common."""
+    K, V, W = 200, 600, 9
+    rng = np.random.default_rng(5)
+    Wm = (rng.integers(-3, 4, (K, 2 * V)) * np.float32(0.25)).astype(np.float32)
+    Wm[:, ::7] += np.float32(1e-6) * rng.standard_normal((K, Wm[:, ::7].shape[1])).astype(np.float32)
+    enc, off = synth.make_corpus(20000, V, seed=29)
+    starts = orc.enumerate_windows(off, W)
+    f = orc.inverse_word_frequency(enc, V, saturate_fp32=False)
+    idx = orc.build_idx(enc, starts, np.arange(0, 3000), W, V)
+    h = Hasher(Wm, normalize=False)
+    for inv in (None, f):
+        for hl in (1, 16, 50):
+            ref = orc.hash_windows(Wm, V, idx, inv, hl)
+            np.testing.assert_array_equal(h.hash_windows(idx, inv_freq=inv, hash_length=hl), ref)
+            np.testing.assert_array_equal(h.hash_windows(idx, inv_freq=inv, hash_length=hl, exact=True), ref)
+    h.close()
+
+
 def test_golden_vectors_from_reference(built_lib):
     """Codes the reference's unmodified FlyVec.get_sparse_embedding produced for a
     seeded matrix (tests/golden/make_hash_golden.py)."""
