@@ -50,7 +50,7 @@ def main():
     tr.run_steps_host_local(np.ascontiguousarray(ids.reshape(more, batch, p["W"])), more, 2e-4)
     W_loc = tr.get_weights()
     np.savez(out / f"rank{rank}.npz", W=W_a, wins=np.stack(wins), ncs=np.array(ncs),
-             windows=st["windows"], W_res=W_res, W_loc=W_loc)
+             windows=st["windows"], W_res=W_res, W_loc=W_loc, mode=tr.comm_mode)
     tr.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -90,3 +90,47 @@ def test_closed_form_equals_dense_reference_form():
         Wcf, nc, s = orc.closed_form_update(p["W0"], idxs, info["win"], info["xx"], p["f"], p["V"], np.float32(1e-3))
         np.testing.assert_allclose(nc, info["nc"], rtol=1e-6)
         assert rel_err(Wcf, Wref) < 1e-6
+
+
+def _ids_worker(rank, port, outdir):
+    """Rank-local feed of input ids: every rank builds the ids of its own windows only, one all-gather
+    lays the ranks' blocks of a chunk of steps side by side as [rank][step][batch*window], and block
+    (step, rank) is read at offset rank * (steps * batch * window) + step * batch * window -- the
+    addressing the library uses for fv_trainer_run_steps_host_local."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    p = small_problem(K=32, V=200, W=7, ntok=8000, seed=13)
+    ns, Wd = len(p["starts"]), p["W"]
+    own = []
+    for step in range(STEPS):
+        lo, hi = shard(ns, BATCH, WORLD, rank, step)
+        own.append(orc.build_idx(p["enc"], p["starts"], p["perm"][lo:hi], Wd, p["V"]).reshape(-1))
+    mine = torch.from_numpy(np.concatenate(own).astype(np.int32))
+    gathered = [torch.empty_like(mine) for _ in range(WORLD)]
+    dist.all_gather(gathered, mine)
+    flat = torch.cat(gathered).numpy()
+    rstride, own_ids = STEPS * BATCH * Wd, BATCH * Wd
+    ok = True
+    for step in range(STEPS):
+        for g in range(WORLD):
+            lo, hi = shard(ns, BATCH, WORLD, g, step)
+            want = orc.build_idx(p["enc"], p["starts"], p["perm"][lo:hi], Wd, p["V"]).reshape(-1)
+            got = flat[g * rstride + step * own_ids:g * rstride + (step + 1) * own_ids]
+            ok = ok and np.array_equal(got, want)
+    np.save(Path(outdir) / f"ids_ok{rank}.npy", np.array([ok]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_rank_local_ids_meet_through_an_all_gather(tmp_path):
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_ids_worker, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    for r in range(WORLD):
+        assert np.load(tmp_path / f"ids_ok{r}.npy")[0]

@@ -17,17 +17,26 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_two_ranks_match_oracle(built_lib, tmp_path):
+@pytest.mark.parametrize("exchange", ["mailbox", "nccl"])
+def test_two_ranks_match_oracle(built_lib, tmp_path, exchange):
+    """Both exchange modes: packets written straight into the peer's memory, and one all-gather per step."""
     if _lib.device_count() < 2:
         pytest.skip("needs two GPUs")
+    import os
     nsteps, batch, world = 4, 128, 2
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29541", str(ROOT / "tests" / "multi_rank_worker.py"),
            str(tmp_path), str(nsteps), str(batch)]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    env = dict(os.environ)
+    if exchange == "nccl":
+        env["FV_COMM"] = "nccl"
+    else:
+        env.pop("FV_COMM", None)
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     r0 = np.load(tmp_path / "rank0.npz")
     r1 = np.load(tmp_path / "rank1.npz")
+    assert int(r0["mode"]) == (1 if exchange == "nccl" else 2)
     np.testing.assert_array_equal(r0["W"], r1["W"])       # replicas identical
     np.testing.assert_array_equal(r0["wins"], r1["wins"])  # both saw the same gathered winners
     assert int(r0["windows"]) == 3 * batch and int(r1["windows"]) == 3 * batch
