@@ -8,19 +8,23 @@
 //                           The dense part of the Hebbian update, W_mu *= (1 - s*X_mu),
 //                           only touches alpha; wt changes at the scattered positions.
 //   tokens, wstart, perm    corpus, window starts, window order.
-//   idx     int  [G*B][w]   input ids of the current global step (all ranks' windows).
-//   pkt     u32  [G][B+Kp]  per rank: B winners then Kp floats of xx; all-gathered.
-//   cnt/rec     [G*B*w]     scatter bookkeeping: one record per distinct touched position.
+//   idx     int  [32][G*B][w] input ids of the next steps (all ranks' windows), two staging buffers.
+//   mailbox                 per rank and step parity a packet of 64-bit words {payload, step sequence
+//                           number}: B winners, (with delta) B second winners, Kp floats of xx.
+//   xx_hi/lo  u64 [8][Kp]   fixed-point accumulators of xx; rec/cnt [G*B*w] scatter bookkeeping: one
+//                           record per distinct touched position.
 //
 // One global step (reference: run_epoch, flyvec/src/cuda_funcs.cu:1662-1812):
-//   k_forward    T4   window -> input ids                    (cuda_funcs.cu:915-936)
-//                T6-8 gather-sum, arg-max, weighted winner    (cuda_funcs.cu:248-305, 488-561)
-//                T8   xx[mu] = sum of weighted winning activations, in a fixed order
-//                     (cuda_funcs.cu:722-744)
-//   (k_build_idx_block, on a side stream: ids of the next 32 steps, all ranks' windows)
-//   all-gather        winners + xx of every rank (NCCL)
-//   k_tag        T10  each touched (mu,i) gets one owner slot; its weight is parked in
-//                     a record and replaced by a tagged NaN    (cuda_funcs.cu:657-672)
+//   (k_build_idx_block, on a side stream: T4, ids of the next 32 steps   (cuda_funcs.cu:915-936))
+//   k_forward    T6-8 gather-sum, arg-max, weighted winner    (cuda_funcs.cu:248-305, 488-561)
+//                T8   every window adds its term of xx[mu] as a fixed-point number: the sum does not
+//                     depend on the order of arrival          (cuda_funcs.cu:722-744)
+//   k_tag        T10  each touched (mu,i) gets one owner record; its weight is parked there and
+//                     replaced by a tagged NaN                 (cuda_funcs.cu:657-672);
+//                     its first CTA turns the xx sums into floats (xx_finish); with several ranks
+//                     eight more CTAs copy this rank's winners into the peers' mailboxes, and every
+//                     consumer of a peer's word checks the sequence number the word carries
+//                     (or, without peer access: k_xx, then one NCCL all-gather of the packets)
 //   k_scan       T11  nc = max|D|: exact D at touched positions, column max of |wt|
 //                     over untouched ones (tags read as 0)     (cu_special_reduction.cu:26-99)
 //   k_apply      T12-13 s = eps/max(prec,nc); alpha *= 1 - s*X; touched weights restored
@@ -59,7 +63,6 @@ struct StepCtl {
   uint32_t out_count;     // entries in this step's outbox (sharded update)
   uint32_t pad;
   uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
-  unsigned long long stamp[8];  // %globaltimer at phase boundaries of the last step (diagnostics)
   // Device-side phase clock: every step kernel's first thread charges the time since the previous
   // mark to the phase that was running and names its own.  No events, so the launches stay chained.
   unsigned long long t_mark;
@@ -1145,7 +1148,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     if (v && v > __ldcg(&d.colmax[p * d.Kp + mu])) atomicMax(&d.colmax[p * d.Kp + mu], v);
   }
   if (!d.shard) return;
-  if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->stamp[6] = global_timer();
 
   // Sharded update: the CTA that finishes last turns this rank's maxima into its partial
   // normaliser and pushes it, with a flag, into every rank's mailbox (its own included).
@@ -1211,8 +1213,6 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   __syncthreads();
   __shared__ int sFail;
   if (threadIdx.x == 0) sFail = 0;
-  const bool stamper = blockIdx.x == 0 && threadIdx.x == 0;
-  if (stamper) d.ctl->stamp[0] = global_timer();
   __syncthreads();
   const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
   __shared__ uint32_t sWord[MAX_RANKS];
@@ -1223,7 +1223,6 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   }
   __syncthreads();
   if (sFail) return;
-  if (stamper) d.ctl->stamp[1] = global_timer();
   if (threadIdx.x == 0) {
     float nc = 0.f;
     if (d.shard) {
@@ -1340,7 +1339,6 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   if (d.shard) {
     // publish: when every CTA has written its entries, the last one tells the peers how many there are
     __shared__ unsigned s_last;
-    if (stamper) d.ctl->stamp[2] = global_timer();
     __syncthreads();
     if (threadIdx.x == 0) {
       // device-scope fence per CTA (covers the CTA's entries, ordered before it by the barrier); the one
@@ -1376,7 +1374,6 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
     }
     __syncthreads();
     if (sFail) return;
-    if (stamper) d.ctl->stamp[3] = global_timer();
     const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gthreads = gridDim.x * blockDim.x;
     for (int r = 0; r < d.G; ++r) {
       if (r == d.rank) continue;
@@ -1392,7 +1389,6 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
         }
       }
     }
-    if (stamper) d.ctl->stamp[4] = global_timer();
   }
   // keep the bound on max |wt| valid for the next forward pass
   vmax = warp_max_u32(vmax);
