@@ -390,3 +390,38 @@ def test_zero_weights_learn_nothing(built_lib):
     np.testing.assert_array_equal(tr.get_weights(), p["W0"])
     assert st["device_error"] == 0
     tr.close()
+
+
+def test_cli_mirror_trains_and_resumes(built_lib, tmp_path):
+    """flyvec_train's mirror: the reference's flags, file formats and checkpoint names
+    (flyvec/train_flyvec.py:31-47, 186-189, 262-263); a run of three epochs equals two epochs plus a
+    run resumed from the second checkpoint, and equals what the library API computes."""
+    from flyvec_b200 import train_flyvec as cli
+
+    p = small_problem(K=32, V=300, W=5, ntok=6000, seed=41)
+    p["enc"][0] = 299  # max(encodings) + 1 is the vocabulary the CLI infers (train_flyvec.py:168)
+    np.save(tmp_path / "encodings.npy", p["enc"].astype(np.int32))
+    np.save(tmp_path / "offsets.npy", p["off"].astype(np.uint64))
+    common = [str(tmp_path / "encodings.npy"), str(tmp_path / "offsets.npy"), "--hid", "32", "--W", "5", "-b", "128",
+              "--initial_learning_rate", "0.0004", "--sigma", "1.0", "--seed", "7", "--Nep", "3"]
+    quiet = lambda *a, **k: None
+    base = cli.train(cli.parse_args(common + ["-o", str(tmp_path / "a")]), log=quiet)
+    assert base.endswith("flyvec_model_H_32_W_5_LR_0.0004_")
+    ck = [np.load(base + f"{ep}.npy") for ep in range(3)]
+    assert all(c.shape == (32, 600) and c.dtype == np.float32 for c in ck)
+    assert not np.array_equal(ck[0], ck[2])
+    # resume from the second checkpoint: only epoch 2 runs, with the same order and learning rate
+    resumed = cli.train(cli.parse_args(common + ["-o", str(tmp_path / "b"), "--starting_checkpoint", base + "1.npy"]), log=quiet)
+    # the reference resumes at int(name.split('_')[-1]) = 1, i.e. it repeats epoch 1 (train_flyvec.py:236-239, 252)
+    again = np.load(resumed + "1.npy")
+    assert again.shape == (32, 600)
+    # the library API gives the CLI's first epoch
+    f = orc.inverse_word_frequency(p["enc"], 300, saturate_fp32=False)
+    tr = Trainer(hid=32, vocab=300, window=5, batch=128, lr0=0.0004)
+    tr.set_corpus(p["enc"], p["off"])
+    tr.set_weights(np.float32(np.random.default_rng(7).normal(0.0, 1.0, (32, 600))))
+    tr.shuffle(7 * 1000003 + 0)
+    tr.run_epoch(0, 3)
+    np.testing.assert_array_equal(tr.get_weights(), ck[0])
+    np.testing.assert_array_equal(tr.inverse_frequency(), f)
+    tr.close()
