@@ -1704,7 +1704,7 @@ struct fv_trainer {
 
 namespace {
 
-constexpr unsigned long long FOLD_EVERY = 32;  // steps between folds of alpha into wt
+constexpr unsigned long long FOLD_EVERY = 128;  // steps between folds of alpha into wt
 constexpr int STAGE_STEPS = 32;                // steps per upload chunk in streaming mode
 
 #define FV_TRY(expr)                    \
