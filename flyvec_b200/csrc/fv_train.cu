@@ -310,15 +310,23 @@ __global__ void k_check_idx(Dev d, int32_t* __restrict__ idx, size_t total) {
 // exceeds four times that bound (plus the rounding of the scale product) the
 // arg-max of the float sums is the arg-max of the exact sums.
 // Otherwise -- about one window in 10^4 -- the warp redoes the window in double
-// with the reference's tie order (smallest (index % 64, index) among equal
-// maxima, cuda_funcs.cu:507-540).
+// with the reference's tie order.  Its kernel runs 64 threads per window: thread t
+// keeps the lowest index of units t, t+64, ... (strict '>', cuda_funcs.cu:507-512);
+// the __shfl_down_sync tree with offsets 16..1 and a strict '>' keeps the lower lane
+// at every level (515-522), so among tied lanes the one with the smallest
+// bit-reversed lane number reaches lane 0; thread 0 prefers warp 0 over warp 1
+// (535-540).  Key among equal maxima: smallest (t / 32, bitreverse5(t % 32), index)
+// with t = index % 64.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ int tie_key(int i) {
+  const unsigned t = (unsigned)i & 63u;
+  return (int)((((t & 32u) | (__brev(t & 31u) >> 27)) << 20) | (unsigned)i);
+}
 __device__ __forceinline__ bool better(float a, int ia, float b, int ib) {
   // true when (a, ia) beats (b, ib) under the reference's tie order
   if (a > b) return true;
   if (a < b) return false;
-  const int ka = ((ia & 63) << 20) | ia, kb = ((ib & 63) << 20) | ib;
-  return ka < kb;
+  return tie_key(ia) < tie_key(ib);
 }
 
 // The double-precision path for one window: per column group all w rows are fetched

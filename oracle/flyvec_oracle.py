@@ -19,11 +19,19 @@ Pinning status
 * hashing: pinned against golden vectors produced by executing the reference's
   unmodified ``flyvec/core.py`` (see ``tests/golden/make_hash_golden.py``).
 * training step: the reference ships no test, golden vector or fixture for its
-  CUDA trainer, and the trainer cannot run on a machine without a GPU.  Unless
-  ``tests/golden/ref_trainer_*.npz`` exists (outputs of the reference trainer
-  captured on a GPU box), **training parity is unpinned**: the restatement
-  below follows the cited lines but has not been checked against the
-  reference binary.
+  CUDA trainer.  The pin is the reference's own kernel text executed on the host:
+  ``oracle/build_oracle.py`` cuts the ``__global__`` functions of the live path
+  out of ``flyvec/src/cuda_funcs.cu`` and ``cu_special_reduction.cu`` where they
+  lie, compiles them against a CUDA-on-host execution model
+  (``oracle/cuda_on_host.h``: blocks in order, threads as lock-step fibers, the
+  warp shuffle as the hardware performs it) and ``tests/test_oracle.py`` compares
+  every stage of :func:`train_step` with that build bit for bit (input ids,
+  activations, winner and second winner incl. exact ties, ``xx``, combine, ``nc``,
+  step size, updated synapses; 1-3 replicas, ``delta`` zero and non-zero).  The
+  reference's complete trainer binary was not run on a GPU; the host-side launch
+  sequence is restated in ``oracle/ref_kernels_host.cpp`` from the cited lines.
+  Where the hardware leaves an order open (float atomics) the host model applies
+  them in thread order within block order, one admissible order.
 """
 from __future__ import annotations
 
@@ -128,18 +136,33 @@ def activations(ds: np.ndarray, idx: np.ndarray, f: np.ndarray | None, V: int) -
 # --------------------------------------------------------------------------
 # T7  winner and m-th winner         flyvec/src/cuda_funcs.cu:488-561
 # --------------------------------------------------------------------------
-def _argmax_ref_order(a: np.ndarray) -> np.ndarray:
-    """Row-wise arg-max with the reference's tie order.
+def tie_rank(K: int) -> np.ndarray:
+    """Rank of every unit in the reference's tie order (smaller wins among equal maxima).
 
-    The kernel runs 64 threads; thread ``t`` scans ``t, t+64, ...`` with a
-    strict ``>`` (cuda_funcs.cu:507-512), the shuffle tree keeps the lower lane
-    on equality (515-522) and warp 0 beats warp 1 (535-540).  Among equal
-    maxima the survivor is therefore the one with the smallest
-    ``(index % 64, index)``.
+    ``get_max_and_m_max_kernel_2`` runs 64 threads per window.  Thread ``t`` scans units
+    ``t, t+64, ...`` with a strict ``>``, so it keeps its lowest index (cuda_funcs.cu:507-512).
+    The warp reduction uses ``__shfl_down_sync`` with offsets 16, 8, 4, 2, 1 and a strict
+    ``>`` (515-522): lane ``l`` keeps its own candidate against lane ``l+offset``, so lane 0
+    ends with the candidate whose lane has the smallest 5-bit *reversed* number (lane
+    priority 0, 16, 8, 24, 4, ...).  Thread 0 then prefers warp 0 over warp 1 (535-540).
+    Key: ``(thread // 32, bitreverse5(thread % 32), index)`` with ``thread = index % 64``.
+    Every thread starts from ``(data[0], 0)`` (505-506), which the key covers: unit 0 has
+    the smallest key of all.
     """
+    i = np.arange(K, dtype=np.int64)
+    t = i % 64
+    lane = t % 32
+    rev = np.zeros(K, dtype=np.int64)
+    for b in range(5):
+        rev |= ((lane >> b) & 1) << (4 - b)
+    return ((t // 32) * 32 + rev) * (K + 1) + i
+
+
+def _argmax_ref_order(a: np.ndarray) -> np.ndarray:
+    """Row-wise arg-max with the reference's tie order (see :func:`tie_rank`)."""
     K = a.shape[1]
     mx = a.max(axis=1, keepdims=True)
-    key = (np.arange(K, dtype=np.int64) % 64) * (K + 1) + np.arange(K, dtype=np.int64)
+    key = tie_rank(K)
     masked = np.where(a == mx, key[None, :], np.iinfo(np.int64).max)
     return (masked.min(axis=1) % (K + 1)).astype(np.int32)
 
@@ -192,10 +215,16 @@ def device_phase(Wm: np.ndarray, idx: np.ndarray, f: np.ndarray, V: int, delta: 
     ok = flat != -1
     fv = f[np.where(ok, flat, 0) % V]
     r1 = np.repeat(win, W)
-    np.add.at(ds, (r1[ok], flat[ok]), fv[ok])
     if delta != 0:
+        # a thread adds both terms of its (window, position) back to back (cuda_funcs.cu:665-668);
+        # windows in block order, positions in thread order: one admissible order of the atomics
         r2 = np.repeat(mmax, W)
-        np.add.at(ds, (r2[ok], flat[ok]), (-delta * fv[ok]).astype(F32))
+        rows = np.stack([r1[ok], r2[ok]], axis=1).reshape(-1)
+        cols = np.repeat(flat[ok], 2)
+        vals = np.stack([fv[ok], (-delta * fv[ok]).astype(F32)], axis=1).reshape(-1)
+        np.add.at(ds, (rows, cols), vals)
+    else:
+        np.add.at(ds, (r1[ok], flat[ok]), fv[ok])
     return ds, xx, win, mmax, a_w
 
 

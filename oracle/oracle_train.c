@@ -14,9 +14,9 @@
  *   combine + abs-max  flyvec/src/cu_special_reduction.cu:26-99
  *   step size          flyvec/src/cuda_funcs.cu:1797-1799
  *   update             flyvec/src/cu_special_reduction.cu:316-354
- * Pinning: checked bit-for-bit against the numpy restatement
- * (oracle/flyvec_oracle.py) in tests/test_oracle.py; neither has been checked
- * against the reference's CUDA binary (training parity unpinned, see that file).
+ * Pinning: checked bit for bit against the numpy restatement (oracle/flyvec_oracle.py) and
+ * against the reference's own kernel text executed on the host (oracle/ref_kernels_host.cpp,
+ * built from a reference checkout) in tests/test_oracle.py.
  */
 #include <math.h>
 #include <stdint.h>
@@ -24,9 +24,17 @@
 #include <string.h>
 #include <omp.h>
 
-static int tie_key(int i) { return ((i & 63) << 20) | i; }
+/* Tie order of get_max_and_m_max_kernel_2 (flyvec/src/cuda_funcs.cu:488-561), 64 threads per window:
+ * a thread keeps its lowest index (strict '>', 507-512); the __shfl_down_sync tree with offsets
+ * 16..1 keeps the lower lane at every level (515-522), so among tied lanes the one with the smallest
+ * bit-reversed lane number reaches lane 0; warp 0 is preferred over warp 1 (535-540). */
+static int tie_key(int i) {
+  const int t = i & 63, lane = t & 31;
+  const int rev = ((lane & 1) << 4) | ((lane & 2) << 2) | (lane & 4) | ((lane & 8) >> 2) | ((lane & 16) >> 4);
+  return (((t >> 5) << 5 | rev) << 20) | i;
+}
 
-/* arg-max with the reference's tie order: smallest (index % 64, index) among equal maxima */
+/* arg-max with the reference's tie order: smallest tie_key among equal maxima */
 static int argmax_ref(const float* a, int K) {
   int best = 0;
   for (int i = 1; i < K; ++i) {

@@ -122,16 +122,17 @@ def test_first_step_winners_bit_exact_fp32_and_fp64_paths(built_lib):
 
 def test_exact_ties_follow_reference_order(built_lib):
     """Duplicate units tie exactly; the reference keeps the one with the smallest
-    (index % 64, index) (cuda_funcs.cu:507-540)."""
+    (thread // 32, bitreverse5(thread % 32), index), thread = index % 64 (cuda_funcs.cu:507-540)."""
     p = small_problem(K=200, V=300, W=7, ntok=8000, seed=5)
     W0 = p["W0"].copy()
-    W0[70] = W0[3]      # 70 % 64 = 6 > 3: unit 3 wins ties
-    W0[130] = W0[69]    # 130 % 64 = 2 < 5: unit 130 wins ties
+    W0[70] = W0[3]      # lanes 6 (reversed 12) and 3 (reversed 24): unit 70 wins ties
+    W0[130] = W0[69]    # lanes 2 (reversed 8) and 5 (reversed 20): unit 130 wins ties
+    W0[33] = W0[1]      # warp 0 beats warp 1: unit 1 wins ties
     p["W0"] = W0
     idx = orc.build_idx(p["enc"], p["starts"], p["perm"][:1000], 7, 300)
     ref, _ = orc.winners(orc.activations(W0, idx, None, 300))
-    assert (ref == 3).sum() + (ref == 130).sum() > 0
-    assert (ref == 70).sum() == 0 and (ref == 69).sum() == 0
+    assert (ref == 70).sum() + (ref == 130).sum() + (ref == 1).sum() > 0
+    assert (ref == 3).sum() == 0 and (ref == 69).sum() == 0 and (ref == 33).sum() == 0
     tr = make_trainer(p, 1000)
     win, _, _, _ = tr.step_debug(0, np.float32(2e-4))
     np.testing.assert_array_equal(win[0], ref)

@@ -125,15 +125,98 @@ def test_step_properties():
 
 
 def test_tie_order_of_winner():
+    """Among equal maxima the reference keeps the smallest (thread // 32, bitreverse5(thread % 32), index),
+    thread = index % 64 (cuda_funcs.cu:507-540)."""
     a = np.zeros((1, 200), np.float32)
-    a[0, [70, 3]] = 5.0       # 70 % 64 = 6 > 3
-    assert orc.winners(a)[0][0] == 3
+    a[0, [70, 3]] = 5.0       # lanes 6 (reversed 12) and 3 (reversed 24): unit 70 survives the shuffle tree
+    assert orc.winners(a)[0][0] == 70
     a[:] = 0
-    a[0, [69, 130]] = 5.0     # 130 % 64 = 2 < 5
+    a[0, [69, 130]] = 5.0     # lanes 5 (reversed 20) and 2 (reversed 8)
     assert orc.winners(a)[0][0] == 130
-    a[:] = 1.0                # all equal: index 0
+    a[:] = 0
+    a[0, [1, 32]] = 5.0       # warp 0 beats warp 1 whatever the lane
+    assert orc.winners(a)[0][0] == 1
+    a[:] = 1.0                # all equal: index 0, then thread 0's next unit
     first, second = orc.winners(a)
-    assert first[0] == 0 and second[0] == 64  # after masking 0, the next smallest (i % 64, i) is 64
+    assert first[0] == 0 and second[0] == 64
+
+
+# ---- T4-T13 pinned on the reference's own kernels, executed on the host --------------
+def _need_reference_kernels():
+    if c_oracle.reference_kernels() is None:
+        pytest.skip("oracle/_ref/ref_kernels_host.so not built (no reference checkout)")
+
+
+@pytest.mark.parametrize("K", [2, 5, 33, 64, 65, 100, 400, 1000])
+def test_winners_match_reference_kernel_on_ties(K):
+    """Tie-heavy activations through get_max_and_m_max_kernel_2 itself (64 lock-step threads,
+    the shuffle tree as written)."""
+    _need_reference_kernels()
+    rng = np.random.default_rng(K)
+    a = rng.integers(0, 3, (200, K)).astype(np.float32)
+    a[::7] = 1.0          # every unit ties
+    a[::5, 0] = 2.0       # unit 0 among the maxima
+    a[1::11] -= 20000.0   # everything below the -9999.9999 mask of the second search
+    for r in range(0, 200, 3):  # two-way exact ties on top of random values
+        i, j = rng.choice(K, 2, replace=False)
+        a[r, i] = a[r, j] = 7.0
+    ref_w, ref_m = c_oracle.reference_winners(a)
+    w, m = orc.winners(a)
+    np.testing.assert_array_equal(w, ref_w)
+    np.testing.assert_array_equal(m, ref_m)
+
+
+@pytest.mark.parametrize("K,V,G,B,delta,ties", [
+    (64, 512, 1, 256, 0.0, False), (64, 512, 2, 128, 0.0, False), (48, 300, 3, 100, 0.3, False),
+    (16, 64, 3, 64, 0.5, True), (16, 64, 2, 128, 1.0, True), (8, 32, 1, 300, 0.0, True),
+])
+def test_train_step_matches_reference_kernels(K, V, G, B, delta, ties):
+    """Every stage of one global step against the reference's own kernel text run on the host in
+    the reference's launch sequence: input ids, weighted activations, winner and second winner,
+    xx, the combined direction, nc, the step size and the updated synapses -- all bit for bit,
+    on random weights and on a coarse grid of weights that produces exact ties everywhere."""
+    _need_reference_kernels()
+    p = small_problem(K=K, V=V, W=11, ntok=20000, seed=5)
+    W0 = p["W0"]
+    if ties:
+        W0 = (np.round(np.random.default_rng(1).standard_normal(W0.shape) * 2) / 2).astype(np.float32)
+    eps = np.float32(2e-4)
+    ref = c_oracle.reference_train_step(W0, p["enc"], p["starts"], p["perm"], p["f"], V, 11, B, G, eps, delta=delta)
+    assert ref["replicas_identical"]
+    idxs = [orc.build_idx(p["enc"], p["starts"], p["perm"][g * B:(g + 1) * B], 11, V) for g in range(G)]
+    Wn, info = orc.train_step(W0, idxs, p["f"], V, eps, delta=delta)
+    for g in range(G):
+        np.testing.assert_array_equal(ref["idx"][g], idxs[g])
+        np.testing.assert_array_equal(ref["a_w"][g], info["a_w"][g])
+        np.testing.assert_array_equal(ref["win"][g], info["win"][g])
+        if delta != 0:
+            np.testing.assert_array_equal(ref["mmax"][g], info["mmax"][g])
+        np.testing.assert_array_equal(ref["xx"][g], info["xx"][g])
+    assert ref["nc"] == info["nc"] and ref["s"] == info["s"]
+    np.testing.assert_array_equal(ref["W"], Wn)
+
+
+def test_c_oracle_matches_reference_kernels_over_steps():
+    """The C restatement (the one the GPU parity tests at full shapes use) follows the
+    reference's kernels bit for bit over consecutive steps, 1 and 3 replicas."""
+    _need_reference_kernels()
+    K, V, W, B = 32, 200, 11, 150
+    p = small_problem(K=K, V=V, W=W, ntok=20000, seed=9)
+    eps = np.float32(1e-3)
+    for G in (1, 3):
+        runner = c_oracle.StepRunner(K, 2 * V, V, W, B, G)
+        Wc = p["W0"].copy()
+        Wr = p["W0"].copy()
+        for step in range(3):
+            order = p["perm"][step * G * B:(step + 1) * G * B]
+            idx = np.stack([orc.build_idx(p["enc"], p["starts"], order[g * B:(g + 1) * B], W, V) for g in range(G)])
+            win, xx, nc, s = runner.step(Wc, idx, [B] * G, p["f"], eps)
+            ref = c_oracle.reference_train_step(Wr, p["enc"], p["starts"], order, p["f"], V, W, B, G, eps)
+            Wr = ref["W"]
+            np.testing.assert_array_equal(win, ref["win"])
+            np.testing.assert_array_equal(xx, ref["xx"])
+            assert nc == ref["nc"] and s == ref["s"]
+            np.testing.assert_array_equal(Wc, Wr)
 
 
 def test_schedules():
