@@ -2001,6 +2001,15 @@ void free_all(fv_trainer* tr) {
   delete tr;
 }
 
+// Which tagging kernel runs and on how many CTAs.  force_un = 0: by the size of a step.
+void choose_tag_variant(fv_trainer* tr, int force_un) {
+  const Dev& d = tr->d;
+  const size_t E = (size_t)d.G * d.B * d.W * (1 + d.has_delta);
+  const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS;
+  tr->tag_un = force_un ? force_un : (((E + XX_THREADS - 1) / XX_THREADS > resident) ? 2 : 1);
+  tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, (int)resident);
+}
+
 int create_impl(const fv_config* cfg, fv_trainer* tr) {
   tr->cfg = *cfg;
   tr->device = cfg->device;
@@ -2102,11 +2111,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   // Three CTAs fit an SM (registers); the grid stays resident together with the 1 + PUSH_CTAS CTAs that
   // serve the exchange.  A CTA takes 512 slots per block round while one round covers the step, else
   // 1024 deduplicated in shared memory (2048 per round measured no faster at 8 ranks).
-  {
-    const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS;
-    tr->tag_un = ((E + XX_THREADS - 1) / XX_THREADS > resident) ? 2 : 1;
-    tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, (int)resident);
-  }
+  choose_tag_variant(tr, 0);
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
   {
     // k_apply waits on peers inside the kernel (sharded update), so its grid must be fully resident
@@ -2637,6 +2642,21 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
     }
   }
   return FV_OK;
+}
+
+int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
+  FV_REQUIRE(tr && key, FV_ERR_INVALID, "fv_trainer_set_option: NULL argument");
+  if (strcmp(key, "spin_limit") == 0) {
+    FV_REQUIRE(value >= 1.0 && value <= 4.0e9, FV_ERR_INVALID, "spin_limit must be in [1, 4e9], got %g", value);
+    tr->d.spin_limit = (unsigned)value;
+    return FV_OK;
+  }
+  if (strcmp(key, "tag_variant") == 0) {
+    FV_REQUIRE(value == 0.0 || value == 1.0 || value == 2.0, FV_ERR_INVALID, "tag_variant must be 0 (by size), 1 or 2, got %g", value);
+    choose_tag_variant(tr, (int)value);
+    return FV_OK;
+  }
+  return fv::fail(FV_ERR_INVALID, "fv_trainer_set_option: unknown option %s", key);
 }
 
 int fv_trainer_comm_mode(fv_trainer* tr, int* mode) {

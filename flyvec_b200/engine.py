@@ -161,6 +161,10 @@ class Trainer:
         check(_lib.lib().fv_trainer_init_comm(self._h, buf))
 
 
+    def set_option(self, key: str, value: float):
+        """Tuning knobs that change no result: ``spin_limit``, ``tag_variant``."""
+        check(_lib.lib().fv_trainer_set_option(self._h, key.encode(), float(value)))
+
     @property
     def comm_mode(self) -> int:
         """0 = single rank, 1 = NCCL all-gather per step, 2 = peer-memory mailboxes."""

@@ -180,6 +180,13 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
  * (cu_special_reduction.cu:61-66, 345-346). */
 int fv_comm_unique_id(uint8_t id[128]);
 int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
+/* String-keyed tuning knobs in the manner of set_model_param_int / set_model_param_float
+ * (model_descriptor.cu:50-112); none changes a result.
+ *   "spin_limit"   polls a device-side wait for a peer's word makes before it gives up and the call
+ *                  returns FV_ERR_TIMEOUT (default 8388608, about ten seconds);
+ *   "tag_variant"  1: the scatter bookkeeping claims positions one slot per thread; 2: it first
+ *                  deduplicates 1024 slots in shared memory; 0: chosen by the size of a step. */
+int fv_trainer_set_option(fv_trainer* tr, const char* key, double value);
 /* How the ranks exchange their per-step packets (B winners and K floats of xx per rank):
  *   0  single rank / not initialised;
  *   1  one NCCL all-gather per step;

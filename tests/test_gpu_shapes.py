@@ -1,0 +1,173 @@
+"""Parity at the shapes the benchmark configurations name, against the C restatement of the
+reference's step (oracle/oracle_train.c, itself checked against the reference's kernels in
+tests/test_oracle.py).  Every kernel variant the production sizes select is reached here:
+the two-slot tagging kernel with its shared-memory dedupe, the periodic fold of the per-unit
+scales, the eight-column-group forward kernel of K = 1000.  All calls go through the C ABI."""
+import numpy as np
+import pytest
+
+from flyvec_b200 import _lib, synth
+from flyvec_b200.engine import Trainer
+from oracle import c_oracle
+from oracle import flyvec_oracle as orc
+from tests.helpers import check_winners, small_problem
+
+pytestmark = pytest.mark.gpu
+
+#: element-wise bound on the synapses after a run: |gpu - ref| <= REL * |ref| + FLOOR.
+#: REL is the parity target's 1e-4; FLOOR covers weights near zero, where a relative bound
+#: means nothing (weights are O(1), one update moves a weight by at most the learning rate).
+REL, FLOOR = 1e-4, 1e-6
+
+
+def assert_weights_close(Wgpu, Wref):
+    err = np.abs(Wgpu.astype(np.float64) - Wref.astype(np.float64))
+    bound = REL * np.abs(Wref.astype(np.float64)) + FLOOR
+    worst = np.unravel_index(np.argmax(err - bound), err.shape)
+    assert (err <= bound).all(), f"weight {worst}: gpu {Wgpu[worst]!r} ref {Wref[worst]!r}"
+    return float((err / (np.abs(Wref) + 1e-30)).max())
+
+
+def corpus(ntok, V, W, s, mean_len, seed):
+    enc, off = synth.make_corpus(ntok, V, s=s, mean_len=mean_len, min_len=W, seed=seed)
+    starts = orc.enumerate_windows(off, W)
+    f = orc.inverse_word_frequency(enc, V, saturate_fp32=False)
+    return enc, off, starts, f
+
+
+def trainer(K, V, W, B, enc, off, W0, perm, world=1, flags=0, delta=0.0):
+    tr = Trainer(hid=K, vocab=V, window=W, batch=B, lr0=2e-4, world=world, flags=flags, delta=delta)
+    tr.set_corpus(enc, off)
+    tr.set_weights(W0)
+    tr.set_permutation(perm)
+    return tr
+
+
+def test_config1_shapes_free_running_300_steps(built_lib):
+    """Config 1 (K=400, V=20000, w=11, 10000 windows per step), 300 consecutive steps with no
+    host interference: the scales are folded into the weights twice on the way (every 128 steps).
+    Per-step normalisers and the final synapses against 300 oracle steps."""
+    K, V, W, B, steps = 400, 20000, 11, 10000, 300
+    enc, off, starts, f = corpus(5_500_000, V, W, 1.0, 25.0, seed=101)
+    assert len(starts) >= steps * B
+    perm = np.random.default_rng(201).permutation(len(starts)).astype(np.uint64)
+    W0 = synth.make_weights(K, 2 * V, seed=1)
+    eps = np.float32(2e-4)
+    tr = trainer(K, V, W, B, enc, off, W0, perm)
+    log = tr.run_steps(0, steps, eps, want_log=True)
+    Wgpu = tr.get_weights()
+    tr.close()
+    runner = c_oracle.StepRunner(K, 2 * V, V, W, B, 1)
+    Wref = W0.copy()
+    ncs = np.zeros(steps, np.float32)
+    for t in range(steps):
+        idx = orc.build_idx(enc, starts, perm[t * B:(t + 1) * B], W, V)
+        _, _, ncs[t], _ = runner.step(Wref, idx[None], [B], f, eps)
+    np.testing.assert_allclose(log["nc"], ncs, rtol=1e-4)
+    assert_weights_close(Wgpu, Wref)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_config2_shapes_emulated_ranks(built_lib, world):
+    """Config 2's global step (world x 10000 windows): every rank's block on one GPU, which makes
+    the scatter bookkeeping large enough for the deduplicating tagging kernel.  Teacher-forced
+    steps against the oracle's `ngpus = world` combine: winners exact (near ties excepted), xx,
+    normaliser, synapses."""
+    K, V, W, B, steps = 400, 20000, 11, 10000, 3
+    enc, off, starts, f = corpus(2_000_000, V, W, 1.0, 25.0, seed=102)
+    assert len(starts) >= steps * world * B
+    perm = np.random.default_rng(202).permutation(len(starts)).astype(np.uint64)
+    W0 = synth.make_weights(K, 2 * V, seed=2)
+    eps = np.float32(2e-4)
+    tr = trainer(K, V, W, B, enc, off, W0, perm, world=world, flags=_lib.FV_FLAG_EMULATE_RANKS)
+    runner = c_oracle.StepRunner(K, 2 * V, V, W, B, world)
+    Wcur = W0.copy()
+    for t in range(steps):
+        win, xx, nc, s = tr.step_debug(t, eps)
+        Wgpu = tr.get_weights()
+        order = perm[t * world * B:(t + 1) * world * B]
+        idx = np.stack([orc.build_idx(enc, starts, order[g * B:(g + 1) * B], W, V) for g in range(world)])
+        Wref = Wcur.copy()
+        rwin, rxx, rnc, rs = runner.step(Wref, idx, [B] * world, f, eps)
+        flips = 0
+        for g in range(world):
+            if not np.array_equal(win[g], rwin[g]):
+                flips += check_winners(win[g], rwin[g], orc.activations(Wcur, idx[g], None, V))
+        if flips == 0:
+            np.testing.assert_allclose(xx, rxx, rtol=2e-5, atol=1e-7)
+            np.testing.assert_allclose(nc, rnc, rtol=1e-5)
+            assert_weights_close(Wgpu, Wref)
+        assert flips <= 2
+        Wcur = Wgpu
+
+
+@pytest.mark.parametrize("K,V,W,B,world,delta", [(64, 40, 11, 700, 2, 0.0), (100, 64, 5, 2000, 1, 0.0), (32, 30, 7, 900, 3, 0.4)])
+def test_dedupe_tagging_kernel_on_duplicate_heavy_steps(built_lib, K, V, W, B, world, delta):
+    """The deduplicating tagging kernel forced at small shapes: a tiny vocabulary makes nearly every
+    (unit, token) pair occur many times inside one block of 1024 slots, ties included."""
+    p = small_problem(K=K, V=V, W=W, ntok=30000, seed=21, zipf_s=1.2)
+    flags = _lib.FV_FLAG_EMULATE_RANKS if world > 1 else 0
+    tr = trainer(K, V, W, B, p["enc"], p["off"], p["W0"], p["perm"], world=world, flags=flags, delta=delta)
+    tr.set_option("tag_variant", 2)
+    eps = np.float32(5e-4)
+    Wcur = p["W0"]
+    for t in range(3):
+        win, xx, nc, s = tr.step_debug(t, eps)
+        Wgpu = tr.get_weights()
+        order = p["perm"][t * world * B:(t + 1) * world * B]
+        idxs = [orc.build_idx(p["enc"], p["starts"], order[g * B:(g + 1) * B], W, V) for g in range(world)]
+        Wref, info = orc.train_step(Wcur, idxs, p["f"], V, eps, delta=delta)
+        for g in range(world):
+            np.testing.assert_array_equal(win[g], info["win"][g])
+        np.testing.assert_allclose(nc, info["nc"], rtol=1e-5)
+        assert_weights_close(Wgpu, Wref)
+        Wcur = Wgpu
+    tr.close()
+
+
+def test_config3_shapes_large_model(built_lib):
+    """Config 3 (K=1000, V=50000, w=15, 20000 windows per step; 400 MB of synapses, beyond the L2):
+    the widest forward kernel and the two-group scan.  Teacher-forced steps, the last one with the
+    anti-Hebbian term on."""
+    K, V, W, B = 1000, 50000, 15, 20000
+    enc, off, starts, f = corpus(1_500_000, V, W, 1.1, 40.0, seed=103)
+    assert len(starts) >= 3 * B
+    perm = np.random.default_rng(203).permutation(len(starts)).astype(np.uint64)
+    W0 = synth.make_weights(K, 2 * V, seed=3)
+    eps = np.float32(2e-4)
+    tr = trainer(K, V, W, B, enc, off, W0, perm)
+    runner = c_oracle.StepRunner(K, 2 * V, V, W, B, 1)
+    Wcur = W0.copy()
+    for t in range(3):
+        win, xx, nc, s = tr.step_debug(t, eps)
+        Wgpu = tr.get_weights()
+        idx = orc.build_idx(enc, starts, perm[t * B:(t + 1) * B], W, V)
+        Wref = Wcur.copy()
+        rwin, rxx, rnc, rs = runner.step(Wref, idx[None], [B], f, eps)
+        flips = 0
+        if not np.array_equal(win[0], rwin[0]):
+            flips = check_winners(win[0], rwin[0], orc.activations(Wcur, idx, None, V))
+        if flips == 0:
+            np.testing.assert_allclose(xx, rxx, rtol=2e-5, atol=1e-7)
+            np.testing.assert_allclose(nc, rnc, rtol=1e-5)
+            assert_weights_close(Wgpu, Wref)
+        assert flips <= 2
+        Wcur = Wgpu
+    tr.close()
+
+
+def test_config3_width_with_second_winner(built_lib):
+    """K = 1000 with delta != 0 (second winner through the widest forward kernel), batch reduced so
+    that the numpy oracle, which carries the anti-Hebbian term, finishes in seconds."""
+    K, V, W, B = 1000, 3000, 15, 1500
+    p = small_problem(K=K, V=V, W=W, ntok=60000, seed=33, mean_len=40.0, zipf_s=1.1)
+    tr = trainer(K, V, W, B, p["enc"], p["off"], p["W0"], p["perm"], delta=0.3)
+    eps = np.float32(2e-4)
+    win, xx, nc, s = tr.step_debug(0, eps)
+    Wgpu = tr.get_weights()
+    tr.close()
+    idx = orc.build_idx(p["enc"], p["starts"], p["perm"][:B], W, V)
+    Wref, info = orc.train_step(p["W0"], [idx], p["f"], V, eps, delta=0.3)
+    assert check_winners(win[0], info["win"][0], orc.activations(p["W0"], idx, None, V)) == 0
+    np.testing.assert_allclose(nc, info["nc"], rtol=1e-5)
+    assert_weights_close(Wgpu, Wref)
