@@ -56,11 +56,11 @@ class FvRunStats(C.Structure):
     _fields_ = [
         ("steps", C.c_uint64), ("windows", C.c_uint64), ("seconds", C.c_double), ("fwd_seconds", C.c_double),
         ("exch_seconds", C.c_double), ("upd_seconds", C.c_double), ("kernel_launches", C.c_uint64),
-        ("last_nc", C.c_float), ("last_scale", C.c_float), ("device_error", C.c_uint32), ("reserved", C.c_uint32),
+        ("last_nc", C.c_float), ("last_scale", C.c_float), ("device_error", C.c_uint32), ("timed_steps", C.c_uint32),
     ]
 
     def as_dict(self):
-        return {k: getattr(self, k) for k, _ in self._fields_ if k != "reserved"}
+        return {k: getattr(self, k) for k, _ in self._fields_}
 
 
 _P = C.c_void_p
@@ -85,6 +85,12 @@ _PROTOTYPES = {
     "fv_trainer_get_permutation": ([_P, _P], C.c_int),
     "fv_trainer_run_epoch": ([_P, C.c_uint64, C.c_uint64, C.POINTER(FvRunStats)], C.c_int),
     "fv_trainer_run_steps": ([_P, C.c_uint64, C.c_uint64, C.c_float, _P, _P, C.POINTER(FvRunStats)], C.c_int),
+    "fv_trainer_run_steps_timed": ([_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.POINTER(FvRunStats)], C.c_int),
+    "fv_trainers_link": ([C.POINTER(_P), C.c_int32], C.c_int),
+    "fv_trainers_run_steps": ([C.POINTER(_P), C.c_int32, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, _P, _P,
+                               C.POINTER(FvRunStats)], C.c_int),
+    "fv_trainers_run_epoch": ([C.POINTER(_P), C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(FvRunStats)], C.c_int),
+    "fv_trainer_last_packets": ([_P, _P, _P], C.c_int),
     "fv_trainer_run_steps_host": ([_P, _P, C.c_uint64, C.c_float, _P, _P, C.POINTER(FvRunStats)], C.c_int),
     "fv_trainer_run_steps_host_local": ([_P, _P, C.c_uint64, C.c_float, _P, _P, C.POINTER(FvRunStats)], C.c_int),
     "fv_trainer_step_debug": ([_P, C.c_uint64, C.c_float, _P, _P, C.POINTER(C.c_float), C.POINTER(C.c_float)],

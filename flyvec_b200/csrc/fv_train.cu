@@ -36,6 +36,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "fv_common.h"
@@ -59,8 +60,8 @@ struct StepCtl {
   int32_t xx_kexp;        // xx is accumulated in units of 2^-xx_kexp this step (written by k_forward)
   uint32_t fwd_next[2];   // window tickets k_forward hands out beyond the first round, by step parity
   uint32_t scan_ticket;   // CTAs of the running k_scan that have finished
-  uint32_t apply_ticket;  // CTAs of the running k_apply that have finished their own slots
-  uint32_t out_count;     // entries in this step's outbox (sharded update)
+  uint32_t apply_ticket;  // (unused)
+  uint32_t out_count;     // (unused)
   uint32_t pad;
   uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
   // Device-side phase clock: every step kernel's first thread charges the time since the previous
@@ -92,8 +93,10 @@ struct Dev {
   uint32_t* mail;          // this rank's mailbox: MAIL_HDR words of flags, then packets [2][G][P]
   uint32_t* const* peers;  // device table of all ranks' mailboxes (peer-mapped), or null
   unsigned spin_limit;     // polls before a wait on a peer's flag gives up
-  int shard;               // 1: rows i with i % G == rank are updated here, the rest arrives from their owners
-  size_t outbox_off;       // word offset of the outbox [2][G*B*W] of (position, value) pairs inside the mailbox
+  int shard;               // 1: rows i with i % G == rank are tagged and scanned here; every other row's scatter
+                           // counts arrive from its owner (see the inbox below)
+  size_t inbox_off;        // word offset of the inbox [G][G*B*W] of 64-bit update entries inside the mailbox
+  size_t inbox_cap;        // entries per sender
   // xx accumulators [XX_SLOTS][Kp]: fixed-point sums (high and low 32-bit digits, each in a 64-bit word) and the
   // number of windows won; filled by k_forward, turned into floats and cleared by xx_finish
   unsigned long long* xx_hi;
@@ -113,10 +116,10 @@ struct Dev {
 // Mailbox header (32-bit words).  Everything is indexed [parity][sender]; a flag holds the sequence
 // number (tick + local + 1) of the step whose data is complete.
 constexpr int MAX_RANKS = 16;
-// The partial normaliser and the outbox count travel inside their flag: one 64-bit word
+// The partial normaliser and the length of a rank's entry list travel inside their flag: one 64-bit word
 // (sequence number in the high half, payload in the low half) written with a single store.
 constexpr int WORD_NC = 2 * MAX_RANKS;         // u64 [2][MAX_RANKS]: seq | float bits of sender's partial nc
-constexpr int WORD_OUT = 6 * MAX_RANKS;        // u64 [2][MAX_RANKS]: seq | entries in sender's outbox
+constexpr int WORD_OUT = 6 * MAX_RANKS;        // u64 [2][MAX_RANKS]: seq | records in sender's touched-position list
 constexpr int MAIL_HDR = 512;                  // words; keeps the packets 2 KiB aligned
 // Packet of rank r for the step of the given parity: P 64-bit words -- B winners, (with delta) B
 // second winners at MO, Kp floats of xx at XO.  Every word carries its own flag: payload in the low
@@ -134,8 +137,20 @@ __device__ __forceinline__ unsigned long long pk_word(uint32_t payload, uint32_t
   return ((unsigned long long)seq << 32) | payload;
 }
 
-__device__ __forceinline__ uint2* outbox(const Dev& d, const uint32_t* mail, int parity) {
-  return reinterpret_cast<uint2*>(const_cast<uint32_t*>(mail) + d.outbox_off) + (size_t)parity * d.G * d.B * d.W * (1 + d.has_delta);
+// Sharded update.  Rank r owns the matrix rows i with i % G == r: it alone tags them, knows how often
+// each of their positions was asked for and evaluates D there.  The other replicas need the same
+// counts to move their copies: the owner stores one 64-bit entry per record of its touched-position
+// list -- low half: position | ENTRY_VALID (or ENTRY_HOLE for a reserved record nobody claimed), high
+// half: the count -- into every peer's inbox at [owner][record index], one 8-byte store that arrives
+// whole.  A receiver takes entries [0, n) of a sender once it has the sender's record count n, waits
+// (bounded) for an entry that is not there yet, applies it and clears it, so an entry is non-zero only
+// between its arrival and its use.  A sender cannot write the entries of the next step before the
+// receiver has used this step's: it needs the receiver's next winners first, and those leave after
+// the receiver's update has finished.
+constexpr uint32_t ENTRY_VALID = 0x80000000u;
+constexpr uint32_t ENTRY_HOLE = 0xffffffffu;
+__device__ __forceinline__ unsigned long long* inbox(const Dev& d, const uint32_t* mail, int sender) {
+  return reinterpret_cast<unsigned long long*>(const_cast<uint32_t*>(mail) + d.inbox_off) + (size_t)sender * d.inbox_cap;
 }
 __device__ __forceinline__ uint32_t fdiv(uint32_t n, uint32_t m, uint32_t s) {
   return (uint32_t)(((unsigned long long)n * m) >> s);
@@ -156,16 +171,16 @@ __device__ __forceinline__ void phase_mark(StepCtl* c, uint32_t next) {
   c->t_mark = now;
   c->phase_now = next;
 }
-// Message passing between GPUs.  Producer: payload stores, ONE system-scope fence by one thread,
-// then relaxed flag stores.  Consumer: relaxed polls of the flag (they are served by the local L2,
-// where a peer's store over NVLink lands), one acquire load once the flag matches.
+// Message passing between GPUs: every word carries its own flag (a sequence number or a valid bit) and
+// is written with ONE relaxed 8-byte store, which arrives whole; a consumer polls the word with relaxed
+// loads (served by the local L2, where a peer's store over NVLink lands).  No fences.
 __device__ __forceinline__ void store_relaxed_sys64(unsigned long long* p, unsigned long long v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ void push_entry(const Dev& d, int k, uint32_t lo, int count) {
+  const unsigned long long e = ((unsigned long long)(uint32_t)count << 32) | lo;
+  for (int r = 0; r < d.G; ++r)
+    if (r != d.rank) store_relaxed_sys64(inbox(d, d.peers[r], d.rank) + k, e);
 }
 __device__ __forceinline__ unsigned long long load_relaxed_sys64(const unsigned long long* p) {
   unsigned long long v;
@@ -228,6 +243,11 @@ __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps, floa
   ctl->eps = eps;
   ctl->delta = delta;
   ctl->fwd_next[0] = ctl->fwd_next[1] = 0u;
+  for (int i = 0; i < 8; ++i) ctl->phase_ns[i] = 0ull;
+  ctl->t_mark = global_timer();
+  ctl->phase_now = PH_OTHER;
+}
+__global__ void k_reset_phase_clock(StepCtl* ctl) {
   for (int i = 0; i < 8; ++i) ctl->phase_ns[i] = 0ull;
   ctl->t_mark = global_timer();
   ctl->phase_now = PH_OTHER;
@@ -713,11 +733,19 @@ __device__ __forceinline__ void push_winners(const Dev& d, int parity, int cta, 
     }
   }
 }
+// CTA 0 finishes xx; further CTAs (when launched) push this rank's winners to the peers.  The tagging
+// kernel does both in its first CTAs; this kernel does them alone where xx must be complete before an
+// all-gather, and where several ranks share one stream, so that every rank's words are out before any
+// rank's tagging looks for them.
 __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
   grid_dependency_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_XX);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
-  xx_finish(d, local);
+  if (blockIdx.x == 0) {
+    xx_finish(d, local);
+  } else {
+    push_winners(d, (int)((d.ctl->tick + local) & 1), blockIdx.x - 1, gridDim.x - 1);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1083,6 +1111,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     const int cn = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
     rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
     cs[u] = (float)(cp + (int)(rc[u].w & 0xffffu)) - delta * (float)(cn + (int)(rc[u].w >> 16));
+    // sharded: the peers learn this record's count now, long before they need it
+    if (d.shard && k < nrec) push_entry(d, k, rc[u].w ? (rc[u].x | ENTRY_VALID) : ENTRY_HOLE, cp + (int)(rc[u].w & 0xffffu));
   }
 
   // part 2: column maxima of |wt| with tags read as 0
@@ -1142,7 +1172,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   for (int k = e0 + TS * nthreads; k < nrec; k += nthreads) {
     const uint4 r = d.rec[k];
     const int cn = d.has_delta ? d.cntn[k] : 0;
-    touched((float)(d.cnt[k] + (int)(r.w & 0xffffu)) - delta * (float)(cn + (int)(r.w >> 16)), r);
+    const int cp = d.cnt[k];
+    touched((float)(cp + (int)(r.w & 0xffffu)) - delta * (float)(cn + (int)(r.w >> 16)), r);
+    if (d.shard) push_entry(d, k, r.w ? (r.x | ENTRY_VALID) : ENTRY_HOLE, cp + (int)(r.w & 0xffffu));
   }
   __shared__ uint32_t s_tmax;
   if (threadIdx.x == 0) s_tmax = 0u;
@@ -1181,9 +1213,12 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   }
   __syncthreads();
   if (threadIdx.x < d.G) {
+    // the partial normaliser to everybody (this rank included), the length of the entry list to the peers
     const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
     unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
     store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_red[0]));
+    unsigned long long* outw = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
+    store_relaxed_sys64(outw + p * MAX_RANKS + d.rank, (seq << 32) | (unsigned)nrec);
   }
 }
 
@@ -1224,10 +1259,14 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   __syncthreads();
   const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
   __shared__ uint32_t sWord[MAX_RANKS];
+  __shared__ uint32_t sCount[MAX_RANKS];
   if (d.shard && threadIdx.x < d.G) {
-    // every rank's partial normaliser (pushed by its k_scan) must have arrived, ours included
+    // every rank's partial normaliser (pushed by its k_scan) must have arrived, ours included,
+    // and with it the length of its entry list
     const unsigned long long* words = reinterpret_cast<const unsigned long long*>(d.mail + WORD_NC);
     if (!wait_word(d, words + p * MAX_RANKS + threadIdx.x, seq, &sWord[threadIdx.x])) sFail = 1;
+    const unsigned long long* outw = reinterpret_cast<const unsigned long long*>(d.mail + WORD_OUT);
+    if (!wait_word(d, outw + p * MAX_RANKS + threadIdx.x, seq, &sCount[threadIdx.x])) sFail = 1;
   }
   __syncthreads();
   if (sFail) return;
@@ -1270,15 +1309,16 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   __syncthreads();
 
   const int E = d.G * d.B * d.W;
-  uint2* __restrict__ my_out = outbox(d, d.mail, p);
   uint32_t vmax = 0u;
   const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(E * (1 + d.has_delta)));
   const float delta = d.ctl->delta;
   if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->list_count[p ^ 1] = 0u;  // the next step counts from zero
-  if (!d.shard) {
+  const int nthreads = gridDim.x * blockDim.x;
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  {
+    // this rank's records: the parked weight comes back with its scatter term
     constexpr int UN = 4;
-    const int nthreads = gridDim.x * blockDim.x;
-    for (int k0 = blockIdx.x * blockDim.x + threadIdx.x; k0 < nrec; k0 += UN * nthreads) {
+    for (int k0 = gtid; k0 < nrec; k0 += UN * nthreads) {
       int cp[UN], cn[UN];
       uint4 r[UN];
 #pragma unroll
@@ -1303,97 +1343,63 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
       }
     }
   }
-  __shared__ unsigned s_wcount[8], s_base;
-  for (int k0 = blockIdx.x * blockDim.x; d.shard && k0 < nrec; k0 += gridDim.x * blockDim.x) {
-    const int k = k0 + (int)threadIdx.x;
-    uint4 r = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
-    const int c = r.w ? 1 : 0;  // a live record
-    float v = 0.f;
-    if (c > 0) {
-      const int mu = (int)(r.x % (uint32_t)d.Kp);
-      const int cn = d.has_delta ? d.cntn[k] : 0;
-      const double scat = (double)(d.cnt[k] + (int)(r.w & 0xffffu)) - (double)delta * (double)(cn + (int)(r.w >> 16));
-      v = (float)((double)__uint_as_float(r.y) + scat * (double)__uint_as_float(r.z) * sX[mu]);
-      d.wt[r.x] = v;
-      d.rec[k].w = 0u;
-      d.cnt[k] = 0;
-      if (d.has_delta) d.cntn[k] = 0;
-      vmax = max(vmax, __float_as_uint(fabsf(v)));
-    }
-    {
-      // the other replicas need this value too: append (position, value) to this step's outbox;
-      // slots are handed out per CTA and loop round (one global atomic), then per warp, then per lane
-      const unsigned owners = __ballot_sync(FULL, c > 0);
-      const int wic = threadIdx.x >> 5, ln = threadIdx.x & 31;
-      if (ln == 0) s_wcount[wic] = (unsigned)__popc(owners);
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        unsigned tot = 0;
-        for (int w = 0; w < 8; ++w) {
-          const unsigned cw = s_wcount[w];
-          s_wcount[w] = tot;
-          tot += cw;
-        }
-        s_base = tot ? atomicAdd(&d.ctl->out_count, tot) : 0u;
-      }
-      __syncthreads();
-      if (c > 0) {
-        const unsigned slot = s_base + s_wcount[wic] + __popc(owners & ((1u << ln) - 1u));
-        my_out[slot] = make_uint2(r.x, __float_as_uint(v));
-      }
-      __syncthreads();
-    }
-  }
   if (d.shard) {
-    // publish: when every CTA has written its entries, the last one tells the peers how many there are
-    __shared__ unsigned s_last;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      // device-scope fence per CTA (covers the CTA's entries, ordered before it by the barrier); the one
-      // system-scope fence is issued by the CTA that publishes.  A system fence from every CTA costs
-      // several microseconds when hundreds of them do it at once.
-      __threadfence();
-      s_last = (atomicAdd(&d.ctl->apply_ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
-    }
-    __syncthreads();
-    if (s_last) {
-      if (threadIdx.x == 0) __threadfence_system();
-      __syncthreads();
-      const unsigned count = *reinterpret_cast<volatile unsigned*>(&d.ctl->out_count);
-      if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
-        // thread 0's system fence above (before the ticket) ordered this CTA's entries; the other
-        // CTAs did the same before their tickets, which this CTA has observed
-        unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
-        store_relaxed_sys64(words + p * MAX_RANKS + d.rank, ((unsigned long long)seq << 32) | count);
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        d.ctl->apply_ticket = 0u;
-        d.ctl->out_count = 0u;
-      }
-    }
-    // pull: the rows owned elsewhere take the values their owners computed.  All CTAs of this
-    // grid are resident (the launch is sized for that), so waiting here cannot starve the
-    // CTAs that still have to publish.
-    if (threadIdx.x < d.G && (int)threadIdx.x != d.rank) {
-      const unsigned long long* words = reinterpret_cast<const unsigned long long*>(d.mail + WORD_OUT);
-      if (!wait_word(d, words + p * MAX_RANKS + threadIdx.x, seq, &sWord[threadIdx.x])) sFail = 1;
-      (void)load_acquire_sys(d.mail + WORD_OUT + 2 * (p * MAX_RANKS + threadIdx.x));  // order the list reads after it
-    }
-    __syncthreads();
-    if (sFail) return;
-    const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gthreads = gridDim.x * blockDim.x;
+    // the rows owned elsewhere: the same arithmetic on this replica's copy of the weight, with the
+    // count the owner sent (the owner's parked weight and this copy are the same number)
+    constexpr int UN = 4;
+    const uint32_t limit = (uint32_t)((size_t)d.N * d.Kp);
     for (int r = 0; r < d.G; ++r) {
       if (r == d.rank) continue;
-      const unsigned n_r = sWord[r];
-      const uint2* __restrict__ theirs = outbox(d, d.peers[r], p);
-      for (unsigned k = gtid; k < n_r; k += gthreads) {
-        const uint2 pv = __ldcg(theirs + k);
-        if (pv.x < (unsigned)((size_t)d.N * d.Kp)) {
-          reinterpret_cast<uint32_t*>(d.wt)[pv.x] = pv.y;
-          vmax = max(vmax, pv.y & ABS_MASK);
-        } else {
-          atomicOr(&d.ctl->error, FV_DEVERR_SLOT_RANGE);
+      const int n_r = (int)min(sCount[r], (uint32_t)d.inbox_cap);
+      unsigned long long* __restrict__ box = inbox(d, d.mail, r);
+      for (int k0 = gtid; k0 < n_r; k0 += UN * nthreads) {
+        unsigned long long e[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int k = k0 + u * nthreads;
+          e[u] = (k < n_r) ? load_relaxed_sys64(box + k) : (unsigned long long)ENTRY_HOLE;
+        }
+        uint32_t w_old[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int k = k0 + u * nthreads;
+          if (!((uint32_t)e[u] & ENTRY_VALID)) {  // still on its way (bounded wait)
+            unsigned polls = 0;
+            for (;;) {
+              e[u] = load_relaxed_sys64(box + k);
+              if ((uint32_t)e[u] & ENTRY_VALID) break;
+              if (wait_expired(d, polls)) {
+                e[u] = (unsigned long long)ENTRY_HOLE;
+                break;
+              }
+            }
+          }
+          const uint32_t lo = (uint32_t)e[u];
+          w_old[u] = 0u;
+          if (lo != ENTRY_HOLE) {
+            if ((lo & ~ENTRY_VALID) < limit) {
+              w_old[u] = __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + (lo & ~ENTRY_VALID));
+            } else {
+              atomicOr(&d.ctl->error, FV_DEVERR_SLOT_RANGE);
+              e[u] = (unsigned long long)ENTRY_HOLE;
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int k = k0 + u * nthreads;
+          if (k >= n_r) continue;
+          box[k] = 0ull;  // used
+          const uint32_t lo = (uint32_t)e[u];
+          if (lo == ENTRY_HOLE) continue;
+          const uint32_t pos = lo & ~ENTRY_VALID;
+          const int irow = (int)fdiv(pos, d.mKp, d.sKp);
+          const int mu = (int)pos - irow * d.Kp;
+          const double scat = (double)(int)(uint32_t)(e[u] >> 32);
+          const float f = __ldg(d.f + (irow >= d.V ? irow - d.V : irow));
+          const float v = (float)((double)__uint_as_float(w_old[u]) + scat * (double)f * sX[mu]);
+          d.wt[pos] = v;
+          vmax = max(vmax, __float_as_uint(fabsf(v)));
         }
       }
     }
@@ -1692,6 +1698,9 @@ struct fv_trainer {
   uint32_t* peer_mail[16] = {nullptr};      // peers' mailboxes mapped into this process
   uint32_t** d_peer_table = nullptr;
   int comm_mode = 0;                         // 0 none, 1 NCCL all-gather per step, 2 peer-memory mailboxes
+  bool linked = false;                       // peers are trainers of this process (fv_trainers_link), not IPC mappings
+  bool lockstep = false;                     // linked ranks sharing one device and one stream: phases run rank after rank
+  bool own_stream = true;                    // false: `stream` belongs to rank 0 of the group
   unsigned long long* d_xx_acc = nullptr;  // xx_hi [Kp], xx_lo [Kp]
   uint32_t* d_xx_wins = nullptr;
   int32_t* d_cnt = nullptr;
@@ -1783,47 +1792,70 @@ int fold_weights(fv_trainer* tr, int local) {
   return FV_OK;
 }
 
-// One global step on tr->stream.  `idx` holds this step's input ids (all ranks' windows).
-// Adds the kernels launched to *launches.
-int enqueue_step(fv_trainer* tr, int local, const int32_t* idx, uint64_t* launches) {
+// One global step on tr->stream is four phases, each a kernel (or a short run of kernels):
+//   0  forward pass (with NCCL exchange: + k_xx + the all-gather; with emulated ranks: every rank's block in turn)
+//   1  tagging (+ xx_finish and the winner push in its first CTAs)
+//   2  scan
+//   3  apply
+// `idx` holds this step's input ids (all ranks' windows).  Adds the kernels launched to *launches.
+constexpr int STEP_PHASES = 5;
+int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint64_t* launches) {
   const Dev& d = tr->d;
   const bool emulate = (d.flags & FV_FLAG_EMULATE_RANKS) != 0;
   const bool single = (d.G == 1);
-  if (emulate && !single) {
-    // every rank's block in turn, each into its own packet slot
-    const int own_rank = tr->d.rank;
-    for (int r = 0; r < d.G; ++r) {
-      tr->d.rank = r;
-      FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
-      launch_pdl(k_xx, 1, XX_THREADS, (size_t)0, tr->stream, tr->d, local);
-      *launches += 2;
-    }
-    tr->d.rank = own_rank;
-  } else {
-    FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
-    *launches += 1;
-    if (tr->comm_mode == 1) {
-      // k_xx finishes the packet, one all-gather delivers everybody's
-      launch_pdl(k_xx, 1, XX_THREADS, (size_t)0, tr->stream, d, local);
+  // several ranks on one stream: a rank's winners and xx must be out before any rank tags, so they
+  // leave in a kernel of their own (phase 1) instead of in the first CTAs of the tagging kernel
+  const bool split_exchange = tr->lockstep && tr->comm_mode == 2 && !emulate && !single;
+  if (phase == 1) {
+    if (split_exchange) {
+      launch_pdl(k_xx, 1 + PUSH_CTAS, XX_THREADS, (size_t)0, tr->stream, d, local);
       *launches += 1;
-      const int parity = (int)((tr->ticks + (unsigned long long)local) & 1);
-      uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P * 2;  // packets are P 64-bit words
-      const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P * 2, base, (size_t)d.P * 2, NCCL_UINT32, tr->comm, tr->stream);
-      if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
     }
+    return FV_OK;
   }
-  // One rank, or peer mailboxes: the first CTAs of the tagging kernel compute xx beside the tagging
-  // (and, with mailboxes, push winners first and xx last); otherwise xx is complete already.
-  const bool fused = single || (tr->comm_mode == 2 && !emulate);
-  const size_t table_smem = tag_table_bytes(tr->tag_un);
-  const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
-  launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx,
-             xx_ctas, push_ctas);
-  launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
-  launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
-  FV_CUDA(cudaGetLastError());
-  *launches += 3;
-  tr->steps_since_fold += 1;
+  if (phase > 1) --phase;
+  if (phase == 0) {
+    if (emulate && !single) {
+      // every rank's block in turn, each into its own packet slot
+      const int own_rank = tr->d.rank;
+      for (int r = 0; r < d.G; ++r) {
+        tr->d.rank = r;
+        FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
+        launch_pdl(k_xx, 1, XX_THREADS, (size_t)0, tr->stream, tr->d, local);
+        *launches += 2;
+      }
+      tr->d.rank = own_rank;
+    } else {
+      FV_DISPATCH_NT(tr->NT, launch_forward, tr, local, idx);
+      *launches += 1;
+      if (tr->comm_mode == 1) {
+        // k_xx finishes the packet, one all-gather delivers everybody's
+        launch_pdl(k_xx, 1, XX_THREADS, (size_t)0, tr->stream, d, local);
+        *launches += 1;
+        const int parity = (int)((tr->ticks + (unsigned long long)local) & 1);
+        uint32_t* base = tr->d_mail + MAIL_HDR + (size_t)parity * d.G * d.P * 2;  // packets are P 64-bit words
+        const int rc = g_nccl.AllGather(base + (size_t)d.rank * d.P * 2, base, (size_t)d.P * 2, NCCL_UINT32, tr->comm, tr->stream);
+        if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+      }
+    }
+  } else if (phase == 1) {
+    // One rank, or peer mailboxes: the first CTAs of the tagging kernel compute xx beside the tagging
+    // (and, with mailboxes, push winners first and xx last); otherwise xx is complete already.
+    const bool fused = single || (tr->comm_mode == 2 && !emulate && !split_exchange);
+    const size_t table_smem = tag_table_bytes(tr->tag_un);
+    const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
+    launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx,
+               xx_ctas, push_ctas);
+    *launches += 1;
+  } else if (phase == 2) {
+    launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
+    *launches += 1;
+  } else {
+    launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
+    FV_CUDA(cudaGetLastError());
+    *launches += 1;
+    tr->steps_since_fold += 1;
+  }
   return FV_OK;
 }
 
@@ -1839,96 +1871,123 @@ int ensure_log(fv_trainer* tr, size_t nsteps) {
   return FV_OK;
 }
 
-// The step loop.  idx_host == nullptr: ids are built on the GPU from the corpus
-// and the current order.  Otherwise they are uploaded in chunks of STAGE_STEPS
-// steps on a second stream, two chunks in flight.
-// idx_local: idx_host holds only this rank's windows (nsteps * batch of them); the ranks' blocks of a
-// chunk are then all-gathered over NVLink on the second stream, so every rank uploads 1/world of the ids.
-int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long long nsteps, float eps,
-                   const int32_t* idx_host, bool idx_local, float* nc_out, float* scale_out, fv_run_stats* stats) {
+// The step loop of one rank, cut into pieces so that several ranks driven by one host thread can be
+// advanced phase by phase (see run_group_lockstep).  idx_host == nullptr: ids are built on the GPU from
+// the corpus and the current order.  Otherwise they are uploaded in chunks of STAGE_STEPS steps on a
+// second stream, two chunks in flight.  idx_local: idx_host holds only this rank's windows
+// (nsteps * batch of them); the ranks' blocks of a chunk are then all-gathered over NVLink on the
+// second stream, so every rank uploads 1/world of the ids.
+struct StepLoop {
+  unsigned long long first_step = 0, nsteps = 0, timed_from = 0;
+  float eps = 0.f;
+  const int32_t* idx_host = nullptr;
+  bool idx_local = false, gather_ids = false;
+  size_t step_ids = 0, own_ids = 0;
+  unsigned long long chunk_id = 0, fold_every = FOLD_EVERY;
+  int chunk_rstride = 0;
+  const int32_t* idx = nullptr;  // ids of the step being enqueued
+  uint64_t launches = 0;
+};
+
+int loop_begin(fv_trainer* tr, StepLoop& L) {
   FV_REQUIRE(tr->have_weights, FV_ERR_STATE, "trainer has no weights: call fv_trainer_set_weights first");
-  if (!idx_host) FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus: call fv_trainer_set_corpus first");
+  if (!L.idx_host) FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus: call fv_trainer_set_corpus first");
   if (tr->d.G > 1 && !(tr->d.flags & FV_FLAG_EMULATE_RANKS))
-    FV_REQUIRE(tr->comm_mode != 0, FV_ERR_STATE, "world > 1 but fv_trainer_init_comm was not called");
-  if (stats) memset(stats, 0, sizeof(*stats));
-  if (nsteps == 0) return FV_OK;
-  FV_REQUIRE(nsteps <= (1ull << 30), FV_ERR_INVALID, "too many steps in one call");
-  fv::DeviceGuard guard(tr->device);
-  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
-  FV_TRY(ensure_log(tr, nsteps));
+    FV_REQUIRE(tr->comm_mode != 0, FV_ERR_STATE, "world > 1 but neither fv_trainer_init_comm nor fv_trainers_link was called");
+  FV_REQUIRE(L.nsteps >= 1 && L.nsteps <= (1ull << 30), FV_ERR_INVALID, "number of steps must be in [1, 2^30]");
+  FV_REQUIRE(L.timed_from < L.nsteps, FV_ERR_INVALID, "timed_from must be smaller than the number of steps");
+  FV_TRY(ensure_log(tr, L.nsteps));
   const Dev& d = tr->d;
-  const unsigned long long fold_every = (d.flags & FV_FLAG_FOLD_EVERY_STEP) ? 1 : FOLD_EVERY;
-  const size_t step_ids = (size_t)d.G * d.B * d.W;
-
+  L.fold_every = (d.flags & FV_FLAG_FOLD_EVERY_STEP) ? 1 : FOLD_EVERY;
+  L.step_ids = (size_t)d.G * d.B * d.W;
+  L.own_ids = (size_t)d.B * d.W;
   for (int b = 0; b < 2; ++b)
-    if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], step_ids * STAGE_STEPS));
-  const bool gather_ids = idx_host && idx_local && d.G > 1 && !(d.flags & FV_FLAG_EMULATE_RANKS);
-  if (idx_host && idx_local && d.G > 1 && !gather_ids)
+    if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], L.step_ids * STAGE_STEPS));
+  L.gather_ids = L.idx_host && L.idx_local && d.G > 1 && !(d.flags & FV_FLAG_EMULATE_RANKS);
+  if (L.idx_host && L.idx_local && d.G > 1 && !L.gather_ids)
     return fv::fail(FV_ERR_INVALID, "rank-local ids need real ranks: with FV_FLAG_EMULATE_RANKS pass all ranks' ids");
-  const size_t own_ids = (size_t)d.B * d.W;
-  for (int b = 0; b < 2 && gather_ids; ++b)
-    if (!tr->d_idx_local[b]) FV_TRY(dev_alloc(&tr->d_idx_local[b], own_ids * STAGE_STEPS));
-  tr->d.idx_rstride = (int)own_ids;
+  if (L.gather_ids) FV_REQUIRE(tr->comm != nullptr, FV_ERR_STATE, "rank-local ids travel through the NCCL communicator: call fv_trainer_init_comm");
+  for (int b = 0; b < 2 && L.gather_ids; ++b)
+    if (!tr->d_idx_local[b]) FV_TRY(dev_alloc(&tr->d_idx_local[b], L.own_ids * STAGE_STEPS));
+  tr->d.idx_rstride = (int)L.own_ids;
+  L.chunk_rstride = (int)L.own_ids;
+  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, L.first_step, L.eps, tr->delta_now);
+  L.launches = 1;
+  return FV_OK;
+}
 
-  k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, first_step, eps, tr->delta_now);
-  uint64_t launches = 1;
-  FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
-  unsigned long long chunk_id = 0;
-  int chunk_rstride = (int)own_ids;
-  for (unsigned long long k = 0; k < nsteps; ++k) {
-    // Input ids arrive in chunks of STAGE_STEPS steps through two device buffers filled on a second
-    // stream, one chunk ahead of the step loop: uploaded from the caller's host memory, or derived
-    // from the resident corpus and window order.
-    const int b = (int)(chunk_id & 1);
-    if (k % STAGE_STEPS == 0) {
-      const unsigned long long n = (nsteps - k < STAGE_STEPS) ? nsteps - k : STAGE_STEPS;
-      // the buffer must no longer be read by the chunk that used it two chunks ago
-      if (chunk_id >= 2) FV_CUDA(cudaStreamWaitEvent(tr->copy_stream, tr->ev_used[b], 0));
-      if (gather_ids) {
-        // this rank's ids of the chunk go up, then one all-gather lays the ranks' blocks side by side:
-        // [rank][step of the chunk][B*w], i.e. the blocks of one step lie n * B*w apart
-        FV_CUDA(cudaMemcpyAsync(tr->d_idx_local[b], idx_host + k * own_ids, n * own_ids * sizeof(int32_t),
-                                cudaMemcpyHostToDevice, tr->copy_stream));
-        // comm mode 1 already uses the communicator on the step stream: keep NCCL calls in one order there
-        cudaStream_t gs = (tr->comm_mode == 1) ? tr->stream : tr->copy_stream;
-        if (gs != tr->copy_stream) {
-          FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
-          FV_CUDA(cudaStreamWaitEvent(gs, tr->ev_copy[b], 0));
-        }
-        const int rc = g_nccl.AllGather(tr->d_idx_local[b], tr->d_idx_stage[b], n * own_ids, NCCL_UINT32, tr->comm, gs);
-        if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather (ids) failed: %s", g_nccl.GetErrorString(rc));
-        chunk_rstride = (int)(n * own_ids);
-      } else if (idx_host) {
-        chunk_rstride = (int)own_ids;
-        FV_CUDA(cudaMemcpyAsync(tr->d_idx_stage[b], idx_host + k * step_ids, n * step_ids * sizeof(int32_t),
-                                cudaMemcpyHostToDevice, tr->copy_stream));
-      } else {
-        k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->copy_stream>>>(d, first_step + k, (int)n, tr->d_idx_stage[b]);
-        launches += 1;
-      }
-      FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
-      FV_CUDA(cudaStreamWaitEvent(tr->stream, tr->ev_copy[b], 0));
-      if (idx_host) {
-        k_check_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, tr->d_idx_stage[b], n * step_ids);
-        launches += 1;
-      }
+// Before step k: the timing mark, and at the start of a chunk the ids of its steps.
+int loop_stage(fv_trainer* tr, StepLoop& L, unsigned long long k) {
+  const Dev& d = tr->d;
+  if (k == L.timed_from) {
+    // the timed region starts here: steps before it are warm-up inside the same call
+    if (k > 0) {
+      k_reset_phase_clock<<<1, 1, 0, tr->stream>>>(tr->d_ctl);
+      L.launches += 1;
     }
-    tr->d.idx_rstride = chunk_rstride;
-    const int32_t* idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * (gather_ids ? own_ids : step_ids);
-    FV_TRY(enqueue_step(tr, (int)k, idx, &launches));
-    if ((k + 1) % STAGE_STEPS == 0 || k + 1 == nsteps) {
-      FV_CUDA(cudaEventRecord(tr->ev_used[chunk_id & 1], tr->stream));
-      ++chunk_id;
+    FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
+  }
+  // Input ids arrive in chunks of STAGE_STEPS steps through two device buffers filled on a second
+  // stream, one chunk ahead of the step loop: uploaded from the caller's host memory, or derived
+  // from the resident corpus and window order.
+  const int b = (int)(L.chunk_id & 1);
+  if (k % STAGE_STEPS == 0) {
+    const unsigned long long n = (L.nsteps - k < STAGE_STEPS) ? L.nsteps - k : STAGE_STEPS;
+    // the buffer must no longer be read by the chunk that used it two chunks ago
+    if (L.chunk_id >= 2) FV_CUDA(cudaStreamWaitEvent(tr->copy_stream, tr->ev_used[b], 0));
+    if (L.gather_ids) {
+      // this rank's ids of the chunk go up, then one all-gather lays the ranks' blocks side by side:
+      // [rank][step of the chunk][B*w], i.e. the blocks of one step lie n * B*w apart
+      FV_CUDA(cudaMemcpyAsync(tr->d_idx_local[b], L.idx_host + k * L.own_ids, n * L.own_ids * sizeof(int32_t),
+                              cudaMemcpyHostToDevice, tr->copy_stream));
+      // comm mode 1 already uses the communicator on the step stream: keep NCCL calls in one order there
+      cudaStream_t gs = (tr->comm_mode == 1) ? tr->stream : tr->copy_stream;
+      if (gs != tr->copy_stream) {
+        FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
+        FV_CUDA(cudaStreamWaitEvent(gs, tr->ev_copy[b], 0));
+      }
+      const int rc = g_nccl.AllGather(tr->d_idx_local[b], tr->d_idx_stage[b], n * L.own_ids, NCCL_UINT32, tr->comm, gs);
+      if (rc != 0) return fv::fail(FV_ERR_COMM, "ncclAllGather (ids) failed: %s", g_nccl.GetErrorString(rc));
+      L.chunk_rstride = (int)(n * L.own_ids);
+    } else if (L.idx_host) {
+      L.chunk_rstride = (int)L.own_ids;
+      FV_CUDA(cudaMemcpyAsync(tr->d_idx_stage[b], L.idx_host + k * L.step_ids, n * L.step_ids * sizeof(int32_t),
+                              cudaMemcpyHostToDevice, tr->copy_stream));
+    } else {
+      k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->copy_stream>>>(d, L.first_step + k, (int)n, tr->d_idx_stage[b]);
+      L.launches += 1;
     }
-    if (tr->steps_since_fold >= fold_every) {
-      FV_TRY(fold_weights(tr, (int)(k + 1)));
-      launches += 2;
+    FV_CUDA(cudaEventRecord(tr->ev_copy[b], tr->copy_stream));
+    FV_CUDA(cudaStreamWaitEvent(tr->stream, tr->ev_copy[b], 0));
+    if (L.idx_host) {
+      k_check_idx<<<tr->entry_grid, 256, 0, tr->stream>>>(d, tr->d_idx_stage[b], n * L.step_ids);
+      L.launches += 1;
     }
   }
-  tr->d.idx_rstride = (int)own_ids;
+  tr->d.idx_rstride = L.chunk_rstride;
+  L.idx = tr->d_idx_stage[b] + (k % STAGE_STEPS) * (L.gather_ids ? L.own_ids : L.step_ids);
+  return FV_OK;
+}
+
+int loop_after_step(fv_trainer* tr, StepLoop& L, unsigned long long k) {
+  if ((k + 1) % STAGE_STEPS == 0 || k + 1 == L.nsteps) {
+    FV_CUDA(cudaEventRecord(tr->ev_used[L.chunk_id & 1], tr->stream));
+    ++L.chunk_id;
+  }
+  if (tr->steps_since_fold >= L.fold_every) {
+    FV_TRY(fold_weights(tr, (int)(k + 1)));
+    L.launches += 2;
+  }
+  return FV_OK;
+}
+
+int loop_end(fv_trainer* tr, StepLoop& L, float* nc_out, float* scale_out, fv_run_stats* stats) {
+  const Dev& d = tr->d;
+  const unsigned long long nsteps = L.nsteps;
+  tr->d.idx_rstride = (int)L.own_ids;
   k_advance<<<1, 1, 0, tr->stream>>>(tr->d_ctl, nsteps);
   tr->ticks += nsteps;
-  launches += 1;
+  L.launches += 1;
   FV_CUDA(cudaEventRecord(tr->ev_end, tr->stream));
   std::vector<float> log(2 * nsteps);
   FV_CUDA(cudaMemcpyAsync(log.data(), tr->d.nc_log, nsteps * sizeof(float), cudaMemcpyDeviceToHost, tr->stream));
@@ -1941,37 +2000,40 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
   StepCtl h;
   FV_CUDA(cudaMemcpy(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost));
   const uint32_t dev_err = h.error;
+  const unsigned long long timed = nsteps - L.timed_from;
   if (getenv("FV_STAMPS")) {
     fprintf(stderr, "[rank %d] per step (us): other %.1f forward %.1f xx %.1f wait %.1f tag %.1f scan %.1f apply %.1f fold %.1f\n", tr->d.rank,
-            h.phase_ns[PH_OTHER] * 1e-3 / nsteps, h.phase_ns[PH_FORWARD] * 1e-3 / nsteps, h.phase_ns[PH_XX] * 1e-3 / nsteps,
-            h.phase_ns[PH_WAIT] * 1e-3 / nsteps, h.phase_ns[PH_TAG] * 1e-3 / nsteps, h.phase_ns[PH_SCAN] * 1e-3 / nsteps,
-            h.phase_ns[PH_APPLY] * 1e-3 / nsteps, h.phase_ns[PH_FOLD] * 1e-3 / nsteps);
+            h.phase_ns[PH_OTHER] * 1e-3 / timed, h.phase_ns[PH_FORWARD] * 1e-3 / timed, h.phase_ns[PH_XX] * 1e-3 / timed,
+            h.phase_ns[PH_WAIT] * 1e-3 / timed, h.phase_ns[PH_TAG] * 1e-3 / timed, h.phase_ns[PH_SCAN] * 1e-3 / timed,
+            h.phase_ns[PH_APPLY] * 1e-3 / timed, h.phase_ns[PH_FOLD] * 1e-3 / timed);
   }
   if (stats) {
+    memset(stats, 0, sizeof(*stats));
     float ms = 0.f;
     FV_CUDA(cudaEventElapsedTime(&ms, tr->ev_begin, tr->ev_end));
     stats->steps = nsteps;
     unsigned long long mine = 0;
-    for (unsigned long long k = 0; k < nsteps; ++k) {
-      if (idx_host) {
+    for (unsigned long long k = L.timed_from; k < nsteps; ++k) {
+      if (L.idx_host) {
         mine += d.B;
       } else {
         uint64_t first, cnt;
-        fv_shard_range(d.Ns, d.B, d.G, d.rank, first_step + k, &first, &cnt);
+        fv_shard_range(d.Ns, d.B, d.G, d.rank, L.first_step + k, &first, &cnt);
         mine += cnt;
       }
     }
     stats->windows = mine;
     stats->seconds = ms * 1e-3;
-    // from the device-side phase clock (whole run, no sampling): forward; xx + waiting for the peers;
+    // from the device-side phase clock (the timed steps, no sampling): forward; xx + waiting for the peers;
     // tag + scan + apply.  Folding and the gaps between steps make up the rest of `seconds`.
     stats->fwd_seconds = h.phase_ns[PH_FORWARD] * 1e-9;
     stats->exch_seconds = (h.phase_ns[PH_XX] + h.phase_ns[PH_WAIT]) * 1e-9;
     stats->upd_seconds = (h.phase_ns[PH_TAG] + h.phase_ns[PH_SCAN] + h.phase_ns[PH_APPLY]) * 1e-9;
-    stats->kernel_launches = launches;
+    stats->kernel_launches = L.launches;
     stats->last_nc = log[nsteps - 1];
     stats->last_scale = log[2 * nsteps - 1];
     stats->device_error = dev_err;
+    stats->timed_steps = (uint32_t)timed;
   }
   if (dev_err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "a token id was outside [0, V) (device check)");
   if (dev_err & FV_DEVERR_WINDOW_RANGE)
@@ -1980,12 +2042,37 @@ int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long 
     return fv::fail(FV_ERR_TIMEOUT, "a peer rank did not deliver its step packet in time; the replicas are out of step");
   if (dev_err & FV_DEVERR_NAN_WEIGHT)
     return fv::fail(FV_ERR_DATA, "a weight was NaN or a unit's scale collapsed to zero (device check)");
+  if (dev_err & FV_DEVERR_SLOT_RANGE)
+    return fv::fail(FV_ERR_DATA, "a scatter record or a peer's update entry was out of range (device check)");
   return FV_OK;
+}
+
+int run_steps_impl(fv_trainer* tr, unsigned long long first_step, unsigned long long nsteps, float eps,
+                   const int32_t* idx_host, bool idx_local, float* nc_out, float* scale_out, fv_run_stats* stats,
+                   unsigned long long timed_from = 0) {
+  if (stats) memset(stats, 0, sizeof(*stats));
+  if (nsteps == 0) return FV_OK;
+  fv::DeviceGuard guard(tr->device);
+  FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
+  StepLoop L;
+  L.first_step = first_step;
+  L.nsteps = nsteps;
+  L.eps = eps;
+  L.idx_host = idx_host;
+  L.idx_local = idx_local;
+  L.timed_from = timed_from;
+  FV_TRY(loop_begin(tr, L));
+  for (unsigned long long k = 0; k < nsteps; ++k) {
+    FV_TRY(loop_stage(tr, L, k));
+    for (int ph = 0; ph < STEP_PHASES; ++ph) FV_TRY(enqueue_phase(tr, ph, (int)k, L.idx, &L.launches));
+    FV_TRY(loop_after_step(tr, L, k));
+  }
+  return loop_end(tr, L, nc_out, scale_out, stats);
 }
 
 void free_all(fv_trainer* tr) {
   cudaSetDevice(tr->device);
-  for (int r = 0; r < 16; ++r)
+  for (int r = 0; r < 16 && !tr->linked; ++r)
     if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
@@ -1996,9 +2083,18 @@ void free_all(fv_trainer* tr) {
   cudaEvent_t evs[] = {tr->ev_begin, tr->ev_end, tr->ev_copy[0], tr->ev_copy[1], tr->ev_used[0], tr->ev_used[1]};
   for (cudaEvent_t e : evs)
     if (e) cudaEventDestroy(e);
-  if (tr->stream) cudaStreamDestroy(tr->stream);
+  if (tr->stream && tr->own_stream) cudaStreamDestroy(tr->stream);
   if (tr->copy_stream) cudaStreamDestroy(tr->copy_stream);
   delete tr;
+}
+
+// Sharded or replicated update once the ranks can write into one another's mailboxes (the
+// environment variable FV_SHARD = 0 / 1 overrides; the anti-Hebbian term needs the replicated one).
+int default_shard(const fv_trainer* tr) {
+  if (tr->d.has_delta || tr->d.G < 2) return 0;
+  const char* e = getenv("FV_SHARD");
+  if (e) return atoi(e) != 0;
+  return 1;
 }
 
 // Which tagging kernel runs and on how many CTAs.  force_un = 0: by the size of a step.
@@ -2064,8 +2160,9 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_TRY(dev_alloc(&tr->d_wt, ((size_t)d.N + 1) * d.Kp));  // one extra all-zero row for padding positions
   FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
-  d.outbox_off = (MAIL_HDR + 2 * 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
-  tr->mail_words = d.outbox_off + (d.G > 1 ? 2 * 2 * (size_t)d.G * d.B * d.W * (1 + d.has_delta) : 0);
+  d.inbox_off = (MAIL_HDR + 2 * 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
+  d.inbox_cap = (d.G > 1 && !d.has_delta) ? (size_t)d.G * d.B * d.W : 0;  // a sender's list can hold every slot of a step
+  tr->mail_words = d.inbox_off + 2 * (size_t)d.G * d.inbox_cap;
   FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
   FV_TRY(dev_alloc(&tr->d_cnt, E));
   if (cfg->delta != 0.0f) {
@@ -2449,6 +2546,14 @@ int fv_trainer_run_steps(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, f
   return run_steps_impl(tr, first_step, nsteps, eps, nullptr, false, nc_out, scale_out, stats);
 }
 
+int fv_trainer_run_steps_timed(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, uint64_t warmup, float eps,
+                               fv_run_stats* stats) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_run_steps_timed: NULL trainer");
+  FV_REQUIRE(warmup < nsteps, FV_ERR_INVALID, "warmup (%llu) must be smaller than nsteps (%llu)", (unsigned long long)warmup,
+             (unsigned long long)nsteps);
+  return run_steps_impl(tr, first_step, nsteps, eps, nullptr, false, nullptr, nullptr, stats, warmup);
+}
+
 int fv_trainer_run_steps_host(fv_trainer* tr, const int32_t* idx_host, uint64_t nsteps, float eps, float* nc_out,
                               float* scale_out, fv_run_stats* stats) {
   FV_REQUIRE(tr && idx_host, FV_ERR_INVALID, "fv_trainer_run_steps_host: NULL argument");
@@ -2461,25 +2566,18 @@ int fv_trainer_run_steps_host_local(fv_trainer* tr, const int32_t* idx_host, uin
   return run_steps_impl(tr, 0, nsteps, eps, idx_host, true, nc_out, scale_out, stats);
 }
 
-int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_stats* stats) {
-  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_run_epoch: NULL trainer");
-  FV_REQUIRE(nep >= 1, FV_ERR_INVALID, "nep must be >= 1");
-  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+// Learning rate of an epoch (returned) and its anti-Hebbian strength (stored in the trainer), cuda_funcs.cu:1229-1230.
+static float epoch_schedule(fv_trainer* tr, uint64_t epoch, uint64_t nep) {
   // eps = lr0 * (1 - epoch/Nep): float quotient, double product, float store
   const float q = (float)epoch / (float)nep;
   const float eps = (float)((double)tr->cfg.lr0 * (1.0 - (double)q));
-  // delta * 0.5 * (1 + tanh((epoch - Nep/8) / 10)), cuda_funcs.cu:1230
+  // delta * 0.5 * (1 + tanh((epoch - Nep/8) / 10))
   tr->delta_now = (float)((double)tr->cfg.delta * 0.5 * (1.0 + tanh(((double)(float)epoch - 0.125 * (double)nep) / 10.0)));
-  const unsigned long long per_step = (unsigned long long)tr->d.G * tr->d.B;
-  const unsigned long long nsteps = (tr->d.Ns + per_step - 1) / per_step;
-  return run_steps_impl(tr, 0, nsteps, eps, nullptr, false, nullptr, nullptr, stats);
+  return eps;
 }
 
-int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* winners, float* xx, float* nc,
-                          float* scale) {
-  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_step_debug: NULL trainer");
-  float nc1 = 0.f, s1 = 0.f;
-  FV_TRY(run_steps_impl(tr, step, 1, eps, nullptr, false, &nc1, &s1, nullptr));
+// Winners [world*batch] and xx [world][K] of the last step, from this rank's copy of all ranks' packets.
+static int read_packets(fv_trainer* tr, int32_t* winners, float* xx) {
   fv::DeviceGuard guard(tr->device);
   const Dev& d = tr->d;
   // the step just run had parity (ticks - 1) & 1
@@ -2496,6 +2594,25 @@ int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* win
         memcpy(xx + (size_t)r * d.K + mu, &bits, sizeof(float));
       }
   }
+  return FV_OK;
+}
+
+int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_stats* stats) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_run_epoch: NULL trainer");
+  FV_REQUIRE(nep >= 1, FV_ERR_INVALID, "nep must be >= 1");
+  FV_REQUIRE(tr->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  const float eps = epoch_schedule(tr, epoch, nep);
+  const unsigned long long per_step = (unsigned long long)tr->d.G * tr->d.B;
+  const unsigned long long nsteps = (tr->d.Ns + per_step - 1) / per_step;
+  return run_steps_impl(tr, 0, nsteps, eps, nullptr, false, nullptr, nullptr, stats);
+}
+
+int fv_trainer_step_debug(fv_trainer* tr, uint64_t step, float eps, int32_t* winners, float* xx, float* nc,
+                          float* scale) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_step_debug: NULL trainer");
+  float nc1 = 0.f, s1 = 0.f;
+  FV_TRY(run_steps_impl(tr, step, 1, eps, nullptr, false, &nc1, &s1, nullptr));
+  FV_TRY(read_packets(tr, winners, xx));
   if (nc) *nc = nc1;
   if (scale) *scale = s1;
   return FV_OK;
@@ -2633,8 +2750,8 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]) {
     FV_TRY(dev_alloc(&tr->d_peer_table, (size_t)MAX_RANKS));
     FV_CUDA(cudaMemcpy(tr->d_peer_table, tr->peer_mail, sizeof(uint32_t*) * MAX_RANKS, cudaMemcpyHostToDevice));
     tr->d.peers = tr->d_peer_table;
-    tr->d.shard = getenv("FV_SHARD") ? 1 : 0;  // sharded update: opt-in (see the mode table in the header)
     tr->comm_mode = 2;
+    tr->d.shard = default_shard(tr);
   } else {
     for (int r = 0; r < G; ++r) {
       if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
@@ -2656,7 +2773,160 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
     choose_tag_variant(tr, (int)value);
     return FV_OK;
   }
+  if (strcmp(key, "shard") == 0) {
+    FV_REQUIRE(value == 0.0 || value == 1.0, FV_ERR_INVALID, "shard must be 0 or 1, got %g", value);
+    FV_REQUIRE(value == 0.0 || (tr->comm_mode == 2 && !tr->d.has_delta), FV_ERR_STATE,
+               "the sharded update needs peer mailboxes (fv_trainer_init_comm or fv_trainers_link first) and delta == 0");
+    tr->d.shard = (int)value;
+    return FV_OK;
+  }
+  if (strcmp(key, "loopback_peers") == 0) {
+    // Test aid: every peer's mailbox is this rank's own, so nothing a peer would send ever arrives and
+    // the first wait for a peer's word runs into spin_limit.
+    FV_REQUIRE(value == 1.0 && tr->d.G > 1 && tr->comm_mode == 0, FV_ERR_STATE, "loopback_peers: needs world > 1 and no communicator yet");
+    fv::DeviceGuard guard(tr->device);
+    for (int r = 0; r < tr->d.G; ++r) tr->peer_mail[r] = tr->d_mail;
+    FV_TRY(dev_alloc(&tr->d_peer_table, (size_t)MAX_RANKS));
+    FV_CUDA(cudaMemcpy(tr->d_peer_table, tr->peer_mail, sizeof(uint32_t*) * MAX_RANKS, cudaMemcpyHostToDevice));
+    tr->d.peers = tr->d_peer_table;
+    tr->linked = true;
+    tr->comm_mode = 2;
+    return FV_OK;
+  }
   return fv::fail(FV_ERR_INVALID, "fv_trainer_set_option: unknown option %s", key);
+}
+
+// ---------------------------------------------------------------------------
+// Several ranks driven by one process
+// ---------------------------------------------------------------------------
+int fv_trainers_link(fv_trainer* const* trs, int32_t n) {
+  FV_REQUIRE(trs && n >= 1 && n <= MAX_RANKS, FV_ERR_INVALID, "fv_trainers_link: need 1..%d trainers", MAX_RANKS);
+  bool same_device = true, distinct = true;
+  for (int r = 0; r < n; ++r) {
+    FV_REQUIRE(trs[r], FV_ERR_INVALID, "fv_trainers_link: trainer %d is NULL", r);
+    const fv_config &a = trs[r]->cfg, &b = trs[0]->cfg;
+    FV_REQUIRE(a.world == n && a.rank == r, FV_ERR_INVALID, "fv_trainers_link: trainer %d has rank %d of %d, expected rank %d of %d", r,
+               a.rank, a.world, r, n);
+    FV_REQUIRE(a.hid == b.hid && a.vocab == b.vocab && a.window == b.window && a.batch == b.batch && a.delta == b.delta &&
+                   a.flags == b.flags && a.prec == b.prec,
+               FV_ERR_INVALID, "fv_trainers_link: trainer %d is configured differently from trainer 0", r);
+    FV_REQUIRE(trs[r]->comm_mode == 0, FV_ERR_STATE, "fv_trainers_link: trainer %d already has a communicator", r);
+    FV_REQUIRE(!(a.flags & FV_FLAG_EMULATE_RANKS), FV_ERR_INVALID, "fv_trainers_link: FV_FLAG_EMULATE_RANKS computes all ranks in one trainer");
+    same_device &= trs[r]->device == trs[0]->device;
+    for (int q = 0; q < r; ++q) distinct &= trs[q]->device != trs[r]->device;
+  }
+  if (n == 1) return FV_OK;
+  FV_REQUIRE(same_device || distinct, FV_ERR_INVALID, "fv_trainers_link: the trainers must sit on %d different devices, or all on one", n);
+  if (distinct) {
+    for (int r = 0; r < n; ++r) {
+      fv::DeviceGuard guard(trs[r]->device);
+      FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", trs[r]->device);
+      for (int q = 0; q < n; ++q) {
+        if (q == r) continue;
+        int can = 0;
+        FV_CUDA(cudaDeviceCanAccessPeer(&can, trs[r]->device, trs[q]->device));
+        FV_REQUIRE(can, FV_ERR_COMM, "device %d cannot access the memory of device %d", trs[r]->device, trs[q]->device);
+        const cudaError_t e = cudaDeviceEnablePeerAccess(trs[q]->device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else FV_CUDA(e);
+      }
+    }
+  }
+  for (int r = 0; r < n; ++r) {
+    fv_trainer* tr = trs[r];
+    fv::DeviceGuard guard(tr->device);
+    for (int q = 0; q < n; ++q) tr->peer_mail[q] = trs[q]->d_mail;
+    FV_TRY(dev_alloc(&tr->d_peer_table, (size_t)MAX_RANKS));
+    FV_CUDA(cudaMemcpy(tr->d_peer_table, tr->peer_mail, sizeof(uint32_t*) * MAX_RANKS, cudaMemcpyHostToDevice));
+    tr->d.peers = tr->d_peer_table;
+    tr->linked = true;
+    tr->comm_mode = 2;
+    tr->d.shard = default_shard(tr);
+    if (same_device) {
+      tr->lockstep = true;
+      if (r > 0) {
+        FV_CUDA(cudaStreamSynchronize(tr->stream));
+        FV_CUDA(cudaStreamDestroy(tr->stream));
+        tr->stream = trs[0]->stream;
+        tr->own_stream = false;
+      }
+    }
+  }
+  return FV_OK;
+}
+
+static int run_group(fv_trainer* const* trs, int n, unsigned long long first_step, unsigned long long nsteps, float eps,
+                     unsigned long long timed_from, float* nc_out, float* scale_out, fv_run_stats* stats) {
+  FV_REQUIRE(trs && n >= 1, FV_ERR_INVALID, "NULL trainer list");
+  for (int r = 0; r < n; ++r)
+    FV_REQUIRE(trs[r] && trs[r]->d.G == n && trs[r]->d.rank == r && (n == 1 || trs[r]->linked), FV_ERR_STATE,
+               "the trainers must be ranks 0..%d of one linked group, in order", n - 1);
+  if (nsteps == 0) return FV_OK;
+  if (n == 1) return run_steps_impl(trs[0], first_step, nsteps, eps, nullptr, false, nc_out, scale_out, stats, timed_from);
+  if (trs[0]->lockstep) {
+    // one device, one stream: every phase of a step for rank 0, 1, ... before the next phase, so that
+    // whatever a kernel waits for has been written by a kernel that is already complete
+    fv::DeviceGuard guard(trs[0]->device);
+    FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", trs[0]->device);
+    std::vector<StepLoop> L(n);
+    for (int r = 0; r < n; ++r) {
+      L[r].first_step = first_step;
+      L[r].nsteps = nsteps;
+      L[r].eps = eps;
+      L[r].timed_from = timed_from;
+      FV_TRY(loop_begin(trs[r], L[r]));
+    }
+    for (unsigned long long k = 0; k < nsteps; ++k) {
+      for (int r = 0; r < n; ++r) FV_TRY(loop_stage(trs[r], L[r], k));
+      for (int ph = 0; ph < STEP_PHASES; ++ph)
+        for (int r = 0; r < n; ++r) FV_TRY(enqueue_phase(trs[r], ph, (int)k, L[r].idx, &L[r].launches));
+      for (int r = 0; r < n; ++r) FV_TRY(loop_after_step(trs[r], L[r], k));
+    }
+    int rc = FV_OK;
+    for (int r = 0; r < n; ++r) {
+      const int e = loop_end(trs[r], L[r], r == 0 ? nc_out : nullptr, r == 0 ? scale_out : nullptr, stats ? stats + r : nullptr);
+      if (e != FV_OK && rc == FV_OK) rc = e;
+    }
+    return rc;
+  }
+  // one device per rank: a host thread each, as the reference drives its GPUs (cuda_funcs.cu:1664-1665)
+  std::vector<int> rcs(n, FV_OK);
+  std::vector<std::string> msgs(n);
+#pragma omp parallel for num_threads(n) schedule(static, 1)
+  for (int r = 0; r < n; ++r) {
+    rcs[r] = run_steps_impl(trs[r], first_step, nsteps, eps, nullptr, false, r == 0 ? nc_out : nullptr, r == 0 ? scale_out : nullptr,
+                            stats ? stats + r : nullptr, timed_from);
+    if (rcs[r] != FV_OK) msgs[r] = fv_last_error();
+  }
+  for (int r = 0; r < n; ++r)
+    if (rcs[r] != FV_OK) return fv::fail(rcs[r], "rank %d: %s", r, msgs[r].c_str());
+  return FV_OK;
+}
+
+int fv_trainers_run_steps(fv_trainer* const* trs, int32_t n, uint64_t first_step, uint64_t nsteps, uint64_t warmup, float eps,
+                          float* nc_out, float* scale_out, fv_run_stats* stats) {
+  FV_REQUIRE(nsteps == 0 || warmup < nsteps, FV_ERR_INVALID, "warmup must be smaller than nsteps");
+  return run_group(trs, n, first_step, nsteps, eps, warmup, nc_out, scale_out, stats);
+}
+
+int fv_trainers_run_epoch(fv_trainer* const* trs, int32_t n, uint64_t epoch, uint64_t nep, fv_run_stats* stats) {
+  FV_REQUIRE(trs && n >= 1 && trs[0], FV_ERR_INVALID, "fv_trainers_run_epoch: NULL trainer list");
+  FV_REQUIRE(nep >= 1, FV_ERR_INVALID, "nep must be >= 1");
+  FV_REQUIRE(trs[0]->have_corpus, FV_ERR_STATE, "trainer has no corpus");
+  float eps = 0.f;
+  for (int r = 0; r < n; ++r) {
+    FV_REQUIRE(trs[r], FV_ERR_INVALID, "fv_trainers_run_epoch: trainer %d is NULL", r);
+    eps = epoch_schedule(trs[r], epoch, nep);
+  }
+  const unsigned long long per_step = (unsigned long long)trs[0]->d.G * trs[0]->d.B;
+  const unsigned long long nsteps = (trs[0]->d.Ns + per_step - 1) / per_step;
+  return run_group(trs, n, 0, nsteps, eps, 0, nullptr, nullptr, stats);
+}
+
+int fv_trainer_last_packets(fv_trainer* tr, int32_t* winners, float* xx) {
+  FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_last_packets: NULL trainer");
+  FV_REQUIRE(tr->ticks > 0, FV_ERR_STATE, "no step has run yet");
+  return read_packets(tr, winners, xx);
 }
 
 int fv_trainer_comm_mode(fv_trainer* tr, int* mode) {

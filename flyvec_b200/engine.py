@@ -142,6 +142,19 @@ class Trainer:
         check(_lib.lib().fv_trainer_step_debug(self._h, step, eps, ptr(win), ptr(xx), C.byref(nc), C.byref(sc)))
         return win.reshape(self.G, self.B), xx, np.float32(nc.value), np.float32(sc.value)
 
+    def run_steps_timed(self, first_step: int, nsteps: int, warmup: int, eps: float) -> dict:
+        """``nsteps`` steps in one call, the first ``warmup`` of them outside the timed region."""
+        st = FvRunStats()
+        check(_lib.lib().fv_trainer_run_steps_timed(self._h, first_step, nsteps, warmup, eps, C.byref(st)))
+        return st.as_dict()
+
+    def last_packets(self):
+        """Winners ``[world][batch]`` and xx ``[world][K]`` of the last step as this rank holds them."""
+        win = np.empty(self.G * self.B, np.int32)
+        xx = np.empty((self.G, self.K), np.float32)
+        check(_lib.lib().fv_trainer_last_packets(self._h, ptr(win), ptr(xx)))
+        return win.reshape(self.G, self.B), xx
+
     def time_forward(self, step: int, reps: int = 50) -> float:
         """Seconds per launch of the fused gather/arg-max kernel, back-to-back launches."""
         sec = C.c_double(0)
@@ -171,6 +184,79 @@ class Trainer:
         m = C.c_int(0)
         check(_lib.lib().fv_trainer_comm_mode(self._h, C.byref(m)))
         return m.value
+
+
+class TrainerGroup:
+    """All ranks of a data-parallel job in ONE process (the reference's arrangement,
+    flyvec/train_flyvec.py:141-229): ``devices[r]`` is rank ``r``'s GPU.  Distinct devices run
+    concurrently, one host thread each; the same device repeated runs the ranks phase by phase
+    on one GPU (for tests)."""
+
+    def __init__(self, devices, hid: int, vocab: int, window: int = 11, batch: int = 10000, lr0: float = 0.002,
+                 delta: float = 0.0, prec: float = 1e-30, flags: int = 0, maxlen: int = 0, shard: bool | None = None):
+        n = len(devices)
+        self.ranks = [Trainer(hid, vocab, window, batch, lr0, delta, prec, device=dev, rank=r, world=n, flags=flags,
+                              maxlen=maxlen) for r, dev in enumerate(devices)]
+        self.n = n
+        self._arr = (C.c_void_p * n)(*[t._h for t in self.ranks])
+        check(_lib.lib().fv_trainers_link(self._arr, n))
+        if shard is not None and n > 1:
+            for t in self.ranks:
+                t.set_option("shard", 1 if shard else 0)
+
+    def close(self):
+        for t in self.ranks:
+            t.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def set_corpus(self, encodings, offsets) -> int:
+        return [t.set_corpus(encodings, offsets) for t in self.ranks][0]
+
+    def set_weights(self, w):
+        for t in self.ranks:
+            t.set_weights(w)
+
+    def set_permutation(self, perm):
+        for t in self.ranks:
+            t.set_permutation(perm)
+
+    def shuffle(self, seed: int):
+        for t in self.ranks:
+            t.shuffle(seed)
+
+    @property
+    def steps_per_epoch(self) -> int:
+        return self.ranks[0].steps_per_epoch
+
+    def run_steps(self, first_step: int, nsteps: int, eps: float, warmup: int = 0, want_log: bool = False):
+        stats = (FvRunStats * self.n)()
+        nc = np.empty(nsteps, np.float32) if want_log else None
+        sc = np.empty(nsteps, np.float32) if want_log else None
+        check(_lib.lib().fv_trainers_run_steps(self._arr, self.n, first_step, nsteps, warmup, eps,
+                                               ptr(nc) if want_log else None, ptr(sc) if want_log else None, stats))
+        out = [s.as_dict() for s in stats]
+        if want_log:
+            out[0]["nc"], out[0]["scale"] = nc, sc
+        return out
+
+    def run_epoch(self, epoch: int, nep: int):
+        stats = (FvRunStats * self.n)()
+        check(_lib.lib().fv_trainers_run_epoch(self._arr, self.n, epoch, nep, stats))
+        return [s.as_dict() for s in stats]
+
+    def step_debug(self, step: int, eps: float):
+        """One step; winners ``[world][batch]`` and xx ``[world][K]`` as rank 0 received them, nc, scale."""
+        st = self.run_steps(step, 1, eps, want_log=True)
+        win, xx = self.ranks[0].last_packets()
+        return win, xx, st[0]["nc"][0], st[0]["scale"][0]
+
+    def get_weights(self, rank: int = 0) -> np.ndarray:
+        return self.ranks[rank].get_weights()
 
 
 def shard_range(num_windows: int, batch: int, world: int, rank: int, step: int):

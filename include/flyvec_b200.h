@@ -82,7 +82,8 @@ typedef struct fv_run_stats {
   float last_nc;           /* normaliser of the last step                      */
   float last_scale;        /* eps / max(prec, nc) of the last step             */
   uint32_t device_error;   /* non-zero: a bounds predicate fired on the device */
-  uint32_t reserved;
+  uint32_t timed_steps;    /* steps between the two timing events (`seconds`, `windows` and the three
+                              phase times cover these; all steps unless the call named a warm-up)     */
 } fv_run_stats;
 
 typedef struct fv_trainer fv_trainer;
@@ -151,6 +152,11 @@ int fv_trainer_run_epoch(fv_trainer* tr, uint64_t epoch, uint64_t nep, fv_run_st
  * NULL, receive nsteps values each (the per-step normaliser and step size). */
 int fv_trainer_run_steps(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, float eps, float* nc_out,
                          float* scale_out, fv_run_stats* stats);
+/* The same with the first `warmup` steps outside the timed region: the timing event is recorded on the
+ * stream between step warmup-1 and step warmup, so stats->seconds, ->windows and the phase times cover
+ * steps [warmup, nsteps) of a loop that is already in its steady state. */
+int fv_trainer_run_steps_timed(fv_trainer* tr, uint64_t first_step, uint64_t nsteps, uint64_t warmup, float eps,
+                               fv_run_stats* stats);
 /* Same loop fed from host memory: idx_host holds nsteps*world*batch windows of
  * `window` pre-built input ids (token, centre token + V, or -1), uploaded inside
  * the call; per-step normalisers are copied back.  This is the streaming form
@@ -185,8 +191,25 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *   "spin_limit"   polls a device-side wait for a peer's word makes before it gives up and the call
  *                  returns FV_ERR_TIMEOUT (default 8388608, about ten seconds);
  *   "tag_variant"  1: the scatter bookkeeping claims positions one slot per thread; 2: it first
- *                  deduplicates 1024 slots in shared memory; 0: chosen by the size of a step. */
+ *                  deduplicates 1024 slots in shared memory; 0: chosen by the size of a step;
+ *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
+ *   "loopback_peers" 1: test aid -- every peer's mailbox is mapped onto this rank's own, so a peer's
+ *                  words never arrive and the first wait for one runs into spin_limit. */
 int fv_trainer_set_option(fv_trainer* tr, const char* key, double value);
+/* Multi-GPU from ONE process, as the reference drives its GPUs (train_flyvec.py:141-146: one
+ * descriptor/arrays pair per device; cuda_funcs.cu:1664-1665: one OpenMP thread per GPU and step).
+ * trs[r] must be rank r of world n.  With one device per rank the ranks map one another's mailboxes
+ * through CUDA peer access and fv_trainers_run_* starts one host thread per GPU.  All ranks on ONE
+ * device (for tests on a single GPU) share a stream and are advanced phase by phase, rank after rank,
+ * so that a kernel never has to wait for one that has not run yet.  Every rank needs the corpus, the
+ * weights and the window order set as for a single trainer.  nc_out / scale_out / stats may be NULL;
+ * stats has n entries. */
+int fv_trainers_link(fv_trainer* const* trs, int32_t n);
+int fv_trainers_run_steps(fv_trainer* const* trs, int32_t n, uint64_t first_step, uint64_t nsteps, uint64_t warmup, float eps,
+                          float* nc_out, float* scale_out, fv_run_stats* stats);
+int fv_trainers_run_epoch(fv_trainer* const* trs, int32_t n, uint64_t epoch, uint64_t nep, fv_run_stats* stats);
+/* winners[world*batch] and xx[world][K] of the last step as THIS rank received them (parity checks). */
+int fv_trainer_last_packets(fv_trainer* tr, int32_t* winners, float* xx);
 /* How the ranks exchange their per-step packets (B winners and K floats of xx per rank):
  *   0  single rank / not initialised;
  *   1  one NCCL all-gather per step;
@@ -196,9 +219,11 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value);
  *      an old sequence number polls that word, every poll loop is bounded, and a peer that never
  *      delivers ends the call with FV_ERR_TIMEOUT.
  * Mode 2 is chosen when every rank can map every other rank's mailbox; the environment variable
- * FV_COMM=nccl forces mode 1.  With FV_SHARD=1 (mode 2 only) each rank updates the matrix rows
- * i % world == rank and pulls the other rows' new values from their owners; measured slower than the
- * replicated update on 2 to 8 B200s, so it is off by default. */
+ * FV_COMM=nccl forces mode 1.  In mode 2 the update is sharded unless delta != 0: rank r does the
+ * scatter bookkeeping and the abs-max scan for the matrix rows i % world == r only and stores the
+ * count of every touched position into its peers' inboxes, from which every replica applies the same
+ * update to its own copy ("shard" option / FV_SHARD=0 select the replicated update, in which every
+ * rank rebuilds every rank's scatter). */
 int fv_trainer_comm_mode(fv_trainer* tr, int* mode);
 /* Which windows of the current order rank `rank` owns in global step `step`
  * (cuda_funcs.cu:1667-1670); pure arithmetic, usable without a GPU. */
