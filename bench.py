@@ -31,10 +31,20 @@ sys.path.insert(0, str(ROOT))
 
 CFG = dict(K=400, V=20000, W=11, batch=10000, lr=2e-4, zipf_s=1.0, chunk_mean=25.0, tokens_per_gpu=50_000_000)
 CORPUS_SEED, WEIGHT_SEED, PERM_SEED = 101, 1, 201
-# DRAM bytes (read + write) of one k_forward launch at config-1 shapes inside the running step loop, from the
-# ncu capture summarised in profiles/train_step_config1.md (caches as the pipeline leaves them); with ncu's
-# cache flush before the launch the same kernel reads 27.4 MB.
-FWD_DRAM_TRAFFIC_BYTES = 2.0e6
+WORKLOAD = "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000/GPU lr=2e-4 W0~N(0,1)"
+
+
+def forward_dram_traffic():
+    """DRAM bytes (read + write) per launch of the forward kernel as the kept ncu capture of this
+    workload measured them: the line ``dram_bytes_per_launch = <number>`` of
+    profiles/k_forward_config1.md, or None when there is no such capture."""
+    import re
+
+    f = ROOT / "profiles" / "k_forward_config1.md"
+    if not f.exists():
+        return None
+    m = re.search(r"^dram_bytes_per_launch\s*=\s*([0-9.eE+]+)", f.read_text(), re.M)
+    return float(m.group(1)) if m else None
 
 
 # ----------------------------------------------------------------------------
@@ -88,6 +98,14 @@ class Dist:
         t = torch.tensor([x], dtype=torch.float64)
         self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
         return float(t[0])
+
+    def gather_obj(self, obj):
+        """``obj`` of every rank, in rank order, on every rank."""
+        if not self.dist:
+            return [obj]
+        box = [None] * self.world
+        self.dist.all_gather_object(box, obj)
+        return box
 
     def close(self):
         if self.dist:
@@ -216,21 +234,31 @@ def bench_train(args):
     eps = np.float32(CFG["lr"])  # one epoch: eps = lr0 * (1 - 0/1)
 
     # ---- device-resident loop ------------------------------------------------
-    tr.run_steps(0, warmup, eps)
+    # Warm-up and timed steps are ONE call: the library records its begin event on the stream between
+    # step `warmup`-1 and step `warmup`, so exactly `steps` steps of a loop that is already in its
+    # steady state (ids staged ahead, every rank in step with its peers) lie between the two events.
     sampler = ClockSampler(local)
-    dist.barrier()
     if rank == 0:
         sampler.start()
+    dist.barrier()
     t0 = time.perf_counter()
-    st = tr.run_steps(warmup, steps, eps)  # returns after the stream is idle
+    st = tr.run_steps_timed(0, warmup + steps, warmup, eps)  # returns after the stream is idle
     wall = time.perf_counter() - t0
     dist.barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    assert st["timed_steps"] == steps
     sec = dist.max(st["seconds"])
     wall = dist.max(wall)
     fwd_s = dist.max(st["fwd_seconds"])
     total_windows = steps * world * B
     value = total_windows / sec
+
+    # ---- the replicas must have stayed identical ------------------------------------
+    import zlib
+
+    Wnow = tr.get_weights()
+    digest = (zlib.crc32(Wnow.tobytes()), float(st["last_nc"]), float(st["last_scale"]))
+    digests = dist.gather_obj(digest)
+    replicas_identical = all(d == digests[0] for d in digests)
 
     # ---- end to end: ids streamed from pinned host memory, normalisers read back ----
     e2e_steps = min(steps, args.e2e_steps)
@@ -250,6 +278,7 @@ def bench_train(args):
     tr.run_steps_host_local(pinned, e2e_steps, eps, nc_out=nc_host)
     e2e_wall = dist.max(time.perf_counter() - t0)
     e2e_value = e2e_steps * world * B / e2e_wall
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- roofline of the dominant kernel ---------------------------------------
     # k_forward is timed live as 50 back-to-back launches between two CUDA events on the trainer's
@@ -260,15 +289,29 @@ def bench_train(args):
     fwd_avg = dist.max(tr.time_forward(warmup + steps, reps=50))
     achieved = fwd_bytes / fwd_avg / 1e9
     step_bytes = B * W * K * 4 + 3 * K * 2 * V * 4 + B * (8 + 4 * W) + B * 2 + K * 4  # the reference schedule's figure
+    # The synapse matrix (64 MB) lives in the L2, so the forward kernel's real ceiling is what the L2 gives
+    # for its access pattern.  Both are measured here, in this run, with the library's probe: random
+    # 1600-byte rows out of 64 MB (the gather), streaming over 64 MB (L2) and over 2 GiB (HBM).
+    probes = None
+    if rank == 0:
+        probes = {"l2_gather_1600B_rows_of_64MB_gbs": engine.probe_read_bandwidth("gather", 64 << 20, K * 4, 40, local),
+                  "l2_stream_64MB_gbs": engine.probe_read_bandwidth("stream", 64 << 20, 16, 40, local),
+                  "hbm_stream_2GiB_gbs": engine.probe_read_bandwidth("stream", 2 << 30, 16, 3, local)}
+
+    # ---- parity of what was timed: 32 steps of this very workload against the oracle (one rank) ----
+    parity = None
+    if world == 1 and not args.no_cpu_baseline:
+        parity = oracle_check(tr, enc, off, steps=32)
 
     out = {
         "metric": "train windows/sec (K=400,V=20k,w=11)", "value": value, "unit": "windows/s", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": sec / steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000/GPU lr=2e-4 W0~N(0,1)",
+        "config": {"workload": WORKLOAD,
                    "corpus_tokens": int(ntok), "windows": int(ns), "global_batch": world * B,
                    "parallelism": f"dp{world}",
                    "exchange": {0: "none", 1: "nccl all-gather per step", 2: "peer-memory mailboxes, flag-in-word packets"}[tr.comm_mode],
+                   "timed_region": "steps [warmup, warmup+steps) of one run call; begin event recorded on the stream after the warm-up steps",
                    "l2": "inputs larger than L2: corpus + window tables (>0.6 GB) stream through; the 64 MB synapse "
                          "matrix is re-read every step by design"},
         "wall_ms_per_step": wall / steps * 1e3,
@@ -278,22 +321,77 @@ def bench_train(args):
                 "what": "fv_trainer_run_steps_host_local: every rank uploads the input ids of its own windows from pinned host "
                         "memory inside the call (all-gathered over NVLink when there are several ranks), per-step "
                         "normaliser copied back"},
-        "gpu_launches": int(st["kernel_launches"]),
+        "gpu_launches": int(round(st["kernel_launches"] * steps / (steps + warmup))),
+        "replicas_identical": replicas_identical,
         "roofline": {"kernel": "k_forward (fused gather-sum + arg-max)", "bound": "hbm", "achieved": achieved,
-                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": FWD_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": forward_dram_traffic(), "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": fwd_bytes, "avg_launch_ms": fwd_avg * 1e3,
-                     "note": "rows are gathered from the L2-resident matrix, so achieved can exceed the HBM figure"},
+                     "measured_in_this_run": probes,
+                     "frac_of_l2_gather": (achieved / probes["l2_gather_1600B_rows_of_64MB_gbs"]) if probes else None,
+                     "note": "rows are gathered from the L2-resident matrix, so achieved can exceed the HBM figure; "
+                             "frac_of_l2_gather sets it against the same access pattern measured in this run"},
         "phases_ms_per_step": {"forward": fwd_s / steps * 1e3, "xx kernel + all-gather (NCCL mode only; mailbox waits fall into update)": dist.max(st["exch_seconds"]) / steps * 1e3,
                                "update": dist.max(st["upd_seconds"]) / steps * 1e3},
         "step_algorithmic_gbs": step_bytes / (sec / steps) / 1e9,
         "last_nc": st["last_nc"],
     }
+    if parity is not None:
+        out["parity_check"] = parity
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_train_baseline(enc, off, seconds_limit=args.cpu_seconds)
     tr.close()
+    if rank == 0 and world == 1 and not args.no_hash:
+        out["hash"] = hash_summary(args)
     dist.close()
     if rank == 0:
         print(json.dumps(out))
+
+
+def oracle_check(tr, enc, off, steps: int = 32):
+    """The timed workload's first `steps` steps once more, from fresh weights, against the C oracle."""
+    from flyvec_b200 import synth
+    from oracle import c_oracle
+    from oracle import flyvec_oracle as orc
+
+    K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
+    W0 = synth.make_weights(K, 2 * V, seed=WEIGHT_SEED)
+    eps = np.float32(CFG["lr"])
+    tr.set_weights(W0)
+    log = tr.run_steps(0, steps, eps, want_log=True)
+    Wgpu = tr.get_weights()
+    perm = tr.get_permutation()[:steps * B]
+    starts = tr.window_starts()
+    f = tr.inverse_frequency()
+    runner = c_oracle.StepRunner(K, 2 * V, V, W, B, 1)
+    Wref = W0.copy()
+    nc = np.zeros(steps, np.float32)
+    enc = np.asarray(enc)
+    for t in range(steps):
+        idx = orc.build_idx(enc, starts, perm[t * B:(t + 1) * B], W, V)
+        _, _, nc[t], _ = runner.step(Wref, idx[None], [B], f, eps)
+    err = np.abs(Wgpu.astype(np.float64) - Wref) / (np.abs(Wref) + 1e-2)
+    return {"steps": steps, "against": "oracle/oracle_train.c on the same seeded inputs",
+            "max_weight_err_rel_with_floor_1e-2": float(err.max()),
+            "max_normaliser_rel_err": float((np.abs(log["nc"] - nc) / nc).max())}
+
+
+def hash_summary(args):
+    """Hashing figures for the default line: token hashing on config-0 shapes and window hashing at the
+    config-4 hash lengths (a 4 M-window slice), each device-resident and end to end through host buffers."""
+    import copy
+
+    a = copy.copy(args)
+    a.steps, a.warmup, a.cpu_seconds = 3, 3, min(args.cpu_seconds, 4.0)
+    out = {}
+    a.items, a.hash_length = 1_000_000, 50
+    out["tokens_config0_hl50"] = hash_numbers(a, windows=False)
+    a.items = 4_000_000
+    state = {}
+    for hl in (4, 16, 50, 128, 200):
+        a.hash_length = hl
+        a.no_cpu_baseline = args.no_cpu_baseline or hl != 50
+        out[f"windows_config4_hl{hl}"] = hash_numbers(a, windows=True, state=state)
+    return out
 
 
 def bench_update_emulated(args):
@@ -320,35 +418,44 @@ def bench_update_emulated(args):
                       "config": {"workload": f"config 1 shapes, {G} x {B} windows per step"}}))
 
 
-def bench_hash(args, windows: bool):
-    """Device-resident and end-to-end throughput of the token / window hasher."""
-    from flyvec_b200 import engine, synth
+def hash_numbers(args, windows: bool, state: dict | None = None) -> dict:
+    """Device-resident and end-to-end throughput of the token / window hasher.  End to end = the host-buffer
+    entry point (fv_hash_tokens / fv_hash_windows) on page-locked ids and codes: upload, kernel and download
+    of the whole batch inside the timed call.  `state` carries the inputs from one hash length to the next."""
+    from flyvec_b200 import _lib, engine, synth
 
     K, V, W = CFG["K"], CFG["V"], CFG["W"]
     hl = args.hash_length
-    Wm = synth.make_weights(K, 2 * V, seed=WEIGHT_SEED)
-    h = engine.Hasher(Wm, normalize=True)
+    state = state if state is not None else {}
     peak, peak_src = measured_peaks()
     code_b = (K + 7) // 8
+    if "h" not in state:
+        state["h"] = engine.Hasher(synth.make_weights(K, 2 * V, seed=WEIGHT_SEED), normalize=True)
+        if windows:
+            n = args.items or 16_000_000
+            enc, off = synth.make_corpus(max(n // 2, 1_000_000), V, seed=104)
+            starts = engine.enumerate_windows(off, W)
+            sel = np.random.default_rng(204).integers(0, len(starts), n)
+            ids = _lib.pinned_empty((n, W), np.int32)
+            ids[...] = build_idx_host(enc, starts, sel, W, V)
+            state["inv_f"] = engine.inverse_frequency(enc, V)
+            state["h"].set_inverse_frequency(state["inv_f"])
+        else:
+            n = args.items or 1_000_000
+            ids = _lib.pinned_empty((n,), np.int32)
+            ids[...] = synth.make_hash_ids(n, V, seed=100)
+            state["inv_f"] = None
+        state["ids"], state["n"] = ids, n
+        state["codes"] = _lib.pinned_empty((n, code_b), np.uint8)
+        state["d_in"] = engine.DeviceBuffer(ids.nbytes)
+        state["d_in"].upload(ids)
+        state["d_out"] = engine.DeviceBuffer(n * code_b)
+    h, ids, n, inv_f, d_in, d_out = state["h"], state["ids"], state["n"], state["inv_f"], state["d_in"], state["d_out"]
     if windows:
-        n = args.items or 16_000_000
-        enc, off = synth.make_corpus(max(n // 2, 1_000_000), V, seed=104)
-        starts = engine.enumerate_windows(off, W)
-        rng = np.random.default_rng(204)
-        sel = rng.integers(0, len(starts), n)
-        ids = build_idx_host(enc, starts, sel, W, V)
-        inv_f = engine.inverse_frequency(enc, V)
-        h.set_inverse_frequency(inv_f)
         per_item = W * K * 4 + W * 4 + code_b
     else:
-        n = args.items or 1_000_000
-        ids = synth.make_hash_ids(n, V, seed=100)
-        inv_f = None
         # large batches go through the vocabulary table: an id in, a code gathered from the table and written out
         per_item = (4 + 2 * code_b) if n >= 4 * V else (K * 4 + code_b)
-    d_in = engine.DeviceBuffer(ids.nbytes)
-    d_in.upload(ids)
-    d_out = engine.DeviceBuffer(n * code_b)
     run = (lambda: h.hash_windows_device(d_in.ptr, n, W, True, hl, d_out.ptr)) if windows else \
           (lambda: h.hash_tokens_device(d_in.ptr, n, hl, d_out.ptr))
     for _ in range(max(args.warmup, 3)):
@@ -359,28 +466,38 @@ def bench_hash(args, windows: bool):
         times.append(run())
     t = float(np.mean(times))
     e2e = None
-    for _ in range(2):  # the first call pays for first-touch of the result array and the allocator's warm-up
+    for _ in range(3):  # the first call makes the staging buffers; best of the following
         t0 = time.perf_counter()
         if windows:
-            h.hash_windows(ids, inv_freq=None, hash_length=hl, packed=True)
+            h.hash_windows(ids, inv_freq=inv_f, hash_length=hl, packed=True, out=state["codes"])
         else:
-            h.hash_tokens(ids, hash_length=hl, packed=True)
-        e2e = time.perf_counter() - t0
+            h.hash_tokens(ids, hash_length=hl, packed=True, out=state["codes"])
+        dt = time.perf_counter() - t0
+        e2e = dt if e2e is None or _ > 0 and dt < e2e else e2e
+    assert np.array_equal(state["codes"], d_out.download((n, code_b), np.uint8)), "host-buffer and device-resident codes differ"
     cpu = None
     if not args.no_cpu_baseline:
-        cpu = cpu_hash_baseline(h.weights(), V, ids, hl, windows, h_f=inv_f,
+        cpu = cpu_hash_baseline(h.weights(), V, np.asarray(ids), hl, windows, h_f=inv_f,
                                 seconds_limit=args.cpu_seconds)
+    pcie_bytes = int(ids.nbytes) + n * code_b
     out = {"metric": "hashed windows/sec" if windows else "hashed tokens/sec", "value": n / t,
            "unit": "windows/s" if windows else "tokens/s", "n_gpus": 1, "steps": len(times), "warmup": max(args.warmup, 3),
            "ms_per_step": t * 1e3, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
            "config": {"workload": ("config 4: window hashing" if windows else "config 0 shapes: token hashing"),
                       "items": n, "hash_length": hl, "l2": "L2 flushed between timed launches"},
-           "e2e": {"value": n / e2e, "unit": "items/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": n * code_b},
+           "e2e": {"value": n / e2e, "unit": "items/s", "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": n * code_b,
+                   "host_link_gbs": pcie_bytes / e2e / 1e9,
+                   "what": "fv_hash_windows / fv_hash_tokens on page-locked host buffers: chunked upload, kernel and download "
+                           "overlapped on two streams"},
            "roofline": {"kernel": "k_hash", "bound": "hbm", "achieved": per_item * n / t / 1e9, "peak": peak,
                         "unit": "GB/s", "frac": per_item * n / t / 1e9 / peak, "traffic": None, "peak_source": peak_src}}
     if cpu:
         out["cpu_baseline"] = cpu
-    print(json.dumps(out))
+    return out
+
+
+def bench_hash(args, windows: bool):
+    print(json.dumps(hash_numbers(args, windows)))
 
 
 def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_limit: float = 15.0):
@@ -450,6 +567,11 @@ def bench_reference(args):
         return
     from flyvec_b200 import synth
 
+    from oracle import c_oracle
+
+    # a launcher may have pinned OpenMP to one thread for its workers (torch.distributed.run does):
+    # this arm is the CPU's turn and uses every core of the host, at any --gpus
+    c_oracle.set_num_threads(os.cpu_count() or 1)
     K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
     enc, off = synth.make_corpus(5_000_000, V, s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=W, seed=CORPUS_SEED)
     limit = args.cpu_seconds_reference
@@ -459,7 +581,7 @@ def bench_reference(args):
            "unit": "windows/s", "n_gpus": args.gpus, "steps": timed, "warmup": 1,
            "ms_per_step": base["seconds_per_step"] * 1e3, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": "train step, config 1 shapes: K=400 V=20000 w=11 batch=10000 lr=2e-4 W0~N(0,1)",
+           "config": {"workload": WORKLOAD,
                       "note": "the reference trainer is CUDA-only; this arm times the C/OpenMP restatement of its "
                               "step (oracle/oracle_train.c) on the host cores, a bounded number of full steps"},
            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -483,6 +605,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--cpu-seconds-reference", type=float, default=90.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-hash", action="store_true", help="leave the hashing figures out of the train line")
     args = ap.parse_args()
     if args.impl == "reference":
         return bench_reference(args)

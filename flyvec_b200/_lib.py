@@ -119,6 +119,7 @@ _PROTOTYPES = {
     "fv_copy_to_device": ([C.c_int, _P, _P, C.c_size_t], C.c_int),
     "fv_copy_to_host": ([C.c_int, _P, _P, C.c_size_t], C.c_int),
     "fv_flush_l2": ([C.c_int, C.c_size_t], C.c_int),
+    "fv_probe_read_bandwidth": ([C.c_int, C.c_int, C.c_size_t, C.c_uint32, C.c_uint32, C.POINTER(C.c_double)], C.c_int),
 }
 
 _lib = None

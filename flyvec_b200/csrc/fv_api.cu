@@ -213,3 +213,113 @@ extern "C" int fv_flush_l2(int device, size_t bytes) {
   FV_CUDA(cudaDeviceSynchronize());
   return FV_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Read-bandwidth probe: what this GPU delivers for the two access patterns of the train step, so that
+// a kernel's rate can be set beside a figure measured in the same run.
+//   pattern 0  streaming: every thread reads 128-bit words with a grid stride, four loads in flight
+//   pattern 1  row gather: a warp reads whole rows of `row_bytes` (a multiple of 16) at pseudo-random
+//              places of the buffer, four rows in flight -- the shape of the forward pass
+// The buffer of `footprint` bytes is read `reps` times after one untimed pass; a footprint below the
+// L2 size measures the L2, a much larger one the HBM.
+// ---------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) k_probe_stream(const uint4* __restrict__ p, size_t n, int reps, unsigned* sink) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nt = (size_t)gridDim.x * blockDim.x;
+  unsigned acc = 0;
+  for (int r = 0; r < reps; ++r) {
+    size_t i = tid;
+    for (; i + 3 * nt < n; i += 4 * nt) {
+      const uint4 a = __ldcg(p + i), b = __ldcg(p + i + nt), c = __ldcg(p + i + 2 * nt), d = __ldcg(p + i + 3 * nt);
+      acc ^= a.x ^ b.y ^ c.z ^ d.w;
+    }
+    for (; i < n; i += nt) acc ^= __ldcg(p + i).x;
+  }
+  if (acc == 0x12345678u) *sink = acc;  // keeps the loads alive
+}
+__global__ void __launch_bounds__(256) k_probe_gather(const uint4* __restrict__ p, unsigned nrows, int row_q, int rows_per_warp,
+                                                      unsigned seed, unsigned* sink) {
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  unsigned s = seed + (unsigned)warp * 2654435761u, acc = 0;
+  for (int k = 0; k < rows_per_warp; k += 4) {
+    const uint4* r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s = s * 1664525u + 1013904223u;
+      r[u] = p + (size_t)((s >> 8) % nrows) * row_q;
+    }
+    for (int q0 = 0; q0 < row_q; q0 += 128) {
+      uint4 v[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int q = q0 + lane + 32 * t;
+          v[u][t] = q < row_q ? __ldcg(r[u] + q) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) acc ^= v[u][t].x ^ v[u][t].w;
+    }
+  }
+  if (acc == 0x12345678u) *sink = acc;
+}
+}  // namespace
+
+extern "C" int fv_probe_read_bandwidth(int device, int pattern, size_t footprint, uint32_t row_bytes, uint32_t reps,
+                                       double* gbytes_per_s) {
+  FV_REQUIRE(gbytes_per_s != nullptr, FV_ERR_INVALID, "fv_probe_read_bandwidth: output pointer is NULL");
+  FV_REQUIRE(pattern == 0 || pattern == 1, FV_ERR_INVALID, "pattern must be 0 (streaming) or 1 (row gather)");
+  FV_REQUIRE(footprint >= (1u << 20) && footprint <= ((size_t)8 << 30), FV_ERR_INVALID, "footprint must be between 1 MiB and 8 GiB");
+  FV_REQUIRE(reps >= 1 && reps <= 100000, FV_ERR_INVALID, "reps out of range");
+  if (pattern == 1) FV_REQUIRE(row_bytes >= 16 && row_bytes % 16 == 0 && row_bytes <= footprint, FV_ERR_INVALID, "row_bytes must be a multiple of 16");
+  fv::DeviceGuard g(device);
+  FV_REQUIRE(g.ok, FV_ERR_CUDA, "cannot select device %d", device);
+  cudaDeviceProp prop;
+  FV_CUDA(cudaGetDeviceProperties(&prop, device));
+  void* buf = nullptr;
+  unsigned* sink = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  FV_CUDA(cudaMalloc(&buf, footprint));
+  cudaError_t e = cudaMalloc((void**)&sink, sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(buf, 1, footprint);
+  if (e == cudaSuccess) e = cudaEventCreate(&e0);
+  if (e == cudaSuccess) e = cudaEventCreate(&e1);
+  double bytes = 0.0;
+  float ms = 0.f;
+  if (e == cudaSuccess) {
+    const int grid = prop.multiProcessorCount * 8;
+    if (pattern == 0) {
+      const size_t n = footprint / 16;
+      k_probe_stream<<<grid, 256>>>(static_cast<const uint4*>(buf), n, 1, sink);
+      cudaEventRecord(e0);
+      k_probe_stream<<<grid, 256>>>(static_cast<const uint4*>(buf), n, (int)reps, sink);
+      cudaEventRecord(e1);
+      bytes = (double)n * 16.0 * reps;
+    } else {
+      const unsigned nrows = (unsigned)(footprint / row_bytes);
+      const int row_q = (int)(row_bytes / 16);
+      // reps full passes' worth of rows, spread over the warps
+      const size_t warps = (size_t)grid * 8;
+      size_t per_warp = ((size_t)nrows * reps + warps - 1) / warps;
+      per_warp = (per_warp + 3) & ~(size_t)3;
+      k_probe_gather<<<grid, 256>>>(static_cast<const uint4*>(buf), nrows, row_q, 64, 1u, sink);
+      cudaEventRecord(e0);
+      k_probe_gather<<<grid, 256>>>(static_cast<const uint4*>(buf), nrows, row_q, (int)per_warp, 7u, sink);
+      cudaEventRecord(e1);
+      bytes = (double)warps * (double)per_warp * (double)row_bytes;
+    }
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(sink);
+  cudaFree(buf);
+  FV_CUDA(e);
+  *gbytes_per_s = bytes / ((double)ms * 1e-3) / 1e9;
+  return FV_OK;
+}

@@ -10,6 +10,8 @@
 #include <cstring>
 #include <vector>
 
+#include <algorithm>
+
 #include "fv_common.h"
 
 namespace {
@@ -402,6 +404,14 @@ struct fv_hasher {
   uint8_t* d_table = nullptr;
   int32_t* d_iota = nullptr;
   uint32_t table_hl = 0, table_flags = 0xffffffffu;
+  // host-buffer calls: two pipeline slots, each a stream with device and pinned staging buffers (made on first use)
+  cudaStream_t pipe_stream[2] = {nullptr, nullptr};
+  cudaEvent_t pipe_done[2] = {nullptr, nullptr};
+  int32_t* pipe_d_in[2] = {nullptr, nullptr};
+  uint8_t* pipe_d_out[2] = {nullptr, nullptr};
+  int32_t* pipe_h_in[2] = {nullptr, nullptr};
+  uint8_t* pipe_h_out[2] = {nullptr, nullptr};
+  size_t pipe_bytes = 0;
 };
 
 namespace {
@@ -413,14 +423,48 @@ namespace {
   } while (0)
 
 template <int NT>
-void launch_hash(fv_hasher* hs, int mode, int grid, const int32_t* in, unsigned long long n, int W, int hl,
+void launch_hash(fv_hasher* hs, cudaStream_t stream, int mode, int grid, const int32_t* in, unsigned long long n, int W, int hl,
                  uint32_t flags, uint8_t* out) {
   if (mode == 0)
-    k_hash<NT, 0><<<grid, 256, 0, hs->stream>>>(hs->h, in, n, W, hl, flags, out);
+    k_hash<NT, 0><<<grid, 256, 0, stream>>>(hs->h, in, n, W, hl, flags, out);
   else if (mode == 1)
-    k_hash<NT, 1><<<grid, 256, 0, hs->stream>>>(hs->h, in, n, W, hl, flags, out);
+    k_hash<NT, 1><<<grid, 256, 0, stream>>>(hs->h, in, n, W, hl, flags, out);
   else
-    k_hash<NT, 2><<<grid, 256, 0, hs->stream>>>(hs->h, in, n, W, hl, flags, out);
+    k_hash<NT, 2><<<grid, 256, 0, stream>>>(hs->h, in, n, W, hl, flags, out);
+}
+
+// The hashing kernel for n items on `stream`; no synchronisation, the device error word only collects.
+void enqueue_hash(fv_hasher* hs, cudaStream_t stream, int mode, const int32_t* d_in, unsigned long long n, int W, uint32_t hash_len,
+                  uint32_t flags, uint8_t* d_out) {
+  const unsigned long long blocks = (n + 7) / 8;
+  const unsigned long long cap = (unsigned long long)hs->num_sms * 8;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  switch (hs->NT) {
+    case 1: launch_hash<1>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 2: launch_hash<2>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 3: launch_hash<3>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 4: launch_hash<4>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 5: launch_hash<5>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 6: launch_hash<6>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    case 7: launch_hash<7>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+    default: launch_hash<8>(hs, stream, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
+  }
+}
+
+// Codes of n token ids gathered from the vocabulary table on `stream` (the table must be current).
+void enqueue_gather(fv_hasher* hs, cudaStream_t stream, const int32_t* d_in, unsigned long long n, int stride, uint8_t* d_out) {
+  const HDev& h = hs->h;
+  const unsigned long long blocks = (n + 7) / 8;
+  const unsigned long long cap = (unsigned long long)hs->num_sms * 16;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  if (stride % 16 == 0)
+    k_gather_codes<uint4><<<grid, 256, 0, stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  else if (stride % 4 == 0)
+    k_gather_codes<uint32_t><<<grid, 256, 0, stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  else if (stride % 2 == 0)
+    k_gather_codes<uint16_t><<<grid, 256, 0, stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  else
+    k_gather_codes<uint8_t><<<grid, 256, 0, stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
 }
 
 int run_hash(fv_hasher* hs, int mode, const int32_t* d_in, unsigned long long n, int W, uint32_t hash_len,
@@ -449,19 +493,10 @@ int run_hash_table(fv_hasher* hs, const int32_t* d_in, unsigned long long n, uin
     hs->table_hl = hash_len;
     hs->table_flags = key_flags;
   }
-  const unsigned long long blocks = (n + 7) / 8;
-  const unsigned long long cap = (unsigned long long)hs->num_sms * 16;
-  const int grid = (int)(blocks < cap ? blocks : cap);
+  if (!d_in) return FV_OK;  // the caller only wanted the table
   FV_CUDA(cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream));
   FV_CUDA(cudaEventRecord(hs->ev0, hs->stream));
-  if (stride % 16 == 0)
-    k_gather_codes<uint4><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
-  else if (stride % 4 == 0)
-    k_gather_codes<uint32_t><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
-  else if (stride % 2 == 0)
-    k_gather_codes<uint16_t><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
-  else
-    k_gather_codes<uint8_t><<<grid, 256, 0, hs->stream>>>(hs->d_table, d_in, n, h.V, stride, d_out, hs->d_err);
+  enqueue_gather(hs, hs->stream, d_in, n, stride, d_out);
   FV_CUDA(cudaGetLastError());
   FV_CUDA(cudaEventRecord(hs->ev1, hs->stream));
   uint32_t err = 0;
@@ -485,21 +520,9 @@ int run_hash(fv_hasher* hs, int mode, const int32_t* d_in, unsigned long long n,
   // many more tokens than vocabulary entries: hash the vocabulary once, then gather
   if (mode == 0 && may_allocate && n >= 4ull * (unsigned long long)hs->h.V)
     return run_hash_table(hs, d_in, n, hash_len, flags, d_out, seconds);
-  unsigned long long blocks = (n + 7) / 8;
-  const unsigned long long cap = (unsigned long long)hs->num_sms * 8;
-  const int grid = (int)(blocks < cap ? blocks : cap);
   FV_CUDA(cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream));
   FV_CUDA(cudaEventRecord(hs->ev0, hs->stream));
-  switch (hs->NT) {
-    case 1: launch_hash<1>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    case 2: launch_hash<2>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    case 3: launch_hash<3>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    case 4: launch_hash<4>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    case 5: launch_hash<5>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    case 6: launch_hash<6>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    case 7: launch_hash<7>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-    default: launch_hash<8>(hs, mode, grid, d_in, n, W, (int)hash_len, flags, d_out); break;
-  }
+  enqueue_hash(hs, hs->stream, mode, d_in, n, W, hash_len, flags, d_out);
   FV_CUDA(cudaGetLastError());
   FV_CUDA(cudaEventRecord(hs->ev1, hs->stream));
   uint32_t err = 0;
@@ -524,6 +547,14 @@ void free_hasher(fv_hasher* hs) {
   if (hs->ev0) cudaEventDestroy(hs->ev0);
   if (hs->ev1) cudaEventDestroy(hs->ev1);
   if (hs->stream) cudaStreamDestroy(hs->stream);
+  for (int b = 0; b < 2; ++b) {
+    if (hs->pipe_d_in[b]) cudaFree(hs->pipe_d_in[b]);
+    if (hs->pipe_d_out[b]) cudaFree(hs->pipe_d_out[b]);
+    if (hs->pipe_h_in[b]) cudaFreeHost(hs->pipe_h_in[b]);
+    if (hs->pipe_h_out[b]) cudaFreeHost(hs->pipe_h_out[b]);
+    if (hs->pipe_done[b]) cudaEventDestroy(hs->pipe_done[b]);
+    if (hs->pipe_stream[b]) cudaStreamDestroy(hs->pipe_stream[b]);
+  }
   delete hs;
 }
 
@@ -667,26 +698,95 @@ int fv_hash_windows_device(fv_hasher* hs, const int32_t* d_idx, uint64_t nwin, u
   return run_hash(hs, weighted ? 1 : 2, d_idx, nwin, (int)window, hash_length, flags, d_out, kernel_seconds);
 }
 
-// Host-buffer forms: upload, hash, download.
+// Host-buffer forms.  The batch goes through the GPU in chunks on two pipeline slots (a stream with
+// its own device buffers each), so the upload of one chunk, the kernel of the previous one and the
+// download of the one before overlap; the buffers live as long as the hasher.  Page-locked caller
+// memory (fv_host_alloc_pinned) is copied from and to directly; pageable memory is staged through
+// the slots' pinned buffers by host threads while the GPU works on the other slot.
+constexpr size_t PIPE_BYTES = (size_t)16 << 20;  // per buffer
+
+static bool is_pinned(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeHost;
+}
+static void host_copy(void* dst, const void* src, size_t bytes) {
+  constexpr size_t PART = (size_t)1 << 20;
+  const long long parts = (long long)((bytes + PART - 1) / PART);
+#pragma omp parallel for schedule(static) if (parts > 4)
+  for (long long i = 0; i < parts; ++i) {
+    const size_t o = (size_t)i * PART;
+    memcpy(static_cast<char*>(dst) + o, static_cast<const char*>(src) + o, bytes - o < PART ? bytes - o : PART);
+  }
+}
+static int ensure_pipeline(fv_hasher* hs) {
+  if (hs->pipe_bytes) return FV_OK;
+  for (int b = 0; b < 2; ++b) {
+    FV_CUDA(cudaStreamCreateWithFlags(&hs->pipe_stream[b], cudaStreamNonBlocking));
+    FV_CUDA(cudaEventCreateWithFlags(&hs->pipe_done[b], cudaEventDisableTiming));
+    FV_CUDA(cudaMalloc((void**)&hs->pipe_d_in[b], PIPE_BYTES));
+    FV_CUDA(cudaMalloc((void**)&hs->pipe_d_out[b], PIPE_BYTES));
+    FV_CUDA(cudaHostAlloc((void**)&hs->pipe_h_in[b], PIPE_BYTES, cudaHostAllocDefault));
+    FV_CUDA(cudaHostAlloc((void**)&hs->pipe_h_out[b], PIPE_BYTES, cudaHostAllocDefault));
+  }
+  hs->pipe_bytes = PIPE_BYTES;
+  return FV_OK;
+}
+
 static int hash_host(fv_hasher* hs, int mode, const int32_t* in, uint64_t n, size_t in_per_item, uint32_t window,
                      uint32_t hash_length, uint32_t flags, uint8_t* out) {
   if (n == 0) return FV_OK;
   fv::DeviceGuard guard(hs->device);
   FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", hs->device);
+  FV_TRY(ensure_pipeline(hs));
   const size_t out_per = (flags & FV_HASH_BYTES) ? (size_t)hs->h.K : (size_t)((hs->h.K + 7) / 8);
-  int32_t* d_in = nullptr;
-  uint8_t* d_out = nullptr;
-  FV_CUDA(cudaMalloc((void**)&d_in, n * in_per_item * sizeof(int32_t)));
-  cudaError_t e = cudaMalloc((void**)&d_out, n * out_per);
-  int rc = FV_OK;
-  if (e == cudaSuccess)
-    e = cudaMemcpyAsync(d_in, in, n * in_per_item * sizeof(int32_t), cudaMemcpyHostToDevice, hs->stream);
-  if (e == cudaSuccess) rc = run_hash(hs, mode, d_in, n, (int)window, hash_length, flags, d_out, nullptr);
-  if (e == cudaSuccess && rc == FV_OK) e = cudaMemcpy(out, d_out, n * out_per, cudaMemcpyDeviceToHost);
-  cudaFree(d_in);
-  if (d_out) cudaFree(d_out);
-  if (rc != FV_OK) return rc;
-  FV_CUDA(e);
+  const size_t in_bytes = in_per_item * sizeof(int32_t);
+  // token batches much larger than the vocabulary: hash the vocabulary once, then every chunk gathers
+  const bool table = (mode == 0 && n >= 4ull * (unsigned long long)hs->h.V);
+  if (table) FV_TRY(run_hash_table(hs, nullptr, 0, hash_length, flags, nullptr, nullptr));
+  FV_CUDA(cudaMemsetAsync(hs->d_err, 0, sizeof(uint32_t), hs->stream));
+  FV_CUDA(cudaStreamSynchronize(hs->stream));
+  const size_t per_max = in_bytes > out_per ? in_bytes : out_per;
+  const uint64_t chunk = std::max<uint64_t>(PIPE_BYTES / per_max, 1);
+  const bool in_direct = is_pinned(in), out_direct = is_pinned(out);
+  uint64_t pending_first[2] = {0, 0}, pending_n[2] = {0, 0};  // chunk whose codes still sit in the slot's pinned buffer
+  uint64_t c = 0;
+  for (uint64_t first = 0; first < n; first += chunk, ++c) {
+    const int b = (int)(c & 1);
+    const uint64_t m = std::min<uint64_t>(chunk, n - first);
+    if (c >= 2) {  // the slot's previous chunk must have left it
+      FV_CUDA(cudaEventSynchronize(hs->pipe_done[b]));
+      if (!out_direct) host_copy(out + pending_first[b] * out_per, hs->pipe_h_out[b], pending_n[b] * out_per);
+    }
+    const int32_t* src = in + first * in_per_item;
+    if (!in_direct) {
+      host_copy(hs->pipe_h_in[b], src, m * in_bytes);
+      src = hs->pipe_h_in[b];
+    }
+    cudaStream_t st = hs->pipe_stream[b];
+    FV_CUDA(cudaMemcpyAsync(hs->pipe_d_in[b], src, m * in_bytes, cudaMemcpyHostToDevice, st));
+    if (table)
+      enqueue_gather(hs, st, hs->pipe_d_in[b], m, (int)out_per, hs->pipe_d_out[b]);
+    else
+      enqueue_hash(hs, st, mode, hs->pipe_d_in[b], m, (int)window, hash_length, flags, hs->pipe_d_out[b]);
+    FV_CUDA(cudaGetLastError());
+    FV_CUDA(cudaMemcpyAsync(out_direct ? out + first * out_per : hs->pipe_h_out[b], hs->pipe_d_out[b], m * out_per,
+                            cudaMemcpyDeviceToHost, st));
+    FV_CUDA(cudaEventRecord(hs->pipe_done[b], st));
+    pending_first[b] = first;
+    pending_n[b] = m;
+  }
+  for (uint64_t k = (c >= 2 ? c - 2 : 0); k < c; ++k) {  // drain in order
+    const int b = (int)(k & 1);
+    FV_CUDA(cudaEventSynchronize(hs->pipe_done[b]));
+    if (!out_direct) host_copy(out + pending_first[b] * out_per, hs->pipe_h_out[b], pending_n[b] * out_per);
+  }
+  uint32_t err = 0;
+  FV_CUDA(cudaMemcpy(&err, hs->d_err, sizeof(err), cudaMemcpyDeviceToHost));
+  if (err & FV_DEVERR_TOKEN_RANGE) return fv::fail(FV_ERR_DATA, "an input id was out of range (device check)");
   return FV_OK;
 }
 
@@ -751,7 +851,10 @@ int fv_hash_tokens_static(fv_hasher* hs, const int32_t* ids, uint64_t n, uint32_
   uint8_t* d_out = base + ((n * sizeof(int32_t) + 255) & ~(size_t)255);
   FV_CUDA(cudaMemcpyAsync(d_ids, ids, n * sizeof(int32_t), cudaMemcpyHostToDevice, hs->stream));
   const int rc = run_hash(hs, 0, d_ids, n, 0, hash_length, flags, d_out, nullptr, /*may_allocate=*/false);
-  if (rc != FV_OK) return rc;
+  if (rc != FV_OK) {
+    cudaStreamSynchronize(hs->stream);  // the upload must not outlive the caller's ids
+    return rc;
+  }
   FV_CUDA(cudaMemcpyAsync(out, d_out, n * out_per, cudaMemcpyDeviceToHost, hs->stream));
   FV_CUDA(cudaStreamSynchronize(hs->stream));
   return FV_OK;

@@ -316,10 +316,20 @@ class Hasher:
     def code_bytes(self, packed: bool) -> int:
         return (self.K + 7) // 8 if packed else self.K
 
-    def hash_tokens(self, ids, hash_length: int = 50, packed: bool = False, zero_unknown: bool = True) -> np.ndarray:
+    def _out(self, out, n: int, packed: bool) -> np.ndarray:
+        """Result array: the caller's (uint8, C-contiguous, e.g. page-locked) or a fresh one."""
+        shape = (n, self.code_bytes(packed))
+        if out is None:
+            return np.empty(shape, np.uint8)
+        if out.dtype != np.uint8 or not out.flags.c_contiguous or out.shape != shape:
+            raise ValueError(f"out must be a C-contiguous uint8 array of shape {shape}")
+        return out
+
+    def hash_tokens(self, ids, hash_length: int = 50, packed: bool = False, zero_unknown: bool = True,
+                    out: np.ndarray | None = None) -> np.ndarray:
         ids = as_c(ids, np.int32).reshape(-1)
         flags = (_lib.FV_HASH_PACKED if packed else _lib.FV_HASH_BYTES) | (0 if zero_unknown else _lib.FV_HASH_NO_UNK)
-        out = np.empty((ids.size, self.code_bytes(packed)), np.uint8)
+        out = self._out(out, ids.size, packed)
         check(_lib.lib().fv_hash_tokens(self._h, ptr(ids), ids.size, hash_length, flags, ptr(out)))
         return out if packed else out.view(np.int8)
 
@@ -339,7 +349,7 @@ class Hasher:
         return out if packed else out.view(np.int8)
 
     def hash_windows(self, idx, inv_freq=None, hash_length: int = 50, packed: bool = False,
-                     exact: bool = False) -> np.ndarray:
+                     exact: bool = False, out: np.ndarray | None = None) -> np.ndarray:
         """``exact``: sum every window in double like the reference instead of certifying float sums
         first (same codes, slower)."""
         idx = as_c(idx, np.int32)
@@ -351,7 +361,7 @@ class Hasher:
         else:
             f = as_c(inv_freq, np.float32)
             assert f.size == self.V
-        out = np.empty((idx.shape[0], self.code_bytes(packed)), np.uint8)
+        out = self._out(out, idx.shape[0], packed)
         check(_lib.lib().fv_hash_windows(self._h, ptr(idx), idx.shape[0], idx.shape[1], ptr(f) if f is not None else None,
                                          hash_length, flags, ptr(out)))
         return out if packed else out.view(np.int8)
@@ -411,3 +421,11 @@ class DeviceBuffer:
 
 def flush_l2(device: int = 0, nbytes: int = 256 << 20):
     check(_lib.lib().fv_flush_l2(device, nbytes))
+
+
+def probe_read_bandwidth(pattern: str, footprint: int, row_bytes: int = 1600, reps: int = 20, device: int = 0) -> float:
+    """GB/s this GPU delivers right now for ``pattern`` = "stream" or "gather" over ``footprint`` bytes."""
+    out = C.c_double(0)
+    check(_lib.lib().fv_probe_read_bandwidth(device, {"stream": 0, "gather": 1}[pattern], footprint, row_bytes, reps,
+                                             C.byref(out)))
+    return out.value

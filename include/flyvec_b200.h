@@ -275,6 +275,13 @@ int fv_copy_to_host(int device, void* dst, const void* src, size_t bytes);
 /* Writes `bytes` of a scratch buffer so that earlier data leave the L2 cache. */
 int fv_flush_l2(int device, size_t bytes);
 
+/* Measurement aid (no reference counterpart): read bandwidth of this GPU, measured on the spot, for the
+ * two access patterns of the train step -- pattern 0: streaming 128-bit loads over `footprint` bytes;
+ * pattern 1: whole rows of `row_bytes` gathered at random places, a warp per row -- each `reps` passes
+ * after a warm-up pass.  A footprint that fits the L2 gives the L2's rate, a much larger one the HBM's. */
+int fv_probe_read_bandwidth(int device, int pattern, size_t footprint, uint32_t row_bytes, uint32_t reps,
+                            double* gbytes_per_s);
+
 #ifdef __cplusplus
 }
 #endif

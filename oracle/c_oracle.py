@@ -30,6 +30,14 @@ def num_threads() -> int:
     return lib().orc_num_threads()
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the C oracle (overrides an inherited OMP_NUM_THREADS)."""
+    L = lib()
+    L.orc_set_num_threads.restype = None
+    L.orc_set_num_threads.argtypes = [C.c_int]
+    L.orc_set_num_threads(int(n))
+
+
 class StepRunner:
     """Holds the scratch memory for repeated calls of the C train step."""
 

@@ -203,3 +203,4 @@ int orc_hash_tokens(const float* syn, int K, int N, int V, const int32_t* ids, i
 }
 
 int orc_num_threads(void) { return omp_get_max_threads(); }
+void orc_set_num_threads(int n) { omp_set_num_threads(n > 0 ? n : 1); }
