@@ -219,7 +219,7 @@ def bench_train(args):
     dist = Dist(world)
     K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
     steps, warmup = args.steps, args.warmup
-    need_windows = (steps + warmup + 8) * world * B
+    need_windows = (steps + warmup + 8 + max(steps, args.e2e_steps)) * world * B
     ntok = args.tokens or min(CFG["tokens_per_gpu"] * world, 400_000_000)
     enc, off = make_or_load_corpus(ntok, rank, dist)
 
@@ -261,7 +261,9 @@ def bench_train(args):
     replicas_identical = all(d == digests[0] for d in digests)
 
     # ---- end to end: ids streamed from pinned host memory, normalisers read back ----
-    e2e_steps = min(steps, args.e2e_steps)
+    # its own step count: a call has fixed costs (control upload, final synchronisation, log read-back) that
+    # a user's epoch of thousands of steps does not notice but 20 steps would
+    e2e_steps = max(steps, args.e2e_steps)
     perm = tr.get_permutation()
     starts = engine.enumerate_windows(np.asarray(off), W)
     first = (warmup + steps) * world * B
@@ -601,7 +603,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="corpus size (default 50M per GPU, at most 400M)")
     ap.add_argument("--items", type=int, default=0, help="hash workloads: number of tokens / windows")
     ap.add_argument("--hash-length", type=int, default=50)
-    ap.add_argument("--e2e-steps", type=int, default=400)
+    ap.add_argument("--e2e-steps", type=int, default=300, help="steps of the end-to-end measurement (at least --steps)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--cpu-seconds-reference", type=float, default=90.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")

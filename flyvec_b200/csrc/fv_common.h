@@ -5,7 +5,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// the public header: in include/ of the source tree, beside this file in an installed package
+#if __has_include("../../include/flyvec_b200.h")
 #include "../../include/flyvec_b200.h"
+#else
+#include "flyvec_b200.h"
+#endif
 
 namespace fv {
 

@@ -4,16 +4,18 @@
 Flags, defaults, input formats (``encodings.npy`` int32 token ids, ``offsets.npy``
 uint64 chunk boundaries) and the checkpoint name and layout
 (``{prefix}_H_{hid}_W_{W}_LR_{lr}_{epoch}.npy``, float32 ``[K][2V]``) are the
-reference's.  ``--seed`` and ``--gpus`` are additions.  With more than one GPU
-the command re-launches itself under ``torch.distributed.run``, one process per
-GPU; each process owns one rank of the data-parallel trainer.
+reference's.  ``--seed`` and ``--gpus`` are additions.  Like the reference
+(flyvec/train_flyvec.py:141-146) one process drives all GPUs: ``--gpus N`` makes
+one trainer per device, links them, and the library runs one host thread per GPU.
+When a launcher has started one process per GPU instead (``RANK`` and
+``WORLD_SIZE`` in the environment) every process is one rank and the ranks meet
+through :mod:`flyvec_b200.rendezvous`.  Nothing here needs PyTorch.
 """
 from __future__ import annotations
 
 import argparse
 import os
 import re
-import sys
 import time
 from pathlib import Path
 
@@ -62,18 +64,16 @@ def checkpoint_epoch(path: str) -> int:
     return int(stem.split("_")[-1])
 
 
-def _dist_env():
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", str(rank)))
-    return rank, world, local
-
-
 def train(args, log=print):
-    """The body of ``main``: one process = one rank."""
-    from .engine import Trainer
+    """The body of ``main``.  One process drives ``--gpus`` devices, unless a launcher made this
+    process one rank of several (then it drives its own device only)."""
+    from .engine import Trainer, TrainerGroup
+    from .rendezvous import Rendezvous, env
 
-    rank, world, local = _dist_env()
+    rank, world, local = env()
+    launched = world > 1
+    if not launched:
+        log = log if rank == 0 else (lambda *a, **k: None)
     output_dir = Path(args.output_dir)
     if rank == 0 and not output_dir.exists():
         output_dir.mkdir(parents=True)
@@ -86,16 +86,20 @@ def train(args, log=print):
     N = 2 * vocab
     log(f"Determined a vocabulary size of {vocab}")
 
-    tr = Trainer(hid=args.hid, vocab=vocab, window=args.W, batch=args.batch_size, lr0=args.initial_learning_rate,
-                 delta=args.delta, prec=args.prec, device=local, rank=rank, world=world)
-    if world > 1:
-        import torch.distributed as dist
-
-        if not dist.is_initialized():
-            dist.init_process_group("gloo")
-        box = [Trainer.comm_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        tr.init_comm(box[0])
+    common = dict(hid=args.hid, vocab=vocab, window=args.W, batch=args.batch_size, lr0=args.initial_learning_rate,
+                  delta=args.delta, prec=args.prec)
+    rdv = None
+    if launched:
+        rdv = Rendezvous(rank, world)
+        tr = Trainer(device=local, rank=rank, world=world, **common)
+        tr.init_comm(rdv.broadcast(Trainer.comm_unique_id() if rank == 0 else None))
+        ngpus = world
+    elif args.gpus > 1:
+        tr = TrainerGroup(list(range(args.gpus)), **common)
+        ngpus = args.gpus
+    else:
+        tr = Trainer(device=0, **common)
+        ngpus = 1
 
     ns = tr.set_corpus(np.asarray(enc), np.asarray(off))
     log(f"Number of phrases:  {ns}")
@@ -107,16 +111,12 @@ def train(args, log=print):
     else:
         rng = np.random.default_rng(args.seed)
         R = np.float32(rng.normal(args.mu, args.sigma, (args.hid, N)))
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-
-        t = torch.from_numpy(np.ascontiguousarray(R))
-        dist.broadcast(t, src=0)  # every replica starts from rank 0's weights
-        R = t.numpy()
+    base_seed = args.seed if args.seed is not None else int(time.time())
+    if rdv is not None:  # every replica starts from rank 0's weights and shuffles with rank 0's seed
+        R = rdv.broadcast_array(R, (args.hid, N), np.float32)
+        base_seed = int(rdv.broadcast_array(np.array([base_seed], np.int64), (1,), np.int64)[0])
     tr.set_weights(R)
 
-    base_seed = args.seed if args.seed is not None else int(time.time())
     for i, ep in enumerate(range(epoch_start, args.Nep)):
         log(f"epoch ID =  {ep}")
         t1 = time.time()
@@ -124,24 +124,26 @@ def train(args, log=print):
         t11 = time.time()
         st = tr.run_epoch(ep, args.Nep)
         t2 = time.time()
+        if isinstance(st, list):
+            windows, seconds = sum(x["windows"] for x in st), max(x["seconds"] for x in st)
+        else:
+            windows, seconds = st["windows"] * ngpus, st["seconds"]
         log(f"time per epoch =  {t2 - t1} [s]   reshuffle time =  {t11 - t1} [s]   "
-            f"windows/s = {st['windows'] * world / max(st['seconds'], 1e-12):.4g}")
+            f"windows/s = {windows / max(seconds, 1e-12):.4g}")
         if rank == 0 and (((i + 1) % args.save_every) == 0 or i == (args.Nep - 1)):
             np.save(out_base + str(ep), tr.get_weights())
+    if rdv is not None:
+        rdv.barrier()
+        rdv.close()
     tr.close()
     return out_base
 
 
 def main(argv=None):
     args = parse_args(argv)
-    if args.gpus > 1 and "RANK" not in os.environ:
-        import subprocess
+    from .rendezvous import env
 
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
-               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29517"),
-               "-m", "flyvec_b200.train_flyvec"] + (sys.argv[1:] if argv is None else list(argv))
-        raise SystemExit(subprocess.call(cmd))
-    rank, _, _ = _dist_env()
+    rank, _, _ = env()
     train(args, log=print if rank == 0 else (lambda *a, **k: None))
 
 

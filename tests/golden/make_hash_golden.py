@@ -99,7 +99,12 @@ def time_reference(FlyVec, normalize_synapses, n_tokens: int = 20000):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else "/root/reference"
+    from oracle.build_oracle import reference_root
+
+    ref = reference_root(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else None)
+    if ref is None:
+        raise SystemExit("no reference checkout: pass its path, or set FLYVEC_REFERENCE")
+    ref_root = str(ref)
     FlyVec, normalize_synapses = import_reference(ref_root)
     from flyvec_b200 import synth
 

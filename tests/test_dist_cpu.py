@@ -22,9 +22,12 @@ WORLD, BATCH, STEPS = 2, 96, 3
 
 
 def shard(ns, batch, world, rank, step):
-    """Python twin of fv_shard_range (checked against the library in test_abi.py)."""
-    lo = min(step * world * batch + rank * batch, ns)
-    return lo, min(lo + batch, ns)
+    """Windows of the order that `rank` owns in global step `step`: the library's own rank
+    arithmetic (fv_shard_range, host code, no device needed)."""
+    from flyvec_b200.engine import shard_range
+
+    first, count = shard_range(ns, batch, world, rank, step)
+    return first, first + count
 
 
 def _worker(rank, port, outdir):

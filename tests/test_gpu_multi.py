@@ -17,9 +17,10 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-@pytest.mark.parametrize("exchange", ["mailbox", "nccl"])
+@pytest.mark.parametrize("exchange", ["mailbox", "mailbox-replicated", "nccl"])
 def test_two_ranks_match_oracle(built_lib, tmp_path, exchange):
-    """Both exchange modes: packets written straight into the peer's memory, and one all-gather per step."""
+    """Packets written straight into the peer's memory with the sharded and with the replicated update,
+    and one all-gather per step."""
     if _lib.device_count() < 2:
         pytest.skip("needs two GPUs")
     import os
@@ -28,10 +29,12 @@ def test_two_ranks_match_oracle(built_lib, tmp_path, exchange):
            "--master-addr", "127.0.0.1", "--master-port", "29541", str(ROOT / "tests" / "multi_rank_worker.py"),
            str(tmp_path), str(nsteps), str(batch)]
     env = dict(os.environ)
+    env.pop("FV_COMM", None)
+    env.pop("FV_SHARD", None)
     if exchange == "nccl":
         env["FV_COMM"] = "nccl"
-    else:
-        env.pop("FV_COMM", None)
+    elif exchange == "mailbox-replicated":
+        env["FV_SHARD"] = "0"
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     r0 = np.load(tmp_path / "rank0.npz")
