@@ -116,6 +116,7 @@ _PROTOTYPES = {
     "fv_device_free": ([C.c_int, _P], C.c_int),
     "fv_host_alloc_pinned": ([C.c_size_t, C.POINTER(_P)], C.c_int),
     "fv_host_free_pinned": ([_P], C.c_int),
+    "fv_device_mem_info": ([C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)], C.c_int),
     "fv_copy_to_device": ([C.c_int, _P, _P, C.c_size_t], C.c_int),
     "fv_copy_to_host": ([C.c_int, _P, _P, C.c_size_t], C.c_int),
     "fv_flush_l2": ([C.c_int, C.c_size_t], C.c_int),
@@ -192,6 +193,13 @@ def pinned_empty(shape, dtype) -> np.ndarray:
     check(lib().fv_host_alloc_pinned(n, C.byref(p)))
     buf = (C.c_char * n).from_address(p.value)
     return np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+
+def device_free_bytes(device: int = 0) -> int:
+    """Free device memory as cudaMemGetInfo reports it."""
+    free, total = C.c_size_t(0), C.c_size_t(0)
+    check(lib().fv_device_mem_info(device, C.byref(free), C.byref(total)))
+    return free.value
 
 
 def device_count() -> int:

@@ -167,6 +167,14 @@ int fv_host_free_pinned(void* ptr) {
   return FV_OK;
 }
 
+int fv_device_mem_info(int device, size_t* free_bytes, size_t* total_bytes) {
+  FV_REQUIRE(free_bytes && total_bytes, FV_ERR_INVALID, "fv_device_mem_info: output pointer is NULL");
+  fv::DeviceGuard g(device);
+  FV_REQUIRE(g.ok, FV_ERR_CUDA, "fv_device_mem_info: cannot select device %d", device);
+  FV_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+  return FV_OK;
+}
+
 int fv_copy_to_device(int device, void* dst, const void* src, size_t bytes) {
   fv::DeviceGuard g(device);
   FV_REQUIRE(g.ok, FV_ERR_CUDA, "fv_copy_to_device: cannot select device %d", device);

@@ -974,6 +974,91 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
   }
 }
 
+// Tagging for the sharded update: a rank claims only the positions of the rows it owns
+// (i % G == rank), i.e. about 1/G of a step's slots.  Every thread takes U slots; the loads of
+// each stage (ids, winners, weights) are issued for all U together, so a block round costs the
+// same chain of dependent accesses as one slot per thread does, and one round covers the step.
+// The live slots of a block round are numbered with one prefix sum (one counter bump per round).
+template <int U>
+__global__ void __launch_bounds__(XX_THREADS, 3) k_tag_own(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
+  grid_dependency_wait();
+  const int parity = (int)((d.ctl->tick + local) & 1);
+  if ((int)blockIdx.x < xx_ctas) {
+    xx_finish(d, local);
+    return;
+  }
+  const int svc = xx_ctas + push_ctas;  // CTAs that serve the exchange instead of tagging
+  if ((int)blockIdx.x < svc) {
+    push_winners(d, parity, blockIdx.x - xx_ctas, push_ctas);
+    return;
+  }
+  if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  __shared__ uint32_t s_scan[XX_WARPS];
+  __shared__ uint32_t s_gbase;
+  const int E = d.G * d.B * d.W;  // the sharded update runs without the anti-Hebbian term: one kind of slot
+  constexpr int TAG_BLOCK = U * XX_THREADS;
+  const int nblocks = (E + TAG_BLOCK - 1) / TAG_BLOCK;
+  const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  // every rank begins with the blocks of its own windows, whose winners are here already
+  const int first_blk = (int)(((long long)nblocks * d.rank) / d.G);
+  for (int b0 = blockIdx.x - svc; b0 < nblocks; b0 += gridDim.x - svc) {
+    const int blk = (b0 + first_blk) % nblocks;
+    int i[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      i[u] = (ev < E) ? step_id(d, idx, ev) : -1;
+    }
+    const unsigned long long* ww[U];
+    unsigned long long w0[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      const bool mine = i[u] >= 0 && (int)((uint32_t)i[u] - fdiv((uint32_t)i[u], d.mG, d.sG) * (uint32_t)d.G) == d.rank;
+      if (!mine) i[u] = -1;
+      const uint32_t q = fdiv((uint32_t)(mine ? ev : 0), d.mW, d.sW);  // window of the global step
+      const uint32_t r = fdiv(q, d.mB, d.sB);                          // its rank
+      ww[u] = packet(d, parity, (int)r) + (int)(q - r * (uint32_t)d.B);
+      w0[u] = mine ? load_relaxed_sys64(ww[u]) : 0ull;
+    }
+    uint32_t pos[U], c0[U];
+    bool go[U];
+    uint32_t mine_n = 0u;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      int mu = -1;
+      if (i[u] >= 0) mu = ((uint32_t)(w0[u] >> 32) == seq) ? (int)(uint32_t)w0[u] : (int)pk_read(d, ww[u], seq, (uint32_t)-1);
+      go[u] = mu >= 0;
+      pos[u] = go[u] ? (uint32_t)((size_t)i[u] * d.Kp + mu) : 0u;
+      c0[u] = go[u] ? __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos[u]) : 0u;
+      mine_n += go[u] ? 1u : 0u;
+    }
+    uint32_t incl = mine_n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(FULL, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_scan[wic] = incl;
+    __syncthreads();
+    uint32_t before = 0u, tot = 0u;
+#pragma unroll
+    for (int w = 0; w < XX_WARPS; ++w) {
+      const uint32_t c = s_scan[w];
+      before += (w < wic) ? c : 0u;
+      tot += c;
+    }
+    if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
+    __syncthreads();
+    uint32_t slot = s_gbase + before + incl - mine_n;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (go[u]) claim_position(d, pos[u], c0[u], slot++, 1u, (uint32_t)E);
+    __syncthreads();  // s_scan and s_gbase are reused by the next round
+  }
+}
+
 // Per-unit combine over ranks: n = number of ranks with xx != 0, X = mean of xx
 // over those ranks (the closed form of cu_special_reduction.cu:42-67 applied to
 // the -xx*W term).
@@ -1715,6 +1800,7 @@ struct fv_trainer {
   unsigned long long ticks = 0;  // host copy of StepCtl::tick
   float delta_now = 0.f;         // anti-Hebbian strength used by the next run_* call
   int tag_un = 1;
+  int tag_own_u = 1, tag_own_grid = 0;  // sharded update: slots per thread and CTAs of the owner-only tagging kernel
   int fwd_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
   size_t fwd_smem = 0, scan_smem = 0, apply_smem = 0;
 };
@@ -1844,8 +1930,18 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     const bool fused = single || (tr->comm_mode == 2 && !emulate && !split_exchange);
     const size_t table_smem = tag_table_bytes(tr->tag_un);
     const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
-    launch_pdl(tr->tag_un == 1 ? k_tag<1> : k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx,
-               xx_ctas, push_ctas);
+    const int own_u = d.shard ? tr->tag_own_u : 1;
+    if (own_u > 1) {
+      // sharded and more slots than resident threads: the batched owner-only kernel, one round
+      const int grid = tr->tag_own_grid + xx_ctas + push_ctas;
+      if (own_u == 2) launch_pdl(k_tag_own<2>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
+      else if (own_u == 4) launch_pdl(k_tag_own<4>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
+      else launch_pdl(k_tag_own<8>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
+    } else {
+      const int un = d.shard ? 1 : tr->tag_un;  // an owner sees 1/G of the slots: duplicates inside a block are rare
+      launch_pdl(un == 1 ? k_tag<1> : k_tag<2>, (d.shard ? tr->tag_own_grid : tr->tag_grid) + xx_ctas + push_ctas, XX_THREADS,
+                 un == 1 ? (size_t)0 : table_smem, tr->stream, d, local, idx, xx_ctas, push_ctas);
+    }
     *launches += 1;
   } else if (phase == 2) {
     launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
@@ -2104,6 +2200,11 @@ void choose_tag_variant(fv_trainer* tr, int force_un) {
   const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS;
   tr->tag_un = force_un ? force_un : (((E + XX_THREADS - 1) / XX_THREADS > resident) ? 2 : 1);
   tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, (int)resident);
+  // sharded update: slots per thread so that one block round covers the step
+  int u = 1;
+  while (u < 8 && (E + (size_t)XX_THREADS * u - 1) / ((size_t)XX_THREADS * u) > resident) u *= 2;
+  tr->tag_own_u = u;
+  tr->tag_own_grid = grid_for(E, XX_THREADS * u, (int)resident);
 }
 
 int create_impl(const fv_config* cfg, fv_trainer* tr) {
@@ -2771,6 +2872,17 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
   if (strcmp(key, "tag_variant") == 0) {
     FV_REQUIRE(value == 0.0 || value == 1.0 || value == 2.0, FV_ERR_INVALID, "tag_variant must be 0 (by size), 1 or 2, got %g", value);
     choose_tag_variant(tr, (int)value);
+    return FV_OK;
+  }
+  if (strcmp(key, "tag_own_slots") == 0) {
+    FV_REQUIRE(value == 0.0 || value == 1.0 || value == 2.0 || value == 4.0 || value == 8.0, FV_ERR_INVALID,
+               "tag_own_slots must be 0 (by size), 1, 2, 4 or 8, got %g", value);
+    choose_tag_variant(tr, 0);
+    if (value != 0.0) {
+      const size_t E = (size_t)tr->d.G * tr->d.B * tr->d.W;
+      tr->tag_own_u = (int)value;
+      tr->tag_own_grid = grid_for(E, XX_THREADS * tr->tag_own_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
+    }
     return FV_OK;
   }
   if (strcmp(key, "shard") == 0) {

@@ -193,6 +193,8 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *   "tag_variant"  1: the scatter bookkeeping claims positions one slot per thread; 2: it first
  *                  deduplicates 1024 slots in shared memory; 0: chosen by the size of a step;
  *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
+ *   "tag_own_slots" slots a thread of the sharded update's tagging kernel takes per round: 1, 2, 4, 8,
+ *                  or 0 for the size-based choice;
  *   "loopback_peers" 1: test aid -- every peer's mailbox is mapped onto this rank's own, so a peer's
  *                  words never arrive and the first wait for one runs into spin_limit. */
 int fv_trainer_set_option(fv_trainer* tr, const char* key, double value);
@@ -270,6 +272,8 @@ int fv_device_alloc(int device, size_t bytes, void** ptr);
 int fv_device_free(int device, void* ptr);
 int fv_host_alloc_pinned(size_t bytes, void** ptr);
 int fv_host_free_pinned(void* ptr);
+/* Free and total device memory as the CUDA runtime reports them (cudaMemGetInfo). */
+int fv_device_mem_info(int device, size_t* free_bytes, size_t* total_bytes);
 int fv_copy_to_device(int device, void* dst, const void* src, size_t bytes);
 int fv_copy_to_host(int device, void* dst, const void* src, size_t bytes);
 /* Writes `bytes` of a scratch buffer so that earlier data leave the L2 cache. */

@@ -120,6 +120,31 @@ def test_config2_shapes_eight_linked_ranks_sharded(built_lib):
     g.close()
 
 
+@pytest.mark.parametrize("slots", [2, 4, 8])
+def test_batched_owner_tagging_on_duplicate_heavy_steps(built_lib, slots):
+    """The sharded update's tagging kernel with several slots per thread, forced at a small shape: a tiny
+    vocabulary makes the same (unit, token) pair occur many times in one block round."""
+    world, B = 3, 700
+    p = small_problem(K=40, V=36, W=9, ntok=40000, seed=29, zipf_s=1.2)
+    g = make_group(p, world, B, shard=True, lr0=5e-4)
+    for t in g.ranks:
+        t.set_option("tag_own_slots", slots)
+    eps = np.float32(5e-4)
+    Wcur = p["W0"]
+    for t in range(3):
+        win, xx, nc, s = g.step_debug(t, eps)
+        Wgpu = replicas_identical(g)
+        order = p["perm"][t * world * B:(t + 1) * world * B]
+        idxs = [orc.build_idx(p["enc"], p["starts"], order[r * B:(r + 1) * B], 9, 36) for r in range(world)]
+        Wref, info = orc.train_step(Wcur, idxs, p["f"], 36, eps)
+        for r in range(world):
+            np.testing.assert_array_equal(win[r], info["win"][r])
+        np.testing.assert_allclose(nc, info["nc"], rtol=1e-5)
+        assert_weights_close(Wgpu, Wref)
+        Wcur = Wgpu
+    g.close()
+
+
 def test_sharded_and_replicated_updates_agree_bit_for_bit(built_lib):
     """Both forms of the update compute the same function of the exchanged data."""
     p = small_problem(K=100, V=400, W=11, ntok=80000, seed=23)

@@ -292,8 +292,10 @@ def test_anti_hebbian_second_winner(built_lib, world):
         assert rel_err(Wgpu, Wref) < STEP_TOL
         Wcur = Wgpu
     # the term must matter: without it the weights differ visibly
-    Wplain, _ = orc.train_step(p["W0"], [orc.build_idx(p["enc"], p["starts"], p["perm"][:batch], p["W"], p["V"])],
-                               p["f"], p["V"], eps)
+    idx0 = orc.build_idx(p["enc"], p["starts"], p["perm"][:batch], p["W"], p["V"])
+    Wplain, _ = orc.train_step(p["W0"], [idx0], p["f"], p["V"], eps)
+    Wdelta, _ = orc.train_step(p["W0"], [idx0], p["f"], p["V"], eps, delta=delta)
+    assert rel_err(Wplain, Wdelta) > 100 * STEP_TOL
     tr.close()
 
 

@@ -34,6 +34,27 @@ def test_static_staging_matches_allocating_path_twice_in_a_row(built_lib):
     h.close()
 
 
+def test_static_staging_allocates_nothing_and_matches_the_oracle(built_lib):
+    """What the entry point is for: the device's free memory is the same before and after its calls
+    (its first call on the device included, which only looks up the array's address), and its codes
+    are the oracle's, compared directly."""
+    from oracle import flyvec_oracle as orc
+
+    K, V = 128, 600
+    W = synth.make_weights(K, 2 * V, seed=12)
+    h = Hasher(W, normalize=True)
+    ids = synth.make_hash_ids(3000, V, seed=5)
+    h.hash_tokens(ids[:16], hash_length=20)  # the hashing kernel itself is loaded by now (CUDA loads kernels on first use)
+    free_before = _lib.device_free_bytes(0)
+    first = h.hash_tokens_static(ids, hash_length=20)
+    second = h.hash_tokens_static(ids[::-1].copy(), hash_length=20, packed=True)
+    assert _lib.device_free_bytes(0) == free_before, "fv_hash_tokens_static changed the amount of free device memory"
+    Wn = orc.normalize_synapses(W)
+    np.testing.assert_array_equal(first, orc.hash_tokens(Wn, V, ids, 20))
+    np.testing.assert_array_equal(second, orc.pack_codes(orc.hash_tokens(Wn, V, ids[::-1], 20)))
+    h.close()
+
+
 def test_static_staging_rejects_oversized_batches(built_lib):
     K, V = 400, 300
     h = Hasher(synth.make_weights(K, 2 * V, seed=3))
