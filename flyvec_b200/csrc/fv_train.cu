@@ -2275,6 +2275,9 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_TRY(dev_alloc(&tr->d_ncb, 2));
   FV_TRY(dev_alloc(&tr->d_ctl, 1));
   FV_CUDA(cudaMemsetAsync(tr->d_cnt, 0, E * sizeof(int32_t), tr->stream));
+  // a record whose last word is zero is a hole; k_apply returns every used record to that state, so the
+  // list must start out as all holes (memory recycled from an earlier allocation is not zero)
+  FV_CUDA(cudaMemsetAsync(tr->d_rec, 0, E * sizeof(uint4), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_colmax, 0, 2 * (size_t)d.Kp * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_ncb, 0, 2 * sizeof(uint32_t), tr->stream));
   FV_CUDA(cudaMemsetAsync(tr->d_ctl, 0, sizeof(StepCtl), tr->stream));
