@@ -396,6 +396,27 @@ def hash_summary(args):
     return out
 
 
+def bench_linked_ranks(args):
+    """`--linked-ranks G`: the G ranks of a multi-GPU job as linked trainers on ONE GPU, advanced phase by
+    phase (profiling aid, not a bench line): with FV_LOCKSTEP_TIMES=1 the library prints what each phase of
+    one rank costs when it never has to wait for a peer."""
+    from flyvec_b200 import engine, synth
+
+    K, V, W, B = CFG["K"], CFG["V"], CFG["W"], CFG["batch"]
+    G = args.linked_ranks
+    enc, off = synth.make_corpus(args.tokens or 12_000_000, V, s=CFG["zipf_s"], mean_len=CFG["chunk_mean"], min_len=W,
+                                 seed=CORPUS_SEED)
+    g = engine.TrainerGroup([0] * G, hid=K, vocab=V, window=W, batch=B, lr0=CFG["lr"],
+                            shard=None if args.shard < 0 else bool(args.shard))
+    g.set_corpus(enc, off)
+    g.set_weights(synth.make_weights(K, 2 * V, seed=WEIGHT_SEED))
+    g.shuffle(PERM_SEED)
+    st = g.run_steps(0, args.warmup + args.steps, np.float32(CFG["lr"]), warmup=args.warmup)
+    print(json.dumps({"metric": "G linked ranks on one GPU, phase by phase", "ranks": G, "steps": args.steps,
+                      "us_per_global_step_all_ranks": st[0]["seconds"] / args.steps * 1e6}))
+    g.close()
+
+
 def bench_update_emulated(args):
     """The replicated update (count, scan, apply) of `--emulate-ranks G` ranks' windows on ONE GPU: every rank's
     forward pass runs in turn, then one update over all G*B windows, exactly what each GPU of a G-GPU job does
@@ -600,6 +621,9 @@ def main():
     ap.add_argument("--workload", choices=["train", "hash_tokens", "hash_windows"], default="train")
     ap.add_argument("--emulate-ranks", type=int, default=0,
                     help="one GPU: time the update of this many ranks' windows (profiling aid, not a bench line)")
+    ap.add_argument("--linked-ranks", type=int, default=0,
+                    help="one GPU: run this many linked ranks phase by phase (profiling aid, not a bench line)")
+    ap.add_argument("--shard", type=int, default=-1, help="with --linked-ranks: 1 sharded, 0 replicated update, -1 default")
     ap.add_argument("--tokens", type=int, default=0, help="corpus size (default 50M per GPU, at most 400M)")
     ap.add_argument("--items", type=int, default=0, help="hash workloads: number of tokens / windows")
     ap.add_argument("--hash-length", type=int, default=50)
@@ -611,6 +635,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return bench_reference(args)
+    if args.linked_ranks:
+        return bench_linked_ranks(args)
     if args.emulate_ranks:
         return bench_update_emulated(args)
     if args.workload == "train":

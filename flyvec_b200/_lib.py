@@ -99,6 +99,7 @@ _PROTOTYPES = {
     "fv_comm_unique_id": ([_P], C.c_int),
     "fv_trainer_init_comm": ([_P, _P], C.c_int),
     "fv_trainer_set_option": ([_P, C.c_char_p, C.c_double], C.c_int),
+    "fv_trainer_get_counter": ([_P, C.c_char_p, C.POINTER(C.c_uint64)], C.c_int),
     "fv_trainer_comm_mode": ([_P, C.POINTER(C.c_int)], C.c_int),
     "fv_shard_range": ([C.c_uint64, C.c_uint32, C.c_int32, C.c_int32, C.c_uint64, C.POINTER(C.c_uint64),
                         C.POINTER(C.c_uint64)], C.c_int),

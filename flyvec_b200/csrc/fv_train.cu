@@ -64,6 +64,8 @@ struct StepCtl {
   uint32_t out_count;     // (unused)
   uint32_t pad;
   uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
+  uint32_t need_scan;     // k_eval found a unit whose maximum its candidate list cannot certify: k_colscan must stream
+  uint32_t scans_run;     // steps of this call in which k_colscan streamed the matrix
   // Device-side phase clock: every step kernel's first thread charges the time since the previous
   // mark to the phase that was running and names its own.  No events, so the launches stay chained.
   unsigned long long t_mark;
@@ -108,6 +110,16 @@ struct Dev {
   uint4* rec;      // [G*B*w] touched-position records {position, parked weight bits, 1/count bits, 0}
   uint32_t* colmax;
   uint32_t* ncb;
+  // Candidate rows of the column maxima (see k_eval): per unit up to CAND_CAP rows and a floor that bounds
+  // |wt| of every scanned row outside the list.
+  int use_cand;
+  int32_t* cand_rows;             // [Kp][CAND_CAP]
+  int32_t* cand_n;                // [Kp] rows listed (may count past CAND_CAP: clamp)
+  uint32_t* cand_floor;           // [Kp] bit pattern of the floor
+  uint32_t* cand_unc;             // [Kp] 1: the running step could not certify this unit's maximum from its list
+  unsigned long long* colarg;     // [Kp] (bit pattern << 32 | row) of the column maximum found by k_colscan
+  double* stat_x;  // [2][Kp] mean xx over the active ranks, written by the scan for the apply kernel
+  int32_t* stat_n; // [2][Kp] number of active ranks
   StepCtl* ctl;
   float* nc_log;
   float* s_log;
@@ -243,6 +255,7 @@ __global__ void k_set_ctl(StepCtl* ctl, unsigned long long base, float eps, floa
   ctl->eps = eps;
   ctl->delta = delta;
   ctl->fwd_next[0] = ctl->fwd_next[1] = 0u;
+  ctl->scans_run = 0u;
   for (int i = 0; i < 8; ++i) ctl->phase_ns[i] = 0ull;
   ctl->t_mark = global_timer();
   ctl->phase_now = PH_OTHER;
@@ -1159,6 +1172,10 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     sC[mu] = X * alpha[mu];
     sN[mu] = n;
     sMax[mu] = 0u;
+    if (blockIdx.x == 0) {  // the apply kernel takes the combine from here instead of polling G words per unit again
+      d.stat_x[p * d.Kp + mu] = X;
+      d.stat_n[p * d.Kp + mu] = n;
+    }
     const uint32_t bad = (mu < d.K && n > 0) ? unit_cancelled(d, p, mu) : 0u;
     sBad[mu] = bad;
     if (bad) s_any_bad = 1;
@@ -1308,6 +1325,316 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 }
 
 // ---------------------------------------------------------------------------
+// Column maxima without streaming the matrix.
+//
+// nc needs, per active unit mu, the largest |wt[i][mu]| over the rows i the step did NOT touch.  The
+// weights only change at touched positions (and when the scales are folded in), so the few rows that
+// can hold that maximum are kept from step to step:
+//   cand_rows[mu][..]  candidate rows,   cand_floor[mu]  a bound: every scanned row outside the list
+//                                                         has |wt| <= floor (bit patterns compare like floats).
+// k_eval reads the candidates' current weights -- a tagged one was touched and is skipped -- and takes
+// their maximum m.  If m >= floor no row outside the list can beat it: m IS the maximum over untouched
+// rows, exactly.  Otherwise (every strong candidate touched in this step) the unit is marked uncertain
+// and k_colscan streams the matrix as k_scan does, tracking the arg-max row; its last CTA then lowers
+// the unit's floor to the maximum found and lists that row.  k_apply keeps the bound true: a touched
+// weight whose new magnitude exceeds its unit's floor is listed (or raises the floor when the list is
+// full).  After a fold or new weights the lists are rebuilt: k_eval marks every unit uncertain,
+// k_colscan finds the maxima, k_collect lists every untouched row above 0.9 of its unit's maximum.
+// With the sharded update a rank keeps lists for the rows it owns.
+// ---------------------------------------------------------------------------
+constexpr int CAND_CAP = 32;
+
+// The first half of k_scan (combine, records, exact D at the touched positions) plus the list query.
+__global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, const int32_t* __restrict__ idx, int rebuild) {
+  grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_SCAN);
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
+  int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
+  uint32_t* sBad = reinterpret_cast<uint32_t*>(sN + d.Kp) + d.Kp;  // same layout as k_scan (its column maxima lie between)
+  const int p = (int)((d.ctl->tick + local) & 1);
+  const int lane = threadIdx.x & 31;
+  const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  __shared__ int s_any_bad;
+  if (threadIdx.x == 0) s_any_bad = 0;
+  __syncthreads();
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    double X = 0.0;
+    int n = 0;
+    if (mu < d.K) unit_stats(d, p, seq, mu, &X, &n);  // waits (bounded) for a peer's xx still on its way
+    sC[mu] = X * alpha[mu];
+    sN[mu] = n;
+    if (blockIdx.x == 0) {
+      d.stat_x[p * d.Kp + mu] = X;
+      d.stat_n[p * d.Kp + mu] = n;
+    }
+    const uint32_t bad = (mu < d.K && n > 0) ? unit_cancelled(d, p, mu) : 0u;
+    sBad[mu] = bad;
+    if (bad) s_any_bad = 1;
+  }
+  __syncthreads();
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nthreads = gridDim.x * blockDim.x;
+  const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s_any_bad) {
+    const unsigned long long* packet0 = packet(d, p, 0);
+    for (int k = e0; k < nrec; k += nthreads) {
+      const uint4 r = d.rec[k];
+      if (r.w == 0u) continue;
+      const int irow = (int)fdiv(r.x, d.mKp, d.sKp);
+      const int mu = (int)r.x - irow * d.Kp;
+      if (!sBad[mu]) continue;
+      const int2 c = cancelled_multiplicity(packet0, d.P, d.G, d.B, d.W, d.MO, d.has_delta, idx, d.idx_rstride, irow, mu, sBad[mu]);
+      if (c.x) d.cnt[k] -= c.x;
+      if (c.y) d.cntn[k] -= c.y;
+    }
+  }
+
+  // the candidate lists: one warp per unit, a lane per candidate
+  {
+    const int warp = (blockIdx.x * SCAN_THREADS + threadIdx.x) >> 5, nwarps = (gridDim.x * SCAN_THREADS) >> 5;
+    const uint32_t* __restrict__ wbits = reinterpret_cast<const uint32_t*>(d.wt);
+    for (int mu = warp; mu < d.K; mu += nwarps) {
+      if (rebuild) {
+        if (lane == 0) {
+          d.cand_unc[mu] = 1u;
+          d.cand_n[mu] = 0;
+          d.ctl->need_scan = 1u;
+        }
+        continue;
+      }
+      if (sN[mu] == 0) continue;  // no update for this unit: its maximum is not needed
+      const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+      uint32_t m = 0u;
+      for (int j = lane; j < n; j += 32) {
+        const int row = __ldcg(d.cand_rows + (size_t)mu * CAND_CAP + j);
+        const uint32_t w = __ldcg(wbits + (size_t)row * d.Kp + mu) & ABS_MASK;
+        m = max(m, w > TAG_BASE ? 0u : w);  // a tag: touched in this step, its exact D is taken at the record
+      }
+      m = warp_max_u32(m);
+      if (lane == 0) {
+        if (m >= __ldcg(d.cand_floor + mu)) {
+          d.colmax[p * d.Kp + mu] = m;
+        } else {
+          d.cand_unc[mu] = 1u;
+          d.ctl->need_scan = 1u;
+        }
+      }
+    }
+  }
+
+  // exact D at the touched positions
+  const float delta = d.ctl->delta;
+  uint32_t tmax = 0u;
+  constexpr int TS = 4;
+  for (int k0 = e0; k0 < nrec; k0 += TS * nthreads) {
+    int cp[TS], cn[TS];
+    uint4 rc[TS];
+#pragma unroll
+    for (int u = 0; u < TS; ++u) {
+      const int k = k0 + u * nthreads;
+      cp[u] = (k < nrec) ? d.cnt[k] : 0;
+      cn[u] = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
+      rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < TS; ++u) {
+      const int k = k0 + u * nthreads;
+      if (k >= nrec) continue;
+      const int own = cp[u] + (int)(rc[u].w & 0xffffu);
+      // sharded: the peers learn this record's count now, long before they need it
+      if (d.shard) push_entry(d, k, rc[u].w ? (rc[u].x | ENTRY_VALID) : ENTRY_HOLE, own);
+      if (rc[u].w == 0u) continue;  // a reserved record nobody claimed
+      const int mu = (int)(rc[u].x - fdiv(rc[u].x, d.mKp, d.sKp) * (uint32_t)d.Kp);
+      if (sN[mu] == 0) continue;    // the unit proved inactive on every rank: no update there
+      const float c = (float)own - delta * (float)(cn[u] + (int)(rc[u].w >> 16));
+      const double D = -sC[mu] * (double)__uint_as_float(rc[u].y) + (double)c * (double)__uint_as_float(rc[u].z) / (double)sN[mu];
+      tmax = max(tmax, __float_as_uint(fabsf((float)D)));
+    }
+  }
+  __shared__ uint32_t s_tmax;
+  if (threadIdx.x == 0) s_tmax = 0u;
+  __syncthreads();
+  tmax = warp_max_u32(tmax);
+  if (lane == 0 && tmax) atomicMax(&s_tmax, tmax);
+  __syncthreads();
+  if (threadIdx.x == 0 && s_tmax) atomicMax(&d.ncb[p], s_tmax);  // one global atomic per CTA
+}
+
+// Sharded update: this rank's partial normaliser (its records and the columns of its rows) and the length
+// of its entry list go to every rank, each in one flagged word.  Run by one CTA once the maxima are final.
+__device__ __forceinline__ void publish_partial(const Dev& d, int local, int p) {
+  __shared__ float s_pub[SCAN_THREADS / 32];
+  const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  float dense = 0.f;
+  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x) {
+    const int n = __ldcg(d.stat_n + p * d.Kp + mu);
+    if (n > 0)
+      dense = fmaxf(dense, (float)(fabs(__ldcg(d.stat_x + p * d.Kp + mu) * alpha[mu]) * (double)__uint_as_float(__ldcg(&d.colmax[p * d.Kp + mu]))));
+  }
+  dense = warp_max(dense);
+  if ((threadIdx.x & 31) == 0) s_pub[threadIdx.x >> 5] = dense;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float nc = __uint_as_float(__ldcg(&d.ncb[p]));
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) nc = fmaxf(nc, s_pub[w]);
+    s_pub[0] = nc;
+  }
+  __syncthreads();
+  if (threadIdx.x < d.G) {
+    const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
+    const unsigned nrec = min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+    unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
+    store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_pub[0]));
+    unsigned long long* outw = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
+    store_relaxed_sys64(outw + p * MAX_RANKS + d.rank, (seq << 32) | nrec);
+  }
+}
+
+// Streams the matrix only when k_eval asked for it: column maxima of |wt| with tags read as 0 and
+// the row of each maximum; the last CTA repairs the lists of the uncertain units.
+__global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, int rebuild) {
+  grid_dependency_wait();
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;
+  const int p = (int)((d.ctl->tick + local) & 1);
+  if (!d.ctl->need_scan) {
+    if (d.shard && blockIdx.x == 0) publish_partial(d, local, p);
+    return;
+  }
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned long long* sArg = reinterpret_cast<unsigned long long*>(smem_raw);  // [Kp] CTA maxima with their rows
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) sArg[mu] = 0ull;
+  __syncthreads();
+  const int Kq = d.Kq;
+  const int groups = SCAN_THREADS / Kq;
+  const int g = threadIdx.x / Kq, q = threadIdx.x - g * Kq;
+  if (g < groups) {
+    const int stride = gridDim.x * groups;
+    unsigned long long a0 = 0ull, a1 = 0ull, a2 = 0ull, a3 = 0ull;  // (bits << 32) | row
+    auto fold_in = [&](const uint4& v, int row) {
+      uint32_t u;
+      u = v.x & ABS_MASK; a0 = max(a0, ((unsigned long long)(u > TAG_BASE ? 0u : u) << 32) | (uint32_t)row);
+      u = v.y & ABS_MASK; a1 = max(a1, ((unsigned long long)(u > TAG_BASE ? 0u : u) << 32) | (uint32_t)row);
+      u = v.z & ABS_MASK; a2 = max(a2, ((unsigned long long)(u > TAG_BASE ? 0u : u) << 32) | (uint32_t)row);
+      u = v.w & ABS_MASK; a3 = max(a3, ((unsigned long long)(u > TAG_BASE ? 0u : u) << 32) | (uint32_t)row);
+    };
+    const uint4* __restrict__ base = reinterpret_cast<const uint4*>(d.wt) + q;
+    const int rmul = d.shard ? d.G : 1, radd = d.shard ? d.rank : 0;
+    const int nrows = d.shard ? (d.N - d.rank + d.G - 1) / d.G : d.N;
+    int row = blockIdx.x * groups + g;
+    for (; row + (SCAN_UNROLL - 1) * stride < nrows; row += SCAN_UNROLL * stride) {
+      uint4 v[SCAN_UNROLL];
+#pragma unroll
+      for (int u = 0; u < SCAN_UNROLL; ++u) v[u] = __ldcg(base + (size_t)(radd + rmul * (row + u * stride)) * Kq);
+#pragma unroll
+      for (int u = 0; u < SCAN_UNROLL; ++u) fold_in(v[u], radd + rmul * (row + u * stride));
+    }
+    for (; row < nrows; row += stride) fold_in(__ldcg(base + (size_t)(radd + rmul * row) * Kq), radd + rmul * row);
+    if (a0 >> 32) atomicMax(&sArg[4 * q + 0], a0);
+    if (a1 >> 32) atomicMax(&sArg[4 * q + 1], a1);
+    if (a2 >> 32) atomicMax(&sArg[4 * q + 2], a2);
+    if (a3 >> 32) atomicMax(&sArg[4 * q + 3], a3);
+  }
+  __syncthreads();
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    const unsigned long long v = sArg[mu];
+    if ((v >> 32) && v > __ldcg(&d.colarg[mu])) atomicMax(&d.colarg[mu], v);
+  }
+  // the CTA that finishes last owns the result
+  __shared__ unsigned s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&d.ctl->scan_ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x) {
+    const unsigned long long v = __ldcg(&d.colarg[mu]);
+    const uint32_t m = (uint32_t)(v >> 32);
+    d.colarg[mu] = 0ull;
+    if (!d.cand_unc[mu]) continue;  // certified by its list (k_eval wrote the same maximum)
+    d.cand_unc[mu] = 0u;
+    d.colmax[p * d.Kp + mu] = m;
+    // No untouched row exceeds m, so m is a valid floor (touched rows are checked against it by k_apply).
+    // A rebuild starts k_collect's threshold from 0.9 m instead.
+    d.cand_floor[mu] = rebuild ? __float_as_uint(0.9f * __uint_as_float(m)) : m;
+    if (m) {
+      const int row = (int)(uint32_t)v;
+      int n = min(d.cand_n[mu], CAND_CAP);
+      bool have = false;
+      for (int j = 0; j < n; ++j) have |= (d.cand_rows[(size_t)mu * CAND_CAP + j] == row);
+      if (!have) {
+        // a full list gives up one of its rows: every listed untouched row is <= m, the new floor, and a
+        // listed touched row is checked again when k_apply writes its new weight
+        const int slot = (n < CAND_CAP) ? n : (int)((d.ctl->tick + local + (unsigned)mu) % CAND_CAP);
+        d.cand_rows[(size_t)mu * CAND_CAP + slot] = row;
+        d.cand_n[mu] = (n < CAND_CAP) ? n + 1 : CAND_CAP;
+      } else {
+        d.cand_n[mu] = n;
+      }
+    }
+  }
+  if (threadIdx.x == 0) {
+    d.ctl->scan_ticket = 0u;
+    d.ctl->need_scan = 0u;
+    d.ctl->scans_run += 1u;
+  }
+  __syncthreads();
+  if (d.shard) publish_partial(d, local, p);
+}
+
+// Rebuild, second pass (after k_colscan left every unit's floor at 0.9 of its maximum and listed the
+// arg-max row): every untouched row above its unit's floor is listed; when a list is full the floor
+// rises to the row that did not fit, so the bound stays true.
+__global__ void __launch_bounds__(SCAN_THREADS, 2) k_collect(Dev d) {
+  grid_dependency_wait();
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;
+  const int Kq = d.Kq;
+  const int groups = SCAN_THREADS / Kq;
+  const int g = threadIdx.x / Kq, q = threadIdx.x - g * Kq;
+  if (g >= groups) return;
+  const int stride = gridDim.x * groups;
+  const uint4* __restrict__ base = reinterpret_cast<const uint4*>(d.wt) + q;
+  const int rmul = d.shard ? d.G : 1, radd = d.shard ? d.rank : 0;
+  const int nrows = d.shard ? (d.N - d.rank + d.G - 1) / d.G : d.N;
+  uint32_t fl[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) fl[c] = __ldcg(d.cand_floor + min(4 * q + c, d.Kp - 1));
+  auto consider = [&](uint32_t bits, int c, int row) {
+    const uint32_t u = bits & ABS_MASK;
+    const int mu = 4 * q + c;
+    if (u > TAG_BASE || u <= fl[c] || mu >= d.K) return;
+    if (u <= (fl[c] = __ldcg(d.cand_floor + mu))) return;  // the floor may have risen meanwhile
+    const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+    for (int j = 0; j < n; ++j)
+      if (__ldcg(d.cand_rows + (size_t)mu * CAND_CAP + j) == row) return;  // the arg-max row is there already
+    const int slot = atomicAdd(d.cand_n + mu, 1);
+    if (slot < CAND_CAP) d.cand_rows[(size_t)mu * CAND_CAP + slot] = row;
+    else atomicMax(d.cand_floor + mu, u);
+  };
+  for (int row = blockIdx.x * groups + g; row < nrows; row += SCAN_UNROLL * stride) {
+    uint4 v[SCAN_UNROLL];
+#pragma unroll
+    for (int u = 0; u < SCAN_UNROLL; ++u) {
+      const int rr = row + u * stride;
+      v[u] = __ldcg(base + (size_t)(radd + rmul * (rr < nrows ? rr : row)) * Kq);
+    }
+#pragma unroll
+    for (int u = 0; u < SCAN_UNROLL; ++u) {
+      const int rr = row + u * stride;
+      if (rr >= nrows) continue;
+      const int r = radd + rmul * rr;
+      consider(v[u].x, 0, r);
+      consider(v[u].y, 1, r);
+      consider(v[u].z, 2, r);
+      consider(v[u].w, 3, r);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // T12 + T13.  Every CTA derives nc and the step size from the K column maxima
 // (cheap) and then walks its share of the slots: owners write
 //   wt = parked + cnt * f_i * s / (n * alpha')     with alpha' = alpha * (1 - s*X)
@@ -1329,9 +1656,8 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
 
   float dense = 0.f;
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
-    double X = 0.0;
-    int n = 0;
-    if (mu < d.K) unit_stats(d, p, (uint32_t)(d.ctl->tick + local + 1), mu, &X, &n);
+    const double X = d.stat_x[p * d.Kp + mu];  // left by the scan kernel
+    const int n = d.stat_n[p * d.Kp + mu];
     sX[mu] = X;
     sN[mu] = n;
     if (n > 0) dense = fmaxf(dense, (float)(fabs(X * alpha[mu]) * (double)__uint_as_float(d.colmax[p * d.Kp + mu])));
@@ -1424,7 +1750,20 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
         d.rec[k].w = 0u;  // the slot is a hole again until it is claimed anew
         if (cp[u]) d.cnt[k] = 0;
         if (cn[u]) d.cntn[k] = 0;
-        vmax = max(vmax, __float_as_uint(fabsf(v)));
+        const uint32_t vb = __float_as_uint(fabsf(v));
+        vmax = max(vmax, vb);
+        if (d.use_cand && vb > __ldcg(d.cand_floor + mu)) {
+          // the new weight rises above its unit's floor: list its row, or lift the floor when the list is full
+          const int irow = (int)(r[u].x / (uint32_t)d.Kp);
+          const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+          bool have = false;
+          for (int j = 0; j < n; ++j) have |= (__ldcg(d.cand_rows + (size_t)mu * CAND_CAP + j) == irow);
+          if (!have) {
+            const int slot = atomicAdd(d.cand_n + mu, 1);
+            if (slot < CAND_CAP) d.cand_rows[(size_t)mu * CAND_CAP + slot] = irow;
+            else atomicMax(d.cand_floor + mu, vb);
+          }
+        }
       }
     }
   }
@@ -1793,6 +2132,8 @@ struct fv_trainer {
   uint4* d_rec = nullptr;
   uint32_t* d_colmax = nullptr;
   uint32_t* d_ncb = nullptr;
+  double* d_stat_x = nullptr;
+  int32_t* d_stat_n = nullptr;
   StepCtl* d_ctl = nullptr;
   float* d_log = nullptr;
   size_t log_cap = 0;
@@ -1800,6 +2141,13 @@ struct fv_trainer {
   unsigned long long ticks = 0;  // host copy of StepCtl::tick
   float delta_now = 0.f;         // anti-Hebbian strength used by the next run_* call
   int tag_un = 1;
+  unsigned long long matrix_scans = 0;  // steps in which the column maxima came from a pass over the matrix
+  bool cand_dirty = true;  // the candidate lists of the column maxima do not describe the current weights
+  int32_t* d_cand_rows = nullptr;
+  int32_t* d_cand_n = nullptr;
+  uint32_t* d_cand_floor = nullptr;
+  uint32_t* d_cand_unc = nullptr;
+  unsigned long long* d_colarg = nullptr;
   int tag_own_u = 1, tag_own_grid = 0;  // sharded update: slots per thread and CTAs of the owner-only tagging kernel
   int fwd_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
   size_t fwd_smem = 0, scan_smem = 0, apply_smem = 0;
@@ -1875,6 +2223,7 @@ int fold_weights(fv_trainer* tr, int local) {
   k_reset_alpha<<<4, 256, 0, tr->stream>>>(tr->d);
   FV_CUDA(cudaGetLastError());
   tr->steps_since_fold = 0;
+  tr->cand_dirty = true;  // every weight changed: the candidate lists are rebuilt in the next step
   return FV_OK;
 }
 
@@ -1944,8 +2293,20 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     }
     *launches += 1;
   } else if (phase == 2) {
-    launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
-    *launches += 1;
+    if (d.use_cand) {
+      const int rebuild = tr->cand_dirty ? 1 : 0;
+      launch_pdl(k_eval, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx, rebuild);
+      launch_pdl(k_colscan, tr->scan_grid, SCAN_THREADS, (size_t)d.Kp * sizeof(unsigned long long), tr->stream, d, local, rebuild);
+      *launches += 2;
+      if (rebuild) {
+        launch_pdl(k_collect, tr->scan_grid, SCAN_THREADS, (size_t)0, tr->stream, d);
+        *launches += 1;
+        tr->cand_dirty = false;
+      }
+    } else {
+      launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
+      *launches += 1;
+    }
   } else {
     launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
     FV_CUDA(cudaGetLastError());
@@ -2096,6 +2457,7 @@ int loop_end(fv_trainer* tr, StepLoop& L, float* nc_out, float* scale_out, fv_ru
   StepCtl h;
   FV_CUDA(cudaMemcpy(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost));
   const uint32_t dev_err = h.error;
+  tr->matrix_scans += tr->d.use_cand ? h.scans_run : nsteps;
   const unsigned long long timed = nsteps - L.timed_from;
   if (getenv("FV_STAMPS")) {
     fprintf(stderr, "[rank %d] per step (us): other %.1f forward %.1f xx %.1f wait %.1f tag %.1f scan %.1f apply %.1f fold %.1f\n", tr->d.rank,
@@ -2172,7 +2534,7 @@ void free_all(fv_trainer* tr) {
     if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
-                  tr->d_mail, tr->d_peer_table, tr->d_xx_acc, tr->d_xx_wins, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_ctl,
+                  tr->d_mail, tr->d_peer_table, tr->d_xx_acc, tr->d_xx_wins, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_stat_x, tr->d_stat_n, tr->d_cand_rows, tr->d_cand_n, tr->d_cand_floor, tr->d_cand_unc, tr->d_colarg, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1], tr->d_idx_local[0], tr->d_idx_local[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -2273,6 +2635,27 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   FV_TRY(dev_alloc(&tr->d_rec, E));
   FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_ncb, 2));
+  FV_TRY(dev_alloc(&tr->d_cand_rows, (size_t)d.Kp * CAND_CAP));
+  FV_TRY(dev_alloc(&tr->d_cand_n, (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_cand_floor, (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_cand_unc, (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_colarg, (size_t)d.Kp));
+  FV_CUDA(cudaMemsetAsync(tr->d_cand_rows, 0, (size_t)d.Kp * CAND_CAP * sizeof(int32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_cand_n, 0, (size_t)d.Kp * sizeof(int32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_cand_floor, 0xff, (size_t)d.Kp * sizeof(uint32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_cand_unc, 0, (size_t)d.Kp * sizeof(uint32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_colarg, 0, (size_t)d.Kp * sizeof(unsigned long long), tr->stream));
+  d.cand_rows = tr->d_cand_rows;
+  d.cand_n = tr->d_cand_n;
+  d.cand_floor = tr->d_cand_floor;
+  d.cand_unc = tr->d_cand_unc;
+  d.colarg = tr->d_colarg;
+  {
+    const char* e = getenv("FV_COLMAX");  // "scan": stream the matrix in every step instead of keeping candidate lists
+    d.use_cand = (e && strcmp(e, "scan") == 0) ? 0 : 1;
+  }
+  FV_TRY(dev_alloc(&tr->d_stat_x, 2 * (size_t)d.Kp));
+  FV_TRY(dev_alloc(&tr->d_stat_n, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_ctl, 1));
   FV_CUDA(cudaMemsetAsync(tr->d_cnt, 0, E * sizeof(int32_t), tr->stream));
   // a record whose last word is zero is a hole; k_apply returns every used record to that state, so the
@@ -2293,6 +2676,8 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.rec = tr->d_rec;
   d.colmax = tr->d_colmax;
   d.ncb = tr->d_ncb;
+  d.stat_x = tr->d_stat_x;
+  d.stat_n = tr->d_stat_n;
   d.ctl = tr->d_ctl;
   k_reset_alpha<<<4, 256, 0, tr->stream>>>(d);
   FV_CUDA(cudaGetLastError());
@@ -2581,6 +2966,7 @@ int fv_trainer_set_weights(fv_trainer* tr, const float* w_kn) {
   cudaFree(tmp);
   FV_CUDA(e);
   tr->steps_since_fold = 0;
+  tr->cand_dirty = true;
   tr->have_weights = true;
   return FV_OK;
 }
@@ -2888,6 +3274,12 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
     }
     return FV_OK;
   }
+  if (strcmp(key, "colmax_lists") == 0) {
+    FV_REQUIRE(value == 0.0 || value == 1.0, FV_ERR_INVALID, "colmax_lists must be 0 or 1, got %g", value);
+    tr->d.use_cand = (int)value;
+    tr->cand_dirty = true;
+    return FV_OK;
+  }
   if (strcmp(key, "shard") == 0) {
     FV_REQUIRE(value == 0.0 || value == 1.0, FV_ERR_INVALID, "shard must be 0 or 1, got %g", value);
     FV_REQUIRE(value == 0.0 || (tr->comm_mode == 2 && !tr->d.has_delta), FV_ERR_STATE,
@@ -2991,11 +3383,42 @@ static int run_group(fv_trainer* const* trs, int n, unsigned long long first_ste
       L[r].timed_from = timed_from;
       FV_TRY(loop_begin(trs[r], L[r]));
     }
+    // FV_LOCKSTEP_TIMES=1: time every phase of rank 0 with an event pair (the ranks run one after the other
+    // here, so these are a rank's own kernel times with nothing to wait for); printed to stderr
+    const bool timing = getenv("FV_LOCKSTEP_TIMES") != nullptr;
+    std::vector<cudaEvent_t> evs;
     for (unsigned long long k = 0; k < nsteps; ++k) {
       for (int r = 0; r < n; ++r) FV_TRY(loop_stage(trs[r], L[r], k));
       for (int ph = 0; ph < STEP_PHASES; ++ph)
-        for (int r = 0; r < n; ++r) FV_TRY(enqueue_phase(trs[r], ph, (int)k, L[r].idx, &L[r].launches));
+        for (int r = 0; r < n; ++r) {
+          const bool mark = timing && r == 0 && k >= timed_from;
+          if (mark) {
+            evs.emplace_back();
+            FV_CUDA(cudaEventCreate(&evs.back()));
+            FV_CUDA(cudaEventRecord(evs.back(), trs[0]->stream));
+          }
+          FV_TRY(enqueue_phase(trs[r], ph, (int)k, L[r].idx, &L[r].launches));
+          if (mark) {
+            evs.emplace_back();
+            FV_CUDA(cudaEventCreate(&evs.back()));
+            FV_CUDA(cudaEventRecord(evs.back(), trs[0]->stream));
+          }
+        }
       for (int r = 0; r < n; ++r) FV_TRY(loop_after_step(trs[r], L[r], k));
+    }
+    if (timing && !evs.empty()) {
+      FV_CUDA(cudaStreamSynchronize(trs[0]->stream));
+      double sum[STEP_PHASES] = {0};
+      for (size_t e = 0; e + 1 < evs.size(); e += 2) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, evs[e], evs[e + 1]);
+        sum[(e / 2) % STEP_PHASES] += ms;
+      }
+      const double steps_timed = (double)(evs.size() / 2 / STEP_PHASES);
+      fprintf(stderr, "[lockstep, rank 0 alone] us per step: forward %.1f exchange %.1f tag %.1f scan %.1f apply %.1f\n",
+              sum[0] * 1e3 / steps_timed, sum[1] * 1e3 / steps_timed, sum[2] * 1e3 / steps_timed, sum[3] * 1e3 / steps_timed,
+              sum[4] * 1e3 / steps_timed);
+      for (cudaEvent_t e : evs) cudaEventDestroy(e);
     }
     int rc = FV_OK;
     for (int r = 0; r < n; ++r) {
@@ -3042,6 +3465,15 @@ int fv_trainer_last_packets(fv_trainer* tr, int32_t* winners, float* xx) {
   FV_REQUIRE(tr, FV_ERR_INVALID, "fv_trainer_last_packets: NULL trainer");
   FV_REQUIRE(tr->ticks > 0, FV_ERR_STATE, "no step has run yet");
   return read_packets(tr, winners, xx);
+}
+
+int fv_trainer_get_counter(fv_trainer* tr, const char* key, uint64_t* value) {
+  FV_REQUIRE(tr && key && value, FV_ERR_INVALID, "fv_trainer_get_counter: NULL argument");
+  if (strcmp(key, "matrix_scans") == 0) {
+    *value = tr->matrix_scans;
+    return FV_OK;
+  }
+  return fv::fail(FV_ERR_INVALID, "fv_trainer_get_counter: unknown counter %s", key);
 }
 
 int fv_trainer_comm_mode(fv_trainer* tr, int* mode) {

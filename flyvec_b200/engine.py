@@ -178,6 +178,12 @@ class Trainer:
         """Tuning knobs that change no result: ``spin_limit``, ``tag_variant``."""
         check(_lib.lib().fv_trainer_set_option(self._h, key.encode(), float(value)))
 
+    def counter(self, key: str) -> int:
+        """Counters since creation, e.g. ``matrix_scans``."""
+        v = C.c_uint64(0)
+        check(_lib.lib().fv_trainer_get_counter(self._h, key.encode(), C.byref(v)))
+        return v.value
+
     @property
     def comm_mode(self) -> int:
         """0 = single rank, 1 = NCCL all-gather per step, 2 = peer-memory mailboxes."""
