@@ -1339,10 +1339,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 // the unit's floor to the maximum found and lists that row.  k_apply keeps the bound true: a touched
 // weight whose new magnitude exceeds its unit's floor is listed (or raises the floor when the list is
 // full).  After a fold or new weights the lists are rebuilt: k_eval marks every unit uncertain,
-// k_colscan finds the maxima, k_collect lists every untouched row above 0.9 of its unit's maximum.
+// k_colscan finds the maxima, k_collect lists every untouched row above CAND_THETA of its unit's maximum.
 // With the sharded update a rank keeps lists for the rows it owns.
 // ---------------------------------------------------------------------------
-constexpr int CAND_CAP = 32;
+constexpr int CAND_CAP = 64;
+constexpr float CAND_THETA = 0.85f;  // a rebuild lists the untouched rows above this fraction of their unit's maximum
 
 // The first half of k_scan (combine, records, exact D at the touched positions) plus the list query.
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, const int32_t* __restrict__ idx, int rebuild) {
@@ -1558,8 +1559,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, i
     d.cand_unc[mu] = 0u;
     d.colmax[p * d.Kp + mu] = m;
     // No untouched row exceeds m, so m is a valid floor (touched rows are checked against it by k_apply).
-    // A rebuild starts k_collect's threshold from 0.9 m instead.
-    d.cand_floor[mu] = rebuild ? __float_as_uint(0.9f * __uint_as_float(m)) : m;
+    // A rebuild starts k_collect's threshold from CAND_THETA * m instead.
+    d.cand_floor[mu] = rebuild ? __float_as_uint(CAND_THETA * __uint_as_float(m)) : m;
     if (m) {
       const int row = (int)(uint32_t)v;
       int n = min(d.cand_n[mu], CAND_CAP);
@@ -1585,7 +1586,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, i
   if (d.shard) publish_partial(d, local, p);
 }
 
-// Rebuild, second pass (after k_colscan left every unit's floor at 0.9 of its maximum and listed the
+// Rebuild, second pass (after k_colscan left every unit's floor at CAND_THETA of its maximum and listed the
 // arg-max row): every untouched row above its unit's floor is listed; when a list is full the floor
 // rises to the row that did not fit, so the bound stays true.
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_collect(Dev d) {
