@@ -1346,28 +1346,95 @@ constexpr int CAND_CAP = 64;
 constexpr float CAND_THETA = 0.85f;  // a rebuild lists the untouched rows above this fraction of their unit's maximum
 
 // The first half of k_scan (combine, records, exact D at the touched positions) plus the list query.
-__global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, const int32_t* __restrict__ idx, int rebuild) {
+// The two jobs are chains of dependent memory accesses, so they run side by side in different CTAs:
+// the first `qblocks` CTAs query the lists (one warp per unit), the others walk the records.
+__global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, const int32_t* __restrict__ idx, int rebuild, int qblocks) {
   grid_dependency_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_SCAN);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
+  const int p = (int)((d.ctl->tick + local) & 1);
+  const int lane = threadIdx.x & 31;
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+
+  if ((int)blockIdx.x < qblocks) {
+    // ---- the candidate lists: one warp per unit, a lane per candidate --------------------------
+    const int mu = blockIdx.x * (SCAN_THREADS / 32) + (threadIdx.x >> 5);
+    if (mu >= d.K) return;
+    if (rebuild) {
+      if (lane == 0) {
+        d.cand_unc[mu] = 1u;
+        d.cand_n[mu] = 0;
+        d.ctl->need_scan = 1u;
+      }
+      return;
+    }
+    // candidates first: their loads do not depend on anything
+    const uint32_t* __restrict__ wbits = reinterpret_cast<const uint32_t*>(d.wt);
+    const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+    const uint32_t floor_bits = __ldcg(d.cand_floor + mu);
+    int row[CAND_CAP / 32];
+#pragma unroll
+    for (int t = 0; t < CAND_CAP / 32; ++t) row[t] = (lane + 32 * t < n) ? __ldcg(d.cand_rows + (size_t)mu * CAND_CAP + lane + 32 * t) : -1;
+    // is the unit active on any rank?  (lane r looks at rank r's xx; a word still on its way is waited for)
+    uint32_t xbits = 0u;
+    if (lane < d.G) {
+      const unsigned long long* word = packet(d, p, lane) + d.XO + mu;
+      const unsigned long long w = load_relaxed_sys64(word);
+      xbits = ((uint32_t)(w >> 32) == seq) ? (uint32_t)w : pk_read(d, word, seq, 0u);
+    }
+    const bool active = __any_sync(FULL, lane < d.G && __uint_as_float(xbits) != 0.f);
+    if (!active) return;  // no update for this unit: its maximum is not needed
+    uint32_t m = 0u;
+#pragma unroll
+    for (int t = 0; t < CAND_CAP / 32; ++t) {
+      if (row[t] < 0) continue;
+      const uint32_t w = __ldcg(wbits + (size_t)row[t] * d.Kp + mu) & ABS_MASK;
+      m = max(m, w > TAG_BASE ? 0u : w);  // a tag: touched in this step, its exact D is taken at the record
+    }
+    m = warp_max_u32(m);
+    if (lane == 0) {
+      if (m >= floor_bits) {
+        d.colmax[p * d.Kp + mu] = m;
+      } else {
+        d.cand_unc[mu] = 1u;
+        d.ctl->need_scan = 1u;
+      }
+    }
+    return;
+  }
+
+  // ---- the records: exact D at the touched positions -------------------------------------------
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
   int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
   uint32_t* sBad = reinterpret_cast<uint32_t*>(sN + d.Kp) + d.Kp;  // same layout as k_scan (its column maxima lie between)
-  const int p = (int)((d.ctl->tick + local) & 1);
-  const int lane = threadIdx.x & 31;
   const double* __restrict__ alpha = d.alpha + p * d.Kp;
   __shared__ int s_any_bad;
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nthreads = (gridDim.x - qblocks) * blockDim.x;
+  const int e0 = (blockIdx.x - qblocks) * blockDim.x + threadIdx.x;
+  constexpr int TS = 4;
+  int cp[TS], cn[TS];
+  uint4 rc[TS];
+  auto load_batch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < TS; ++u) {
+      const int k = k0 + u * nthreads;
+      cp[u] = (k < nrec) ? d.cnt[k] : 0;
+      cn[u] = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
+      rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  load_batch(e0);  // in flight while the combine below polls the packets
   if (threadIdx.x == 0) s_any_bad = 0;
   __syncthreads();
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
     if (mu < d.K) unit_stats(d, p, seq, mu, &X, &n);  // waits (bounded) for a peer's xx still on its way
     sC[mu] = X * alpha[mu];
     sN[mu] = n;
-    if (blockIdx.x == 0) {
+    if ((int)blockIdx.x == qblocks) {  // the later kernels take the combine from here
       d.stat_x[p * d.Kp + mu] = X;
       d.stat_n[p * d.Kp + mu] = n;
     }
@@ -1376,10 +1443,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
     if (bad) s_any_bad = 1;
   }
   __syncthreads();
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
-  const int nthreads = gridDim.x * blockDim.x;
-  const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
   if (s_any_bad) {
+    // some rank's windows for a unit do not count although the unit is active elsewhere: take them
+    // out of this thread's records before anybody (here or in k_apply) reads the counts
     const unsigned long long* packet0 = packet(d, p, 0);
     for (int k = e0; k < nrec; k += nthreads) {
       const uint4 r = d.rec[k];
@@ -1391,55 +1457,12 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
       if (c.x) d.cnt[k] -= c.x;
       if (c.y) d.cntn[k] -= c.y;
     }
+    load_batch(e0);  // the counts have changed
   }
-
-  // the candidate lists: one warp per unit, a lane per candidate
-  {
-    const int warp = (blockIdx.x * SCAN_THREADS + threadIdx.x) >> 5, nwarps = (gridDim.x * SCAN_THREADS) >> 5;
-    const uint32_t* __restrict__ wbits = reinterpret_cast<const uint32_t*>(d.wt);
-    for (int mu = warp; mu < d.K; mu += nwarps) {
-      if (rebuild) {
-        if (lane == 0) {
-          d.cand_unc[mu] = 1u;
-          d.cand_n[mu] = 0;
-          d.ctl->need_scan = 1u;
-        }
-        continue;
-      }
-      if (sN[mu] == 0) continue;  // no update for this unit: its maximum is not needed
-      const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
-      uint32_t m = 0u;
-      for (int j = lane; j < n; j += 32) {
-        const int row = __ldcg(d.cand_rows + (size_t)mu * CAND_CAP + j);
-        const uint32_t w = __ldcg(wbits + (size_t)row * d.Kp + mu) & ABS_MASK;
-        m = max(m, w > TAG_BASE ? 0u : w);  // a tag: touched in this step, its exact D is taken at the record
-      }
-      m = warp_max_u32(m);
-      if (lane == 0) {
-        if (m >= __ldcg(d.cand_floor + mu)) {
-          d.colmax[p * d.Kp + mu] = m;
-        } else {
-          d.cand_unc[mu] = 1u;
-          d.ctl->need_scan = 1u;
-        }
-      }
-    }
-  }
-
-  // exact D at the touched positions
   const float delta = d.ctl->delta;
   uint32_t tmax = 0u;
-  constexpr int TS = 4;
   for (int k0 = e0; k0 < nrec; k0 += TS * nthreads) {
-    int cp[TS], cn[TS];
-    uint4 rc[TS];
-#pragma unroll
-    for (int u = 0; u < TS; ++u) {
-      const int k = k0 + u * nthreads;
-      cp[u] = (k < nrec) ? d.cnt[k] : 0;
-      cn[u] = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
-      rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
-    }
+    if (k0 != e0) load_batch(k0);
 #pragma unroll
     for (int u = 0; u < TS; ++u) {
       const int k = k0 + u * nthreads;
@@ -1649,6 +1672,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sX = reinterpret_cast<double*>(smem_raw);  // mean xx over active ranks, later s / (n * alpha')
   int* sN = reinterpret_cast<int*>(sX + d.Kp);
+  uint32_t* sFloor = reinterpret_cast<uint32_t*>(sN + d.Kp);  // the units' candidate floors as this kernel found them
   __shared__ float sRed[8];
   __shared__ float sScale;
   const int p = (int)((d.ctl->tick + local) & 1);
@@ -1659,6 +1683,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     const double X = d.stat_x[p * d.Kp + mu];  // left by the scan kernel
     const int n = d.stat_n[p * d.Kp + mu];
+    sFloor[mu] = d.use_cand ? __ldcg(d.cand_floor + mu) : 0xffffffffu;  // final since the previous kernel; it can only rise here
     sX[mu] = X;
     sN[mu] = n;
     if (n > 0) dense = fmaxf(dense, (float)(fabs(X * alpha[mu]) * (double)__uint_as_float(d.colmax[p * d.Kp + mu])));
@@ -1753,7 +1778,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
         if (cn[u]) d.cntn[k] = 0;
         const uint32_t vb = __float_as_uint(fabsf(v));
         vmax = max(vmax, vb);
-        if (d.use_cand && vb > __ldcg(d.cand_floor + mu)) {
+        if (vb > sFloor[mu] && vb > __ldcg(d.cand_floor + mu)) {
           // the new weight rises above its unit's floor: list its row, or lift the floor when the list is full
           const int irow = (int)(r[u].x / (uint32_t)d.Kp);
           const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
@@ -2296,7 +2321,8 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
   } else if (phase == 2) {
     if (d.use_cand) {
       const int rebuild = tr->cand_dirty ? 1 : 0;
-      launch_pdl(k_eval, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx, rebuild);
+      const int qblocks = (d.K + SCAN_THREADS / 32 - 1) / (SCAN_THREADS / 32);  // a warp per unit
+      launch_pdl(k_eval, tr->scan_grid + qblocks, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx, rebuild, qblocks);
       launch_pdl(k_colscan, tr->scan_grid, SCAN_THREADS, (size_t)d.Kp * sizeof(unsigned long long), tr->stream, d, local, rebuild);
       *launches += 2;
       if (rebuild) {
@@ -2686,7 +2712,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   // launch geometry: whole multiples of the SM count
   tr->fwd_smem = (size_t)d.Kp * sizeof(float);
   tr->scan_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + 2 * sizeof(uint32_t));
-  tr->apply_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int));
+  tr->apply_smem = (size_t)d.Kp * (sizeof(double) + sizeof(int) + sizeof(uint32_t));
   int fwd_bps = 0;
   cudaError_t oerr = cudaSuccess;
   FV_DISPATCH_NT(tr->NT, forward_occupancy, &fwd_bps, tr->fwd_smem, &oerr);
