@@ -32,6 +32,7 @@
 //                                                               cu_special_reduction.cu:316-354)
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -64,8 +65,8 @@ struct StepCtl {
   uint32_t out_count;     // (unused)
   uint32_t pad;
   uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
-  uint32_t need_scan;     // k_eval found a unit whose maximum its candidate list cannot certify: k_colscan must stream
-  uint32_t scans_run;     // steps of this call in which k_colscan streamed the matrix
+  uint32_t need_scan;     // (unused)
+  uint32_t scans_run;     // units whose column k_eval had to read in this call (their candidates were all touched)
   // Device-side phase clock: every step kernel's first thread charges the time since the previous
   // mark to the phase that was running and names its own.  No events, so the launches stay chained.
   unsigned long long t_mark;
@@ -1334,16 +1335,46 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
 //                                                         has |wt| <= floor (bit patterns compare like floats).
 // k_eval reads the candidates' current weights -- a tagged one was touched and is skipped -- and takes
 // their maximum m.  If m >= floor no row outside the list can beat it: m IS the maximum over untouched
-// rows, exactly.  Otherwise (every strong candidate touched in this step) the unit is marked uncertain
-// and k_colscan streams the matrix as k_scan does, tracking the arg-max row; its last CTA then lowers
-// the unit's floor to the maximum found and lists that row.  k_apply keeps the bound true: a touched
-// weight whose new magnitude exceeds its unit's floor is listed (or raises the floor when the list is
-// full).  After a fold or new weights the lists are rebuilt: k_eval marks every unit uncertain,
-// k_colscan finds the maxima, k_collect lists every untouched row above CAND_THETA of its unit's maximum.
+// rows, exactly.  Otherwise (every strong candidate touched in this step) the CTA that queried the unit
+// reads the unit's whole column, which gives the exact maximum and its row, lowers the floor to that
+// maximum and lists the row.  k_apply keeps the bound true: a touched weight whose new magnitude
+// exceeds its unit's floor is listed (or raises the floor when the list is full).  After a fold or
+// new weights the lists are rebuilt in the next step by two passes over the matrix: k_colscan finds
+// every unit's maximum, k_collect lists every untouched row above CAND_THETA of it.
 // With the sharded update a rank keeps lists for the rows it owns.
 // ---------------------------------------------------------------------------
 constexpr int CAND_CAP = 64;
 constexpr float CAND_THETA = 0.85f;  // a rebuild lists the untouched rows above this fraction of their unit's maximum
+
+// Sharded update: this rank's partial normaliser (its records and the columns of its rows) and the length
+// of its entry list go to every rank, each in one flagged word.  Run by one CTA once the maxima are final.
+__device__ __forceinline__ void publish_partial(const Dev& d, int local, int p) {
+  __shared__ float s_pub[SCAN_THREADS / 32];
+  const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  float dense = 0.f;
+  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x) {
+    const int n = __ldcg(d.stat_n + p * d.Kp + mu);
+    if (n > 0)
+      dense = fmaxf(dense, (float)(fabs(__ldcg(d.stat_x + p * d.Kp + mu) * alpha[mu]) * (double)__uint_as_float(__ldcg(&d.colmax[p * d.Kp + mu]))));
+  }
+  dense = warp_max(dense);
+  if ((threadIdx.x & 31) == 0) s_pub[threadIdx.x >> 5] = dense;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float nc = __uint_as_float(__ldcg(&d.ncb[p]));
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) nc = fmaxf(nc, s_pub[w]);
+    s_pub[0] = nc;
+  }
+  __syncthreads();
+  if (threadIdx.x < d.G) {
+    const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
+    const unsigned nrec = min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+    unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
+    store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_pub[0]));
+    unsigned long long* outw = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
+    store_relaxed_sys64(outw + p * MAX_RANKS + d.rank, (seq << 32) | nrec);
+  }
+}
 
 // The first half of k_scan (combine, records, exact D at the touched positions) plus the list query.
 // The two jobs are chains of dependent memory accesses, so they run side by side in different CTAs:
@@ -1358,51 +1389,103 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
 
   if ((int)blockIdx.x < qblocks) {
     // ---- the candidate lists: one warp per unit, a lane per candidate --------------------------
-    const int mu = blockIdx.x * (SCAN_THREADS / 32) + (threadIdx.x >> 5);
-    if (mu >= d.K) return;
-    if (rebuild) {
+    constexpr int QW = SCAN_THREADS / 32;
+    __shared__ int s_unc[QW];
+    const int wic = threadIdx.x >> 5;
+    const int mu = blockIdx.x * QW + wic;
+    if (lane == 0) s_unc[wic] = 0;
+    if (mu < d.K && rebuild) {
+      // new weights or a fold: every list starts afresh; k_colscan and k_collect follow in this step
       if (lane == 0) {
         d.cand_unc[mu] = 1u;
         d.cand_n[mu] = 0;
-        d.ctl->need_scan = 1u;
       }
-      return;
-    }
-    // candidates first: their loads do not depend on anything
-    const uint32_t* __restrict__ wbits = reinterpret_cast<const uint32_t*>(d.wt);
-    const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
-    const uint32_t floor_bits = __ldcg(d.cand_floor + mu);
-    int row[CAND_CAP / 32];
+    } else if (mu < d.K) {
+      // candidates first: their loads do not depend on anything
+      const uint32_t* __restrict__ wbits = reinterpret_cast<const uint32_t*>(d.wt);
+      const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+      const uint32_t floor_bits = __ldcg(d.cand_floor + mu);
+      int row[CAND_CAP / 32];
 #pragma unroll
-    for (int t = 0; t < CAND_CAP / 32; ++t) row[t] = (lane + 32 * t < n) ? __ldcg(d.cand_rows + (size_t)mu * CAND_CAP + lane + 32 * t) : -1;
-    // is the unit active on any rank?  (lane r looks at rank r's xx; a word still on its way is waited for)
-    uint32_t xbits = 0u;
-    if (lane < d.G) {
-      const unsigned long long* word = packet(d, p, lane) + d.XO + mu;
-      const unsigned long long w = load_relaxed_sys64(word);
-      xbits = ((uint32_t)(w >> 32) == seq) ? (uint32_t)w : pk_read(d, word, seq, 0u);
-    }
-    const bool active = __any_sync(FULL, lane < d.G && __uint_as_float(xbits) != 0.f);
-    if (!active) return;  // no update for this unit: its maximum is not needed
-    uint32_t m = 0u;
+      for (int t = 0; t < CAND_CAP / 32; ++t) row[t] = (lane + 32 * t < n) ? __ldcg(d.cand_rows + (size_t)mu * CAND_CAP + lane + 32 * t) : -1;
+      // is the unit active on any rank?  (lane r looks at rank r's xx; a word still on its way is waited for)
+      uint32_t xbits = 0u;
+      if (lane < d.G) {
+        const unsigned long long* word = packet(d, p, lane) + d.XO + mu;
+        const unsigned long long w = load_relaxed_sys64(word);
+        xbits = ((uint32_t)(w >> 32) == seq) ? (uint32_t)w : pk_read(d, word, seq, 0u);
+      }
+      const bool active = __any_sync(FULL, lane < d.G && __uint_as_float(xbits) != 0.f);
+      if (active) {  // otherwise no update for this unit: its maximum is not needed
+        uint32_t m = 0u;
 #pragma unroll
-    for (int t = 0; t < CAND_CAP / 32; ++t) {
-      if (row[t] < 0) continue;
-      const uint32_t w = __ldcg(wbits + (size_t)row[t] * d.Kp + mu) & ABS_MASK;
-      m = max(m, w > TAG_BASE ? 0u : w);  // a tag: touched in this step, its exact D is taken at the record
-    }
-    m = warp_max_u32(m);
-    if (lane == 0) {
-      if (m >= floor_bits) {
-        d.colmax[p * d.Kp + mu] = m;
-      } else {
-        d.cand_unc[mu] = 1u;
-        d.ctl->need_scan = 1u;
+        for (int t = 0; t < CAND_CAP / 32; ++t) {
+          if (row[t] < 0) continue;
+          const uint32_t w = __ldcg(wbits + (size_t)row[t] * d.Kp + mu) & ABS_MASK;
+          m = max(m, w > TAG_BASE ? 0u : w);  // a tag: touched in this step, its exact D is taken at the record
+        }
+        m = warp_max_u32(m);
+        if (lane == 0) {
+          if (m >= floor_bits) d.colmax[p * d.Kp + mu] = m;
+          else s_unc[wic] = 1;
+        }
       }
     }
-    return;
-  }
-
+    __syncthreads();
+    // A unit whose strong candidates were all touched in this step: the whole CTA reads the unit's column
+    // (tags as 0), which gives the exact maximum and its row; the floor drops to that maximum -- no
+    // untouched row exceeds it, and k_apply checks every touched one against it -- and the row is listed.
+    for (int w = 0; w < QW; ++w) {
+      if (!s_unc[w]) continue;
+      const int cu = blockIdx.x * QW + w;
+      const uint32_t* __restrict__ col = reinterpret_cast<const uint32_t*>(d.wt) + cu;
+      const int rmul = d.shard ? d.G : 1, radd = d.shard ? d.rank : 0;
+      const int nrows = d.shard ? (d.N - d.rank + d.G - 1) / d.G : d.N;
+      unsigned long long best = 0ull;  // (bits << 32) | row
+      constexpr int RU = 8;
+      for (int r0 = threadIdx.x; r0 < nrows; r0 += RU * SCAN_THREADS) {
+        uint32_t v[RU];
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+          const int r = r0 + u * SCAN_THREADS;
+          v[u] = (r < nrows) ? (__ldcg(col + (size_t)(radd + rmul * r) * d.Kp) & ABS_MASK) : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+          const int r = r0 + u * SCAN_THREADS;
+          if (r < nrows && v[u] <= TAG_BASE) best = max(best, ((unsigned long long)v[u] << 32) | (uint32_t)(radd + rmul * r));
+        }
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) best = max(best, __shfl_xor_sync(FULL, best, o));
+      __shared__ unsigned long long s_best[QW];
+      if (lane == 0) s_best[wic] = best;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        for (int k = 1; k < QW; ++k) best = max(best, s_best[k]);
+        const uint32_t m = (uint32_t)(best >> 32);
+        d.colmax[p * d.Kp + cu] = m;
+        d.cand_floor[cu] = m;
+        if (m) {
+          const int row = (int)(uint32_t)best;
+          const int n = min(d.cand_n[cu], CAND_CAP);
+          bool have = false;
+          for (int j = 0; j < n; ++j) have |= (d.cand_rows[(size_t)cu * CAND_CAP + j] == row);
+          if (!have) {
+            // a full list gives up one of its rows: every listed untouched row is <= m, the new floor, and a
+            // listed touched row is checked again when k_apply writes its new weight
+            const int slot = (n < CAND_CAP) ? n : (int)((d.ctl->tick + local + (unsigned)cu) % CAND_CAP);
+            d.cand_rows[(size_t)cu * CAND_CAP + slot] = row;
+            d.cand_n[cu] = (n < CAND_CAP) ? n + 1 : CAND_CAP;
+          } else {
+            d.cand_n[cu] = n;
+          }
+        }
+        atomicAdd(&d.ctl->scans_run, 1u);
+      }
+      __syncthreads();
+    }
+  } else {
   // ---- the records: exact D at the touched positions -------------------------------------------
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* sC = reinterpret_cast<double*>(smem_raw);        // X*alpha
@@ -1485,48 +1568,27 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
   if (lane == 0 && tmax) atomicMax(&s_tmax, tmax);
   __syncthreads();
   if (threadIdx.x == 0 && s_tmax) atomicMax(&d.ncb[p], s_tmax);  // one global atomic per CTA
+  }  // records
+  if (!d.shard || rebuild) return;  // (a rebuild step publishes from k_colscan, once the maxima exist)
+  // Sharded update: the CTA that finishes last publishes this rank's partial normaliser.
+  __shared__ unsigned s_last_eval;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last_eval = (atomicAdd(&d.ctl->scan_ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!s_last_eval) return;
+  __threadfence();
+  if (threadIdx.x == 0) d.ctl->scan_ticket = 0u;
+  publish_partial(d, local, p);
 }
 
-// Sharded update: this rank's partial normaliser (its records and the columns of its rows) and the length
-// of its entry list go to every rank, each in one flagged word.  Run by one CTA once the maxima are final.
-__device__ __forceinline__ void publish_partial(const Dev& d, int local, int p) {
-  __shared__ float s_pub[SCAN_THREADS / 32];
-  const double* __restrict__ alpha = d.alpha + p * d.Kp;
-  float dense = 0.f;
-  for (int mu = threadIdx.x; mu < d.K; mu += blockDim.x) {
-    const int n = __ldcg(d.stat_n + p * d.Kp + mu);
-    if (n > 0)
-      dense = fmaxf(dense, (float)(fabs(__ldcg(d.stat_x + p * d.Kp + mu) * alpha[mu]) * (double)__uint_as_float(__ldcg(&d.colmax[p * d.Kp + mu]))));
-  }
-  dense = warp_max(dense);
-  if ((threadIdx.x & 31) == 0) s_pub[threadIdx.x >> 5] = dense;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float nc = __uint_as_float(__ldcg(&d.ncb[p]));
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) nc = fmaxf(nc, s_pub[w]);
-    s_pub[0] = nc;
-  }
-  __syncthreads();
-  if (threadIdx.x < d.G) {
-    const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
-    const unsigned nrec = min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
-    unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
-    store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_pub[0]));
-    unsigned long long* outw = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
-    store_relaxed_sys64(outw + p * MAX_RANKS + d.rank, (seq << 32) | nrec);
-  }
-}
-
-// Streams the matrix only when k_eval asked for it: column maxima of |wt| with tags read as 0 and
-// the row of each maximum; the last CTA repairs the lists of the uncertain units.
+// First pass of a rebuild (launched after k_eval in the step that follows new weights or a fold): column
+// maxima of |wt| with tags read as 0 and the row of each maximum; the last CTA starts every unit's list
+// with that row and leaves the floor at CAND_THETA of the maximum for k_collect.
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, int rebuild) {
   grid_dependency_wait();
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;
   const int p = (int)((d.ctl->tick + local) & 1);
-  if (!d.ctl->need_scan) {
-    if (d.shard && blockIdx.x == 0) publish_partial(d, local, p);
-    return;
-  }
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned long long* sArg = reinterpret_cast<unsigned long long*>(smem_raw);  // [Kp] CTA maxima with their rows
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) sArg[mu] = 0ull;
@@ -1602,8 +1664,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, i
   }
   if (threadIdx.x == 0) {
     d.ctl->scan_ticket = 0u;
-    d.ctl->need_scan = 0u;
-    d.ctl->scans_run += 1u;
   }
   __syncthreads();
   if (d.shard) publish_partial(d, local, p);
@@ -2167,7 +2227,8 @@ struct fv_trainer {
   unsigned long long ticks = 0;  // host copy of StepCtl::tick
   float delta_now = 0.f;         // anti-Hebbian strength used by the next run_* call
   int tag_un = 1;
-  unsigned long long matrix_scans = 0;  // steps in which the column maxima came from a pass over the matrix
+  unsigned long long matrix_scans = 0;    // steps in which the column maxima came from a pass over the matrix
+  unsigned long long column_rescans = 0;  // single units whose column was read because their candidates were all touched
   bool cand_dirty = true;  // the candidate lists of the column maxima do not describe the current weights
   int32_t* d_cand_rows = nullptr;
   int32_t* d_cand_n = nullptr;
@@ -2322,13 +2383,15 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     if (d.use_cand) {
       const int rebuild = tr->cand_dirty ? 1 : 0;
       const int qblocks = (d.K + SCAN_THREADS / 32 - 1) / (SCAN_THREADS / 32);  // a warp per unit
-      launch_pdl(k_eval, tr->scan_grid + qblocks, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx, rebuild, qblocks);
-      launch_pdl(k_colscan, tr->scan_grid, SCAN_THREADS, (size_t)d.Kp * sizeof(unsigned long long), tr->stream, d, local, rebuild);
-      *launches += 2;
+      const int rblocks = std::max(tr->scan_grid - qblocks, tr->num_sms);  // one resident wave together with the query CTAs
+      launch_pdl(k_eval, rblocks + qblocks, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx, rebuild, qblocks);
+      *launches += 1;
       if (rebuild) {
+        launch_pdl(k_colscan, tr->scan_grid, SCAN_THREADS, (size_t)d.Kp * sizeof(unsigned long long), tr->stream, d, local, rebuild);
         launch_pdl(k_collect, tr->scan_grid, SCAN_THREADS, (size_t)0, tr->stream, d);
-        *launches += 1;
+        *launches += 2;
         tr->cand_dirty = false;
+        tr->matrix_scans += 1;
       }
     } else {
       launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
@@ -2484,7 +2547,8 @@ int loop_end(fv_trainer* tr, StepLoop& L, float* nc_out, float* scale_out, fv_ru
   StepCtl h;
   FV_CUDA(cudaMemcpy(&h, tr->d_ctl, sizeof(h), cudaMemcpyDeviceToHost));
   const uint32_t dev_err = h.error;
-  tr->matrix_scans += tr->d.use_cand ? h.scans_run : nsteps;
+  if (!tr->d.use_cand) tr->matrix_scans += nsteps;
+  tr->column_rescans += h.scans_run;
   const unsigned long long timed = nsteps - L.timed_from;
   if (getenv("FV_STAMPS")) {
     fprintf(stderr, "[rank %d] per step (us): other %.1f forward %.1f xx %.1f wait %.1f tag %.1f scan %.1f apply %.1f fold %.1f\n", tr->d.rank,
@@ -3498,6 +3562,10 @@ int fv_trainer_get_counter(fv_trainer* tr, const char* key, uint64_t* value) {
   FV_REQUIRE(tr && key && value, FV_ERR_INVALID, "fv_trainer_get_counter: NULL argument");
   if (strcmp(key, "matrix_scans") == 0) {
     *value = tr->matrix_scans;
+    return FV_OK;
+  }
+  if (strcmp(key, "column_rescans") == 0) {
+    *value = tr->column_rescans;
     return FV_OK;
   }
   return fv::fail(FV_ERR_INVALID, "fv_trainer_get_counter: unknown counter %s", key);

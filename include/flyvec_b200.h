@@ -193,8 +193,8 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *   "tag_variant"  1: the scatter bookkeeping claims positions one slot per thread; 2: it first
  *                  deduplicates 1024 slots in shared memory; 0: chosen by the size of a step;
  *   "colmax_lists" 1 (default): the largest untouched weight of every unit comes from a short list of
- *                  candidate rows kept from step to step, and the matrix is only streamed when a list
- *                  cannot certify its maximum; 0: the matrix is streamed in every step (FV_COLMAX=scan
+ *                  candidate rows kept from step to step (a unit whose list cannot certify its maximum
+ *                  has its column read on the spot); 0: the matrix is streamed in every step (FV_COLMAX=scan
  *                  in the environment selects the same);
  *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
  *   "tag_own_slots" slots a thread of the sharded update's tagging kernel takes per round: 1, 2, 4, 8,
@@ -216,8 +216,10 @@ int fv_trainers_run_steps(fv_trainer* const* trs, int32_t n, uint64_t first_step
 int fv_trainers_run_epoch(fv_trainer* const* trs, int32_t n, uint64_t epoch, uint64_t nep, fv_run_stats* stats);
 /* winners[world*batch] and xx[world][K] of the last step as THIS rank received them (parity checks). */
 int fv_trainer_last_packets(fv_trainer* tr, int32_t* winners, float* xx);
-/* Counters of a trainer since its creation: "matrix_scans" = steps whose column maxima needed a pass
- * over the synapse matrix (every step without candidate lists). */
+/* Counters of a trainer since its creation: "matrix_scans" = steps whose column maxima needed passes
+ * over the whole synapse matrix (every step without candidate lists; with them only the step after new
+ * weights or a fold); "column_rescans" = single units whose column had to be read in a step because all
+ * their candidate rows had been touched. */
 int fv_trainer_get_counter(fv_trainer* tr, const char* key, uint64_t* value);
 /* How the ranks exchange their per-step packets (B winners and K floats of xx per rank):
  *   0  single rank / not initialised;
