@@ -988,13 +988,16 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
   }
 }
 
-// Tagging for the sharded update: a rank claims only the positions of the rows it owns
-// (i % G == rank), i.e. about 1/G of a step's slots.  Every thread takes U slots; the loads of
-// each stage (ids, winners, weights) are issued for all U together, so a block round costs the
-// same chain of dependent accesses as one slot per thread does, and one round covers the step.
-// The live slots of a block round are numbered with one prefix sum (one counter bump per round).
-template <int U>
-__global__ void __launch_bounds__(XX_THREADS, 3) k_tag_own(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
+// Tagging with U slots per thread, for steps with more slots than resident threads (several ranks).
+// Every stage is issued for all U slots of a thread before any result is used -- the ids, the winners,
+// the weights, and then the claims themselves: a claim is ONE compare-and-swap whose answer is either
+// the weight that was expected (this slot owns the position and writes the record) or the tag of the
+// slot that got there first (this slot adds its multiplicity to that record's count); no retry is
+// needed, because during this kernel a weight can only turn into a tag.  So a block round costs the
+// same chain of dependent accesses as one slot per thread, and one round covers the step.
+// OWN: the sharded update -- a rank claims only the positions of the rows it owns (i % G == rank).
+template <int U, bool OWN>
+__global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
   grid_dependency_wait();
   const int parity = (int)((d.ctl->tick + local) & 1);
   if ((int)blockIdx.x < xx_ctas) {
@@ -1010,10 +1013,14 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_own(Dev d, int local, con
   const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
   __shared__ uint32_t s_scan[XX_WARPS];
   __shared__ uint32_t s_gbase;
-  const int E = d.G * d.B * d.W;  // the sharded update runs without the anti-Hebbian term: one kind of slot
+  // With delta != 0 every (window, position) contributes twice: +f_i to the first winner's row and
+  // -delta*f_i to the second winner's row (cuda_funcs.cu:665-668).  Virtual slot ev = kind * E + e.
+  const int E = d.G * d.B * d.W;
+  const int EV = E * (1 + d.has_delta);
   constexpr int TAG_BLOCK = U * XX_THREADS;
-  const int nblocks = (E + TAG_BLOCK - 1) / TAG_BLOCK;
+  const int nblocks = (EV + TAG_BLOCK - 1) / TAG_BLOCK;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  uint32_t* __restrict__ wbits = reinterpret_cast<uint32_t*>(d.wt);
   // every rank begins with the blocks of its own windows, whose winners are here already
   const int first_blk = (int)(((long long)nblocks * d.rank) / d.G);
   for (int b0 = blockIdx.x - svc; b0 < nblocks; b0 += gridDim.x - svc) {
@@ -1022,18 +1029,20 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_own(Dev d, int local, con
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-      i[u] = (ev < E) ? step_id(d, idx, ev) : -1;
+      i[u] = (ev < EV) ? step_id(d, idx, ev >= E ? ev - E : ev) : -1;
     }
     const unsigned long long* ww[U];
     unsigned long long w0[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
-      const bool mine = i[u] >= 0 && (int)((uint32_t)i[u] - fdiv((uint32_t)i[u], d.mG, d.sG) * (uint32_t)d.G) == d.rank;
+      bool mine = i[u] >= 0;
+      if (OWN) mine = mine && (int)((uint32_t)i[u] - fdiv((uint32_t)i[u], d.mG, d.sG) * (uint32_t)d.G) == d.rank;
       if (!mine) i[u] = -1;
-      const uint32_t q = fdiv((uint32_t)(mine ? ev : 0), d.mW, d.sW);  // window of the global step
-      const uint32_t r = fdiv(q, d.mB, d.sB);                          // its rank
-      ww[u] = packet(d, parity, (int)r) + (int)(q - r * (uint32_t)d.B);
+      const int kind = (mine && ev >= E) ? 1 : 0;
+      const uint32_t q = fdiv((uint32_t)(mine ? ev - kind * E : 0), d.mW, d.sW);  // window of the global step
+      const uint32_t r = fdiv(q, d.mB, d.sB);                                    // its rank
+      ww[u] = packet(d, parity, (int)r) + kind * d.MO + (int)(q - r * (uint32_t)d.B);
       w0[u] = mine ? load_relaxed_sys64(ww[u]) : 0ull;
     }
     uint32_t pos[U], c0[U];
@@ -1042,10 +1051,11 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_own(Dev d, int local, con
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       int mu = -1;
+      // a peer's winner may still be on its way: the word says so (bounded wait; -1 after a timeout)
       if (i[u] >= 0) mu = ((uint32_t)(w0[u] >> 32) == seq) ? (int)(uint32_t)w0[u] : (int)pk_read(d, ww[u], seq, (uint32_t)-1);
       go[u] = mu >= 0;
       pos[u] = go[u] ? (uint32_t)((size_t)i[u] * d.Kp + mu) : 0u;
-      c0[u] = go[u] ? __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos[u]) : 0u;
+      c0[u] = go[u] ? __ldcg(wbits + pos[u]) : 0u;
       mine_n += go[u] ? 1u : 0u;
     }
     uint32_t incl = mine_n;
@@ -1065,10 +1075,37 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_own(Dev d, int local, con
     }
     if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
     __syncthreads();
-    uint32_t slot = s_gbase + before + incl - mine_n;
+    const uint32_t slot0 = s_gbase + before + incl - mine_n;
+    // the claims of all U slots leave together ...
+    uint32_t prev[U], slot[U];
+    uint32_t nslot = slot0;
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (go[u]) claim_position(d, pos[u], c0[u], slot++, 1u, (uint32_t)E);
+    for (int u = 0; u < U; ++u) {
+      slot[u] = nslot;
+      nslot += go[u] ? 1u : 0u;
+      prev[u] = c0[u];
+      if (go[u] && (c0[u] & ABS_MASK) <= TAG_BASE) prev[u] = atomicCAS(wbits + pos[u], c0[u], TAG_BASE | (slot[u] + 1u));
+    }
+    // ... and their answers are used afterwards
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!go[u]) continue;
+      const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
+      const uint32_t mult = ev >= E ? 0x10000u : 1u;
+      if (prev[u] == c0[u] && (c0[u] & ABS_MASK) <= TAG_BASE) {
+        // this slot owns the position: the weight is parked in its record
+        const int irow = (int)fdiv(pos[u], d.mKp, d.sKp);
+        d.rec[slot[u]] = make_uint4(pos[u], c0[u], __float_as_uint(__ldg(d.f + (irow >= d.V ? irow - d.V : irow))), mult);
+      } else {
+        const uint32_t owner = (prev[u] & 0x007fffffu) - 1u;
+        if ((prev[u] & ABS_MASK) <= TAG_BASE || (prev[u] >> 31) || owner >= (uint32_t)EV) {
+          atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);  // neither the expected weight nor a tag
+        } else {
+          if (mult & 0xffffu) atomicAdd(&d.cnt[owner], 1);
+          if (mult >> 16) atomicAdd(&d.cntn[owner], 1);
+        }
+      }
+    }
     __syncthreads();  // s_scan and s_gbase are reused by the next round
   }
 }
@@ -2235,7 +2272,7 @@ struct fv_trainer {
   uint32_t* d_cand_floor = nullptr;
   uint32_t* d_cand_unc = nullptr;
   unsigned long long* d_colarg = nullptr;
-  int tag_own_u = 1, tag_own_grid = 0;  // sharded update: slots per thread and CTAs of the owner-only tagging kernel
+  int tag_batch_u = 1, tag_batch_grid = 0;  // slots per thread and CTAs of the tagging kernel
   int fwd_grid = 0, tag_grid = 0, scan_grid = 0, apply_grid = 0, entry_grid = 0;
   size_t fwd_smem = 0, scan_smem = 0, apply_smem = 0;
 };
@@ -2366,17 +2403,23 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     const bool fused = single || (tr->comm_mode == 2 && !emulate && !split_exchange);
     const size_t table_smem = tag_table_bytes(tr->tag_un);
     const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
-    const int own_u = d.shard ? tr->tag_own_u : 1;
-    if (own_u > 1) {
-      // sharded and more slots than resident threads: the batched owner-only kernel, one round
-      const int grid = tr->tag_own_grid + xx_ctas + push_ctas;
-      if (own_u == 2) launch_pdl(k_tag_own<2>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
-      else if (own_u == 4) launch_pdl(k_tag_own<4>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
-      else launch_pdl(k_tag_own<8>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
+    // 1: one slot per thread (a step fits one round of the resident threads); 2: dedupe in shared memory;
+    // 3: U slots per thread with batched claims (what large steps use)
+    const int own = d.shard ? 1 : 0;
+    const int u = tr->tag_batch_u;
+    const int grid = tr->tag_batch_grid + xx_ctas + push_ctas;
+    if (tr->tag_un == 2 && !own) {
+      launch_pdl(k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx, xx_ctas, push_ctas);
+    } else if (u == 1) {
+      launch_pdl(k_tag<1>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
     } else {
-      const int un = d.shard ? 1 : tr->tag_un;  // an owner sees 1/G of the slots: duplicates inside a block are rare
-      launch_pdl(un == 1 ? k_tag<1> : k_tag<2>, (d.shard ? tr->tag_own_grid : tr->tag_grid) + xx_ctas + push_ctas, XX_THREADS,
-                 un == 1 ? (size_t)0 : table_smem, tr->stream, d, local, idx, xx_ctas, push_ctas);
+#define FV_TAG_BATCH(U_)                                                                                                      \
+  (own ? launch_pdl(k_tag_batch<U_, true>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas)   \
+       : launch_pdl(k_tag_batch<U_, false>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas))
+      if (u == 2) FV_TAG_BATCH(2);
+      else if (u == 4) FV_TAG_BATCH(4);
+      else FV_TAG_BATCH(8);
+#undef FV_TAG_BATCH
     }
     *launches += 1;
   } else if (phase == 2) {
@@ -2651,13 +2694,14 @@ void choose_tag_variant(fv_trainer* tr, int force_un) {
   const Dev& d = tr->d;
   const size_t E = (size_t)d.G * d.B * d.W * (1 + d.has_delta);
   const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS;
-  tr->tag_un = force_un ? force_un : (((E + XX_THREADS - 1) / XX_THREADS > resident) ? 2 : 1);
+  tr->tag_un = (force_un == 2) ? 2 : 1;
   tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, (int)resident);
-  // sharded update: slots per thread so that one block round covers the step
+  // slots per thread so that one block round covers the step
   int u = 1;
   while (u < 8 && (E + (size_t)XX_THREADS * u - 1) / ((size_t)XX_THREADS * u) > resident) u *= 2;
-  tr->tag_own_u = u;
-  tr->tag_own_grid = grid_for(E, XX_THREADS * u, (int)resident);
+  if (force_un == 1) u = 1;
+  tr->tag_batch_u = u;
+  tr->tag_batch_grid = grid_for(E, XX_THREADS * u, (int)resident);
 }
 
 int create_impl(const fv_config* cfg, fv_trainer* tr) {
@@ -3354,14 +3398,14 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
     choose_tag_variant(tr, (int)value);
     return FV_OK;
   }
-  if (strcmp(key, "tag_own_slots") == 0) {
+  if (strcmp(key, "tag_slots") == 0) {
     FV_REQUIRE(value == 0.0 || value == 1.0 || value == 2.0 || value == 4.0 || value == 8.0, FV_ERR_INVALID,
-               "tag_own_slots must be 0 (by size), 1, 2, 4 or 8, got %g", value);
+               "tag_slots must be 0 (by size), 1, 2, 4 or 8, got %g", value);
     choose_tag_variant(tr, 0);
     if (value != 0.0) {
-      const size_t E = (size_t)tr->d.G * tr->d.B * tr->d.W;
-      tr->tag_own_u = (int)value;
-      tr->tag_own_grid = grid_for(E, XX_THREADS * tr->tag_own_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
+      const size_t E = (size_t)tr->d.G * tr->d.B * tr->d.W * (1 + tr->d.has_delta);
+      tr->tag_batch_u = (int)value;
+      tr->tag_batch_grid = grid_for(E, XX_THREADS * tr->tag_batch_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
     }
     return FV_OK;
   }

@@ -190,15 +190,15 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  * (model_descriptor.cu:50-112); none changes a result.
  *   "spin_limit"   polls a device-side wait for a peer's word makes before it gives up and the call
  *                  returns FV_ERR_TIMEOUT (default 8388608, about ten seconds);
- *   "tag_variant"  1: the scatter bookkeeping claims positions one slot per thread; 2: it first
- *                  deduplicates 1024 slots in shared memory; 0: chosen by the size of a step;
+ *   "tag_variant"  2: the scatter bookkeeping first deduplicates 1024 slots in shared memory; 1: one
+ *                  slot per thread and block round; 0 (default): as many slots per thread as make one
+ *                  round cover the step, their loads and claims issued together;
+ *   "tag_slots"    the slots per thread of the default variant: 1, 2, 4, 8, or 0 for the size-based choice;
  *   "colmax_lists" 1 (default): the largest untouched weight of every unit comes from a short list of
  *                  candidate rows kept from step to step (a unit whose list cannot certify its maximum
  *                  has its column read on the spot); 0: the matrix is streamed in every step (FV_COLMAX=scan
  *                  in the environment selects the same);
  *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
- *   "tag_own_slots" slots a thread of the sharded update's tagging kernel takes per round: 1, 2, 4, 8,
- *                  or 0 for the size-based choice;
  *   "loopback_peers" 1: test aid -- every peer's mailbox is mapped onto this rank's own, so a peer's
  *                  words never arrive and the first wait for one runs into spin_limit. */
 int fv_trainer_set_option(fv_trainer* tr, const char* key, double value);

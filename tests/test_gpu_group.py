@@ -122,13 +122,13 @@ def test_config2_shapes_eight_linked_ranks_sharded(built_lib):
 
 @pytest.mark.parametrize("slots", [2, 4, 8])
 def test_batched_owner_tagging_on_duplicate_heavy_steps(built_lib, slots):
-    """The sharded update's tagging kernel with several slots per thread, forced at a small shape: a tiny
-    vocabulary makes the same (unit, token) pair occur many times in one block round."""
+    """The tagging kernel with several slots per thread (owner-only form of the sharded update), forced at a
+    small shape: a tiny vocabulary makes the same (unit, token) pair occur many times in one block round."""
     world, B = 3, 700
     p = small_problem(K=40, V=36, W=9, ntok=40000, seed=29, zipf_s=1.2)
     g = make_group(p, world, B, shard=True, lr0=5e-4)
     for t in g.ranks:
-        t.set_option("tag_own_slots", slots)
+        t.set_option("tag_slots", slots)
     eps = np.float32(5e-4)
     Wcur = p["W0"]
     for t in range(3):

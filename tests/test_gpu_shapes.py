@@ -71,10 +71,11 @@ def test_config1_shapes_free_running_300_steps(built_lib):
     assert_weights_close(Wgpu, Wref)
 
 
-@pytest.mark.parametrize("world", [4, 8])
-def test_config2_shapes_emulated_ranks(built_lib, world):
+@pytest.mark.parametrize("world,variant", [(4, 0), (8, 0), (8, 2)])
+def test_config2_shapes_emulated_ranks(built_lib, world, variant):
     """Config 2's global step (world x 10000 windows): every rank's block on one GPU, which makes
-    the scatter bookkeeping large enough for the deduplicating tagging kernel.  Teacher-forced
+    the scatter bookkeeping larger than one slot per resident thread: the tagging kernel takes 2 and
+    4 slots per thread (variant 0) or deduplicates in shared memory (variant 2).  Teacher-forced
     steps against the oracle's `ngpus = world` combine: winners exact (near ties excepted), xx,
     normaliser, synapses."""
     K, V, W, B, steps = 400, 20000, 11, 10000, 3
@@ -84,6 +85,7 @@ def test_config2_shapes_emulated_ranks(built_lib, world):
     W0 = synth.make_weights(K, 2 * V, seed=2)
     eps = np.float32(2e-4)
     tr = trainer(K, V, W, B, enc, off, W0, perm, world=world, flags=_lib.FV_FLAG_EMULATE_RANKS)
+    tr.set_option("tag_variant", variant)
     runner = c_oracle.StepRunner(K, 2 * V, V, W, B, world)
     Wcur = W0.copy()
     for t in range(steps):
@@ -105,14 +107,19 @@ def test_config2_shapes_emulated_ranks(built_lib, world):
         Wcur = Wgpu
 
 
+@pytest.mark.parametrize("slots", [0, 2, 8])
 @pytest.mark.parametrize("K,V,W,B,world,delta", [(64, 40, 11, 700, 2, 0.0), (100, 64, 5, 2000, 1, 0.0), (32, 30, 7, 900, 3, 0.4)])
-def test_dedupe_tagging_kernel_on_duplicate_heavy_steps(built_lib, K, V, W, B, world, delta):
-    """The deduplicating tagging kernel forced at small shapes: a tiny vocabulary makes nearly every
-    (unit, token) pair occur many times inside one block of 1024 slots, ties included."""
+def test_tagging_variants_on_duplicate_heavy_steps(built_lib, K, V, W, B, world, delta, slots):
+    """The tagging kernels for large steps forced at small shapes -- the deduplicating one (slots = 0) and
+    the one with several slots per thread and batched claims: a tiny vocabulary makes nearly every
+    (unit, token) pair occur many times inside one block round, ties and the second winner's kind included."""
     p = small_problem(K=K, V=V, W=W, ntok=30000, seed=21, zipf_s=1.2)
     flags = _lib.FV_FLAG_EMULATE_RANKS if world > 1 else 0
     tr = trainer(K, V, W, B, p["enc"], p["off"], p["W0"], p["perm"], world=world, flags=flags, delta=delta)
-    tr.set_option("tag_variant", 2)
+    if slots == 0:
+        tr.set_option("tag_variant", 2)
+    else:
+        tr.set_option("tag_slots", slots)
     eps = np.float32(5e-4)
     Wcur = p["W0"]
     for t in range(3):
