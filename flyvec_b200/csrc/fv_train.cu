@@ -2832,7 +2832,10 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   // Three CTAs fit an SM (registers); the grid stays resident together with the 1 + PUSH_CTAS CTAs that
   // serve the exchange.  A CTA takes 512 slots per block round while one round covers the step, else
   // 1024 deduplicated in shared memory (2048 per round measured no faster at 8 ranks).
-  choose_tag_variant(tr, 0);
+  {
+    const char* e = getenv("FV_TAG_VARIANT");  // same as the "tag_variant" option, for whole runs
+    choose_tag_variant(tr, e ? atoi(e) : 0);
+  }
   tr->entry_grid = grid_for(E, 256, tr->num_sms * 8);
   {
     // k_apply waits on peers inside the kernel (sharded update), so its grid must be fully resident
