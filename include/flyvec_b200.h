@@ -190,9 +190,10 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  * (model_descriptor.cu:50-112); none changes a result.
  *   "spin_limit"   polls a device-side wait for a peer's word makes before it gives up and the call
  *                  returns FV_ERR_TIMEOUT (default 8388608, about ten seconds);
- *   "tag_variant"  2: the scatter bookkeeping first deduplicates 1024 slots in shared memory; 1: one
- *                  slot per thread and block round; 0 (default): as many slots per thread as make one
- *                  round cover the step, their loads and claims issued together;
+ *   "tag_variant"  the scatter bookkeeping of a step: 1: one slot per thread and block round; 2: 1024 slots
+ *                  deduplicated in shared memory before they are claimed; 3: several slots per thread, their
+ *                  loads and claims issued together; 0 (default): 1 while a step fits the resident threads, else
+ *                  2 for the replicated and 3 for the sharded update;
  *   "tag_slots"    the slots per thread of the default variant: 1, 2, 4, 8, or 0 for the size-based choice;
  *   "colmax_lists" 1 (default): the largest untouched weight of every unit comes from a short list of
  *                  candidate rows kept from step to step (a unit whose list cannot certify its maximum

@@ -71,11 +71,11 @@ def test_config1_shapes_free_running_300_steps(built_lib):
     assert_weights_close(Wgpu, Wref)
 
 
-@pytest.mark.parametrize("world,variant", [(4, 0), (8, 0), (8, 2)])
+@pytest.mark.parametrize("world,variant", [(4, 0), (8, 0), (8, 3)])
 def test_config2_shapes_emulated_ranks(built_lib, world, variant):
     """Config 2's global step (world x 10000 windows): every rank's block on one GPU, which makes
-    the scatter bookkeeping larger than one slot per resident thread: the tagging kernel takes 2 and
-    4 slots per thread (variant 0) or deduplicates in shared memory (variant 2).  Teacher-forced
+    the scatter bookkeeping larger than one slot per resident thread: the tagging kernel deduplicates
+    in shared memory (variant 0, the default at this size) or takes 4 slots per thread (variant 3).  Teacher-forced
     steps against the oracle's `ngpus = world` combine: winners exact (near ties excepted), xx,
     normaliser, synapses."""
     K, V, W, B, steps = 400, 20000, 11, 10000, 3
