@@ -800,15 +800,15 @@ int fv_hash_tokens(fv_hasher* hs, const int32_t* ids, uint64_t n, uint32_t hash_
 // ---------------------------------------------------------------------------
 // Token hashing without any allocation.
 //
-// fv_hash_tokens stages the ids and the codes in device buffers it allocates and
-// frees on every call.  That is fine for bulk work, but it hurts two kinds of
-// callers of this library: a service that hashes a few query tokens at a time on
-// the GPU a trainer is running on (cudaFree waits for the whole device, so every
-// small request would stall the training stream), and a process whose device
-// memory is owned up front by somebody else's pool, where an extra cudaMalloc may
-// simply fail.  For them the staging area is the fixed array below: it is part of
-// the library image, so every GPU that loads the library holds these
-// FV_STATIC_SCRATCH_BYTES until the process exits, whether the call is used or not.
+// fv_hash_tokens makes its staging buffers (device memory, pinned host memory and, for large
+// batches, a table of the whole vocabulary's codes) the first time it is called on a hasher.
+// That is fine for bulk work, but two kinds of callers of this library cannot allocate at
+// that moment: a process whose device memory is owned up front by somebody else's pool,
+// where an extra cudaMalloc may simply fail, and a service that answers a few query tokens
+// at a time beside a trainer that already fills the GPU and must not see its footprint grow.
+// For them the staging area is the fixed array below: it is part of the library image, so
+// every GPU that loads the library holds these FV_STATIC_SCRATCH_BYTES until the process
+// exits, whether the call is used or not.
 //
 // The array's name is only a handle on the host; the device address is looked up
 // once per device with cudaGetSymbolAddress (with that device current) the first

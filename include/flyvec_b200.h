@@ -231,11 +231,12 @@ int fv_trainer_get_counter(fv_trainer* tr, const char* key, uint64_t* value);
  *      an old sequence number polls that word, every poll loop is bounded, and a peer that never
  *      delivers ends the call with FV_ERR_TIMEOUT.
  * Mode 2 is chosen when every rank can map every other rank's mailbox; the environment variable
- * FV_COMM=nccl forces mode 1.  In mode 2 the update is sharded unless delta != 0: rank r does the
- * scatter bookkeeping and the abs-max scan for the matrix rows i % world == r only and stores the
- * count of every touched position into its peers' inboxes, from which every replica applies the same
- * update to its own copy ("shard" option / FV_SHARD=0 select the replicated update, in which every
- * rank rebuilds every rank's scatter). */
+ * FV_COMM=nccl forces mode 1.  In mode 2 the update is replicated by default (every rank rebuilds every
+ * rank's scatter from the exchanged winners: one exchange per step) or, with the "shard" option /
+ * FV_SHARD=1 and delta == 0, sharded: rank r does the scatter bookkeeping and the column maxima for the
+ * matrix rows i % world == r only and stores the count of every touched position into its peers' inboxes,
+ * from which every replica applies the same update to its own copy (two exchanges per step, 1/world of
+ * the bookkeeping). */
 int fv_trainer_comm_mode(fv_trainer* tr, int* mode);
 /* Which windows of the current order rank `rank` owns in global step `step`
  * (cuda_funcs.cu:1667-1670); pure arithmetic, usable without a GPU. */
@@ -257,8 +258,8 @@ int fv_hasher_get_weights(fv_hasher* h, float* w_kn);
 int fv_hash_tokens(fv_hasher* h, const int32_t* ids, uint64_t n, uint32_t hash_length, uint32_t flags, uint8_t* out);
 /* No counterpart in the reference.  Same result as fv_hash_tokens, but the call allocates nothing: ids and codes
  * are staged in a fixed 8 MiB device array that is part of the library (held by every GPU that loads it).  Meant for
- * callers that must not allocate while they hash: small requests served next to a running trainer (cudaFree would
- * stall its stream) or processes whose device memory belongs to another pool.  n * (4 + bytes per code) + 256 must
+ * callers that must not allocate while they hash: processes whose device memory belongs to another pool, or small
+ * requests served next to a trainer that fills the GPU (fv_hash_tokens makes staging buffers on its first call).  n * (4 + bytes per code) + 256 must
  * fit into 8 MiB, else FV_ERR_INVALID.  The first call on a device looks up the array's address and should be made
  * before any stream capture is started; overlapping calls on one GPU race on the array. */
 int fv_hash_tokens_static(fv_hasher* h, const int32_t* ids, uint64_t n, uint32_t hash_length, uint32_t flags,
