@@ -17,9 +17,9 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-@pytest.mark.parametrize("exchange", ["mailbox", "mailbox-replicated", "nccl"])
+@pytest.mark.parametrize("exchange", ["mailbox", "mailbox-sharded", "nccl"])
 def test_two_ranks_match_oracle(built_lib, tmp_path, exchange):
-    """Packets written straight into the peer's memory with the sharded and with the replicated update,
+    """Packets written straight into the peer's memory with the replicated and with the sharded update,
     and one all-gather per step."""
     if _lib.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -33,8 +33,8 @@ def test_two_ranks_match_oracle(built_lib, tmp_path, exchange):
     env.pop("FV_SHARD", None)
     if exchange == "nccl":
         env["FV_COMM"] = "nccl"
-    elif exchange == "mailbox-replicated":
-        env["FV_SHARD"] = "0"
+    elif exchange == "mailbox-sharded":
+        env["FV_SHARD"] = "1"
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     r0 = np.load(tmp_path / "rank0.npz")
