@@ -65,6 +65,7 @@ struct StepCtl {
   uint32_t out_count;     // (unused)
   uint32_t pad;
   uint32_t list_count[2]; // records reserved in this step's touched-position list, by step parity
+  unsigned long long update_arrivals;  // CTAs of k_update that have reached the meeting point, over all steps
   uint32_t need_scan;     // (unused)
   uint32_t scans_run;     // units whose column k_eval had to read in this call (their candidates were all touched)
   // Device-side phase clock: every step kernel's first thread charges the time since the previous
@@ -1957,6 +1958,312 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
 }
 
 // ---------------------------------------------------------------------------
+// k_eval and k_apply as ONE kernel for ordinary steps (no list rebuild, replicated or single-rank update).
+// Both halves are short chains of dependent accesses and the second needs only two things of the first
+// grid-wide -- the largest |D| at the records and the units' column maxima -- so the grid meets once at a
+// counter instead of ending and starting again: one launch less per step, and a record CTA keeps the
+// records it evaluated in registers and applies them without loading them a second time.
+//   CTAs [0, qblocks)   query the candidate lists (as in k_eval), then help nobody: they are done
+//   the other CTAs      evaluate D at their records, meet, derive nc and the step size, apply their records
+// The meeting point is a 64-bit arrival counter that only grows (`target` = the count once all CTAs of this
+// launch are in; the host counts the launches), so nothing has to be reset; every CTA of the grid is resident (the launch is sized by the occupancy calculator), the wait is
+// bounded like every other wait here.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, const int32_t* __restrict__ idx, int qblocks,
+                                                            unsigned long long target) {
+  grid_dependency_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_SCAN);
+  if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
+  const int p = (int)((d.ctl->tick + local) & 1);
+  const int lane = threadIdx.x & 31;
+  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+
+  // ---- first half ---------------------------------------------------------------------------------
+  constexpr int TS = 4;
+  int cp[TS], cn[TS];
+  uint4 rc[TS];
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* sC = reinterpret_cast<double*>(smem_raw);                // X*alpha, later s / (n * alpha')
+  double* sXm = sC + d.Kp;                                         // mean xx over the active ranks
+  int* sN = reinterpret_cast<int*>(sXm + d.Kp);                    // active ranks
+  uint32_t* sBad = reinterpret_cast<uint32_t*>(sN + d.Kp);         // ranks whose windows must leave the counts
+  uint32_t* sFloor = sBad + d.Kp;                                  // the units' candidate floors
+  const bool query_cta = (int)blockIdx.x < qblocks;
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nthreads = (gridDim.x - qblocks) * blockDim.x;
+  const int e0 = ((int)blockIdx.x - qblocks) * (int)blockDim.x + (int)threadIdx.x;
+  const float delta = d.ctl->delta;
+
+  if (query_cta) {
+    constexpr int QW = SCAN_THREADS / 32;
+    __shared__ int s_unc[QW];
+    const int wic = threadIdx.x >> 5;
+    const int mu = blockIdx.x * QW + wic;
+    if (lane == 0) s_unc[wic] = 0;
+    if (mu < d.K) {
+      const uint32_t* __restrict__ wbits = reinterpret_cast<const uint32_t*>(d.wt);
+      const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+      const uint32_t floor_bits = __ldcg(d.cand_floor + mu);
+      int row[CAND_CAP / 32];
+#pragma unroll
+      for (int t = 0; t < CAND_CAP / 32; ++t) row[t] = (lane + 32 * t < n) ? __ldcg(d.cand_rows + (size_t)mu * CAND_CAP + lane + 32 * t) : -1;
+      uint32_t xbits = 0u;
+      if (lane < d.G) {
+        const unsigned long long* word = packet(d, p, lane) + d.XO + mu;
+        const unsigned long long w = load_relaxed_sys64(word);
+        xbits = ((uint32_t)(w >> 32) == seq) ? (uint32_t)w : pk_read(d, word, seq, 0u);
+      }
+      const bool active = __any_sync(FULL, lane < d.G && __uint_as_float(xbits) != 0.f);
+      if (active) {
+        uint32_t m = 0u;
+#pragma unroll
+        for (int t = 0; t < CAND_CAP / 32; ++t) {
+          if (row[t] < 0) continue;
+          const uint32_t w = __ldcg(wbits + (size_t)row[t] * d.Kp + mu) & ABS_MASK;
+          m = max(m, w > TAG_BASE ? 0u : w);
+        }
+        m = warp_max_u32(m);
+        if (lane == 0) {
+          if (m >= floor_bits) d.colmax[p * d.Kp + mu] = m;
+          else s_unc[wic] = 1;
+        }
+      }
+    }
+    __syncthreads();
+    for (int w = 0; w < QW; ++w) {
+      if (!s_unc[w]) continue;
+      // every strong candidate of this unit was touched: read its whole column (see k_eval)
+      const int cu = blockIdx.x * QW + w;
+      const uint32_t* __restrict__ col = reinterpret_cast<const uint32_t*>(d.wt) + cu;
+      unsigned long long best = 0ull;
+      constexpr int RU = 8;
+      for (int r0 = threadIdx.x; r0 < d.N; r0 += RU * SCAN_THREADS) {
+        uint32_t v[RU];
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+          const int r = r0 + u * SCAN_THREADS;
+          v[u] = (r < d.N) ? (__ldcg(col + (size_t)r * d.Kp) & ABS_MASK) : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+          const int r = r0 + u * SCAN_THREADS;
+          if (r < d.N && v[u] <= TAG_BASE) best = max(best, ((unsigned long long)v[u] << 32) | (uint32_t)r);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) best = max(best, __shfl_xor_sync(FULL, best, o));
+      __shared__ unsigned long long s_best[QW];
+      if (lane == 0) s_best[wic] = best;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        for (int k = 1; k < QW; ++k) best = max(best, s_best[k]);
+        const uint32_t m = (uint32_t)(best >> 32);
+        d.colmax[p * d.Kp + cu] = m;
+        d.cand_floor[cu] = m;
+        if (m) {
+          const int row = (int)(uint32_t)best;
+          const int n = min(d.cand_n[cu], CAND_CAP);
+          bool have = false;
+          for (int j = 0; j < n; ++j) have |= (d.cand_rows[(size_t)cu * CAND_CAP + j] == row);
+          if (!have) {
+            const int slot = (n < CAND_CAP) ? n : (int)((d.ctl->tick + local + (unsigned)cu) % CAND_CAP);
+            d.cand_rows[(size_t)cu * CAND_CAP + slot] = row;
+            d.cand_n[cu] = (n < CAND_CAP) ? n + 1 : CAND_CAP;
+          } else {
+            d.cand_n[cu] = n;
+          }
+        }
+        atomicAdd(&d.ctl->scans_run, 1u);
+      }
+      __syncthreads();
+    }
+  } else {
+    const double* __restrict__ alpha = d.alpha + p * d.Kp;
+    __shared__ int s_any_bad;
+    auto load_batch = [&](int k0) {
+#pragma unroll
+      for (int u = 0; u < TS; ++u) {
+        const int k = k0 + u * nthreads;
+        cp[u] = (k < nrec) ? d.cnt[k] : 0;
+        cn[u] = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
+        rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+      }
+    };
+    load_batch(e0);  // in flight while the combine below polls the packets
+    if (threadIdx.x == 0) s_any_bad = 0;
+    __syncthreads();
+    for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+      double X = 0.0;
+      int n = 0;
+      if (mu < d.K) unit_stats(d, p, seq, mu, &X, &n);
+      sC[mu] = X * alpha[mu];
+      sXm[mu] = X;
+      sN[mu] = n;
+      const uint32_t bad = (mu < d.K && n > 0) ? unit_cancelled(d, p, mu) : 0u;
+      sBad[mu] = bad;
+      if (bad) s_any_bad = 1;
+    }
+    __syncthreads();
+    if (s_any_bad) {
+      const unsigned long long* packet0 = packet(d, p, 0);
+      for (int k = e0; k < nrec; k += nthreads) {
+        const uint4 r = d.rec[k];
+        if (r.w == 0u) continue;
+        const int irow = (int)fdiv(r.x, d.mKp, d.sKp);
+        const int mu = (int)r.x - irow * d.Kp;
+        if (!sBad[mu]) continue;
+        const int2 c = cancelled_multiplicity(packet0, d.P, d.G, d.B, d.W, d.MO, d.has_delta, idx, d.idx_rstride, irow, mu, sBad[mu]);
+        if (c.x) d.cnt[k] -= c.x;
+        if (c.y) d.cntn[k] -= c.y;
+      }
+      load_batch(e0);  // the counts have changed
+    }
+    uint32_t tmax = 0u;
+    auto eval_batch = [&]() {
+#pragma unroll
+      for (int u = 0; u < TS; ++u) {
+        if (rc[u].w == 0u) continue;  // a hole (or past the end)
+        const int mu = (int)(rc[u].x - fdiv(rc[u].x, d.mKp, d.sKp) * (uint32_t)d.Kp);
+        if (sN[mu] == 0) continue;
+        const float c = (float)(cp[u] + (int)(rc[u].w & 0xffffu)) - delta * (float)(cn[u] + (int)(rc[u].w >> 16));
+        const double D = -sC[mu] * (double)__uint_as_float(rc[u].y) + (double)c * (double)__uint_as_float(rc[u].z) / (double)sN[mu];
+        tmax = max(tmax, __float_as_uint(fabsf((float)D)));
+      }
+    };
+    eval_batch();
+    for (int k0 = e0 + TS * nthreads; k0 < nrec; k0 += TS * nthreads) {  // more records than one batch per thread (many ranks)
+      load_batch(k0);
+      eval_batch();
+    }
+    if (e0 + TS * nthreads < nrec) load_batch(e0);  // back to the first batch for the second half
+    __shared__ uint32_t s_tmax;
+    if (threadIdx.x == 0) s_tmax = 0u;
+    __syncthreads();
+    tmax = warp_max_u32(tmax);
+    if (lane == 0 && tmax) atomicMax(&s_tmax, tmax);
+    __syncthreads();
+    if (threadIdx.x == 0 && s_tmax) atomicMax(&d.ncb[p], s_tmax);
+  }
+
+  // ---- the grid meets -------------------------------------------------------------------------------
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(&d.ctl->update_arrivals, 1ull);
+    unsigned polls = 0;
+    while (*reinterpret_cast<volatile unsigned long long*>(&d.ctl->update_arrivals) < target) {
+      if (wait_expired(d, polls)) {
+        s_fail = 1;
+        break;
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  if (s_fail || query_cta) return;
+
+  // ---- second half: normaliser, step size, the records come back with their scatter term ------------
+  const double* __restrict__ alpha = d.alpha + p * d.Kp;
+  double* __restrict__ alpha_next = d.alpha + (p ^ 1) * d.Kp;
+  __shared__ float sRed[SCAN_THREADS / 32];
+  __shared__ float sScale;
+  const bool first = (int)blockIdx.x == qblocks;  // the CTA that writes what there is one of
+  float dense = 0.f;
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    sFloor[mu] = __ldcg(d.cand_floor + mu);
+    if (sN[mu] > 0) dense = fmaxf(dense, (float)(fabs(sC[mu]) * (double)__uint_as_float(__ldcg(&d.colmax[p * d.Kp + mu]))));
+  }
+  dense = warp_max(dense);
+  if (lane == 0) sRed[threadIdx.x >> 5] = dense;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float nc = __uint_as_float(__ldcg(&d.ncb[p]));
+    for (int w = 0; w < SCAN_THREADS / 32; ++w) nc = fmaxf(nc, sRed[w]);
+    const float eps = d.ctl->eps;
+    const float s = (d.prec > nc) ? eps / d.prec : eps / nc;  // cuda_funcs.cu:1797-1799
+    sScale = s;
+    if (first) {
+      d.nc_log[local] = nc;
+      d.s_log[local] = s;
+    }
+  }
+  __syncthreads();
+  const float s = sScale;
+  for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
+    const int n = sN[mu];
+    double a = alpha[mu];
+    double coef = 0.0;
+    if (n > 0) {
+      a = a * (1.0 - (double)s * sXm[mu]);
+      if (a != 0.0)
+        coef = (double)s / ((double)n * a);
+      else
+        atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+    }
+    sC[mu] = coef;
+    if (first) {
+      alpha_next[mu] = a;
+      d.stat_x[p * d.Kp + mu] = sXm[mu];
+      d.stat_n[p * d.Kp + mu] = n;
+    }
+  }
+  __syncthreads();
+  uint32_t vmax = 0u;
+  auto apply_batch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < TS; ++u) {
+      if (rc[u].w == 0u) continue;  // a hole
+      const int k = k0 + u * nthreads;
+      const int mu = (int)(rc[u].x - fdiv(rc[u].x, d.mKp, d.sKp) * (uint32_t)d.Kp);
+      const double scat = (double)(cp[u] + (int)(rc[u].w & 0xffffu)) - (double)delta * (double)(cn[u] + (int)(rc[u].w >> 16));
+      const float v = (float)((double)__uint_as_float(rc[u].y) + scat * (double)__uint_as_float(rc[u].z) * sC[mu]);
+      d.wt[rc[u].x] = v;
+      d.rec[k].w = 0u;  // the slot is a hole again until it is claimed anew
+      if (cp[u]) d.cnt[k] = 0;
+      if (cn[u]) d.cntn[k] = 0;
+      const uint32_t vb = __float_as_uint(fabsf(v));
+      vmax = max(vmax, vb);
+      if (vb > sFloor[mu] && vb > __ldcg(d.cand_floor + mu)) {
+        // the new weight rises above its unit's floor: list its row, or lift the floor when the list is full
+        const int irow = (int)fdiv(rc[u].x, d.mKp, d.sKp);
+        const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
+        bool have = false;
+        for (int j = 0; j < n; ++j) have |= (__ldcg(d.cand_rows + (size_t)mu * CAND_CAP + j) == irow);
+        if (!have) {
+          const int slot = atomicAdd(d.cand_n + mu, 1);
+          if (slot < CAND_CAP) d.cand_rows[(size_t)mu * CAND_CAP + slot] = irow;
+          else atomicMax(d.cand_floor + mu, vb);
+        }
+      }
+    }
+  };
+  apply_batch(e0);
+  for (int k0 = e0 + TS * nthreads; k0 < nrec; k0 += TS * nthreads) {
+#pragma unroll
+    for (int u = 0; u < TS; ++u) {
+      const int k = k0 + u * nthreads;
+      cp[u] = (k < nrec) ? d.cnt[k] : 0;
+      cn[u] = (k < nrec && d.has_delta) ? d.cntn[k] : 0;
+      rc[u] = (k < nrec) ? d.rec[k] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    apply_batch(k0);
+  }
+  // keep the bound on max |wt| valid for the next forward pass
+  vmax = warp_max_u32(vmax);
+  if (lane == 0 && vmax > d.ctl->wabsmax) atomicMax(&d.ctl->wabsmax, vmax);
+  // what the next step must find cleared (no CTA reads these again in this step: all are past the meeting point)
+  if (first) {
+    for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) d.colmax[(p ^ 1) * d.Kp + mu] = 0u;
+    if (threadIdx.x == 0) {
+      d.ncb[p ^ 1] = 0u;
+      d.ctl->list_count[p ^ 1] = 0u;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Folding the scale into the weights: wt[i][mu] *= alpha[mu]; then alpha = 1.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
@@ -2266,6 +2573,11 @@ struct fv_trainer {
   int tag_un = 1;
   unsigned long long matrix_scans = 0;    // steps in which the column maxima came from a pass over the matrix
   unsigned long long column_rescans = 0;  // single units whose column was read because their candidates were all touched
+  bool fused_update = true;      // ordinary steps run evaluation and apply as one kernel (k_update)
+  bool fused_this_step = false;
+  int update_grid = 0;           // CTAs of k_update: all resident at once
+  size_t update_smem = 0;
+  unsigned long long update_launches = 0;
   bool cand_dirty = true;  // the candidate lists of the column maxima do not describe the current weights
   int32_t* d_cand_rows = nullptr;
   int32_t* d_cand_n = nullptr;
@@ -2423,7 +2735,18 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     }
     *launches += 1;
   } else if (phase == 2) {
-    if (d.use_cand) {
+    tr->fused_this_step = false;
+    if (d.use_cand && !tr->cand_dirty && !d.shard && tr->fused_update && tr->update_grid > 0) {
+      // an ordinary step: evaluation and apply in one kernel
+      const int qblocks = (d.K + SCAN_THREADS / 32 - 1) / (SCAN_THREADS / 32);
+      tr->update_launches += 1;
+      launch_pdl(k_update, tr->update_grid, SCAN_THREADS, tr->update_smem, tr->stream, d, local, idx, qblocks,
+                 tr->update_launches * (unsigned long long)tr->update_grid);
+      FV_CUDA(cudaGetLastError());
+      *launches += 1;
+      tr->fused_this_step = true;
+      tr->steps_since_fold += 1;
+    } else if (d.use_cand) {
       const int rebuild = tr->cand_dirty ? 1 : 0;
       const int qblocks = (d.K + SCAN_THREADS / 32 - 1) / (SCAN_THREADS / 32);  // a warp per unit
       const int rblocks = std::max(tr->scan_grid - qblocks, tr->num_sms);  // one resident wave together with the query CTAs
@@ -2440,7 +2763,7 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
       launch_pdl(k_scan, tr->scan_grid, SCAN_THREADS, tr->scan_smem, tr->stream, d, local, idx);
       *launches += 1;
     }
-  } else {
+  } else if (!tr->fused_this_step) {
     launch_pdl(k_apply, tr->apply_grid, 256, tr->apply_smem, tr->stream, d, local, idx);
     FV_CUDA(cudaGetLastError());
     *launches += 1;
@@ -2850,6 +3173,17 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
     if (apply_bps < 1) apply_bps = 1;
     if (apply_bps > 4) apply_bps = 4;
     tr->apply_grid = grid_for(E, 256, tr->num_sms * apply_bps);
+  }
+  {
+    // k_update's CTAs meet inside the kernel, so the whole grid must be resident
+    tr->update_smem = (size_t)d.Kp * (2 * sizeof(double) + sizeof(int) + 2 * sizeof(uint32_t));
+    int bps = 0;
+    FV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, k_update, SCAN_THREADS, tr->update_smem));
+    if (bps > 2) bps = 2;
+    const int qblocks = (d.K + SCAN_THREADS / 32 - 1) / (SCAN_THREADS / 32);
+    tr->update_grid = (bps >= 1 && tr->num_sms * bps > qblocks + tr->num_sms / 2) ? tr->num_sms * bps : 0;
+    const char* e = getenv("FV_FUSED_UPDATE");
+    tr->fused_update = e ? atoi(e) != 0 : true;
   }
   FV_TRY(dev_alloc(&tr->d_xx_acc, 2 * (size_t)XX_SLOTS * d.Kp));
   FV_TRY(dev_alloc(&tr->d_xx_wins, (size_t)d.Kp));
@@ -3417,6 +3751,11 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
       tr->tag_batch_u = (int)value;
       tr->tag_batch_grid = grid_for(E, XX_THREADS * tr->tag_batch_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
     }
+    return FV_OK;
+  }
+  if (strcmp(key, "fused_update") == 0) {
+    FV_REQUIRE(value == 0.0 || value == 1.0, FV_ERR_INVALID, "fused_update must be 0 or 1, got %g", value);
+    tr->fused_update = value != 0.0;
     return FV_OK;
   }
   if (strcmp(key, "colmax_lists") == 0) {

@@ -199,6 +199,9 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *                  candidate rows kept from step to step (a unit whose list cannot certify its maximum
  *                  has its column read on the spot); 0: the matrix is streamed in every step (FV_COLMAX=scan
  *                  in the environment selects the same);
+ *   "fused_update" 1 (default): in ordinary steps the evaluation of the normaliser and the update of the
+ *                  touched weights run as one kernel whose CTAs meet once at a counter; 0: two kernels
+ *                  (FV_FUSED_UPDATE=0 in the environment selects the same);
  *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
  *   "loopback_peers" 1: test aid -- every peer's mailbox is mapped onto this rank's own, so a peer's
  *                  words never arrive and the first wait for one runs into spin_limit. */

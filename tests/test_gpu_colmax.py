@@ -1,7 +1,8 @@
 """The column maxima behind the normaliser, computed two ways: from the candidate lists kept from step to
 step (the default) and by streaming the whole matrix in every step.  Both are exact, so whole runs must
 agree bit for bit -- weights, per-step normalisers and step sizes -- whatever the shape, across folds of
-the scales, with one rank, emulated ranks and linked ranks with the sharded update."""
+the scales, with one rank, emulated ranks and linked ranks with the sharded update; and the same with the
+evaluation and the apply kernel fused into one (the default) or apart."""
 import numpy as np
 import pytest
 
@@ -13,9 +14,10 @@ from tests.helpers import small_problem
 pytestmark = pytest.mark.gpu
 
 
-def run_single(p, B, steps, lists, world=1, flags=0, lr0=1e-3, delta=0.0):
+def run_single(p, B, steps, lists, world=1, flags=0, lr0=1e-3, delta=0.0, fused=True):
     tr = Trainer(hid=p["K"], vocab=p["V"], window=p["W"], batch=B, lr0=lr0, world=world, flags=flags, delta=delta)
     tr.set_option("colmax_lists", 1 if lists else 0)
+    tr.set_option("fused_update", 1 if fused else 0)
     tr.set_corpus(p["enc"], p["off"])
     tr.set_weights(p["W0"])
     tr.set_permutation(p["perm"])
@@ -44,6 +46,11 @@ def test_lists_and_streaming_agree_bit_for_bit(built_lib, K, V, W, B, steps, wor
     np.testing.assert_array_equal(Wa, Wb)
     assert scans_b == (steps, 0)
     assert scans_a[0] == 1 + (steps - 1) // 128  # the first step and the step after every fold
+    # and with evaluation and apply as two kernels instead of one
+    Wc, ncc, sc, scans_c = run_single(p, B, steps, True, world, flags, delta=delta, fused=False)
+    np.testing.assert_array_equal(ncc, nca)
+    np.testing.assert_array_equal(Wc, Wa)
+    assert scans_c == scans_a
 
 
 def test_lists_spare_the_matrix_pass_at_config1_shapes(built_lib):
