@@ -1729,9 +1729,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_collect(Dev d) {
     const int mu = 4 * q + c;
     if (u > TAG_BASE || u <= fl[c] || mu >= d.K) return;
     if (u <= (fl[c] = __ldcg(d.cand_floor + mu))) return;  // the floor may have risen meanwhile
-    const int n = min(__ldcg(d.cand_n + mu), CAND_CAP);
-    for (int j = 0; j < n; ++j)
-      if (__ldcg(d.cand_rows + (size_t)mu * CAND_CAP + j) == row) return;  // the arg-max row is there already
+    // the only row listed before this pass is the arg-max row, in the first place; every other row is
+    // considered by exactly one thread, so nothing else can be there twice
+    if (__ldcg(d.cand_rows + (size_t)mu * CAND_CAP) == row) return;
     const int slot = atomicAdd(d.cand_n + mu, 1);
     if (slot < CAND_CAP) d.cand_rows[(size_t)mu * CAND_CAP + slot] = row;
     else atomicMax(d.cand_floor + mu, u);
