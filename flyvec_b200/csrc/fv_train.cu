@@ -80,6 +80,9 @@ enum Phase { PH_OTHER = 0, PH_FORWARD = 1, PH_XX = 2, PH_WAIT = 3, PH_TAG = 4, P
 // Everything a kernel needs, passed by value.
 struct Dev {
   int K, Kp, Kq, V, N, W, B, G, rank, P, XO;  // P = packet words, XO = offset of xx inside a packet
+  // Steps this trainer had executed when the running call began.  A kernel's step number is tick0 + local:
+  // the host knows it, so no kernel has to fetch it from the control block before it can form an address.
+  unsigned long long tick0;
   // exact n / divisor for n < 2^31 as (n * m) >> s (64-bit product): m = ceil(2^s / divisor), s = 31 + ceil(log2 divisor)
   uint32_t mW, sW, mB, sB, mKp, sKp, mG, sG;
   int idx_rstride; // ids of a step: rank r's block of B*W ids starts r * idx_rstride elements into the step's buffer
@@ -464,13 +467,13 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.x * FWD_WARPS + (threadIdx.x >> 5);
   const int nwarps = gridDim.x * FWD_WARPS;
-  const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
+  const double* __restrict__ alpha = d.alpha + ((d.tick0 + local) & 1) * d.Kp;
   const int Kq = d.Kq;
   const int32_t* __restrict__ idx_own = idx + (size_t)d.rank * d.idx_rstride;
 
   // tickets: this launch draws from the counter of its parity and clears the other one, so that
   // consecutive launches need nobody else to reset anything
-  const int par = (int)((d.ctl->tick + local) & 1);
+  const int par = (int)((d.tick0 + local) & 1);
   if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->fwd_next[par ^ 1] = 0u;
 
   int j = warp;
@@ -533,7 +536,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
 
   // winners go into this rank's packet as flagged words; the tagging kernel forwards them to the peers
   // (remote stores issued here would have to drain before this kernel can end)
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   unsigned long long* win_out = (lane == 0) ? packet(d, par, d.rank) : nullptr;
   const int zrow = d.N;  // the all-zero row
   const int nbatch = (d.W + 3) >> 2;
@@ -687,9 +690,9 @@ constexpr int XX_WARPS = XX_THREADS / 32;
 // shared-memory hash table of the tagging kernel: 2 * UN * XX_THREADS slots, at most half full
 constexpr size_t tag_table_bytes(int un) { return un > 1 ? (size_t)(2 * 2 * un + 2 * un) * XX_THREADS * sizeof(uint32_t) : 0; }
 __device__ __forceinline__ void xx_finish(const Dev& d, int local) {
-  const int parity = (int)((d.ctl->tick + local) & 1);
+  const int parity = (int)((d.tick0 + local) & 1);
   const bool mailbox = d.peers != nullptr && d.G > 1;
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   const int kexp = d.ctl->xx_kexp;
   for (int mu = threadIdx.x; mu < d.Kp; mu += XX_THREADS) {
     float x = 0.f;
@@ -759,7 +762,7 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
   if (blockIdx.x == 0) {
     xx_finish(d, local);
   } else {
-    push_winners(d, (int)((d.ctl->tick + local) & 1), blockIdx.x - 1, gridDim.x - 1);
+    push_winners(d, (int)((d.tick0 + local) & 1), blockIdx.x - 1, gridDim.x - 1);
   }
 }
 
@@ -808,7 +811,7 @@ template <int UN>  // slots per thread and block round: a CTA deduplicates UN * 
 __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
   grid_dependency_wait();
   extern __shared__ __align__(16) unsigned char tag_smem[];
-  const int parity = (int)((d.ctl->tick + local) & 1);
+  const int parity = (int)((d.tick0 + local) & 1);
   if ((int)blockIdx.x < xx_ctas) {
     xx_finish(d, local);
     return;
@@ -819,7 +822,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
     return;
   }
   if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   // Stage 1: a block of TAG_BLOCK slots is deduplicated in a shared-memory hash table keyed by the
   // matrix position, so a (unit, token) pair that occurs many times in the block -- frequent tokens
   // do -- reaches global memory once, with its multiplicity.  Same-address global atomics complete
@@ -1000,7 +1003,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
 template <int U, bool OWN>
 __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
   grid_dependency_wait();
-  const int parity = (int)((d.ctl->tick + local) & 1);
+  const int parity = (int)((d.tick0 + local) & 1);
   if ((int)blockIdx.x < xx_ctas) {
     xx_finish(d, local);
     return;
@@ -1011,7 +1014,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
     return;
   }
   if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   __shared__ uint32_t s_scan[XX_WARPS];
   __shared__ uint32_t s_gbase;
   // With delta != 0 every (window, position) contributes twice: +f_i to the first winner's row and
@@ -1197,13 +1200,13 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   int* sN = reinterpret_cast<int*>(sC + d.Kp);             // active ranks
   uint32_t* sMax = reinterpret_cast<uint32_t*>(sN + d.Kp); // CTA column maxima
   uint32_t* sBad = sMax + d.Kp;                            // ranks whose windows must leave the counts (unit_cancelled)
-  const int p = (int)((d.ctl->tick + local) & 1);
+  const int p = (int)((d.tick0 + local) & 1);
   const int lane = threadIdx.x & 31;
   const double* __restrict__ alpha = d.alpha + p * d.Kp;
   __shared__ int s_any_bad;
   if (threadIdx.x == 0) s_any_bad = 0;
   __syncthreads();
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     double X = 0.0;
     int n = 0;
@@ -1355,7 +1358,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
   __syncthreads();
   if (threadIdx.x < d.G) {
     // the partial normaliser to everybody (this rank included), the length of the entry list to the peers
-    const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
+    const unsigned long long seq = (unsigned)(d.tick0 + local + 1);
     unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
     store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_red[0]));
     unsigned long long* outw = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
@@ -1405,7 +1408,7 @@ __device__ __forceinline__ void publish_partial(const Dev& d, int local, int p) 
   }
   __syncthreads();
   if (threadIdx.x < d.G) {
-    const unsigned long long seq = (unsigned)(d.ctl->tick + local + 1);
+    const unsigned long long seq = (unsigned)(d.tick0 + local + 1);
     const unsigned nrec = min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
     unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
     store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_pub[0]));
@@ -1421,9 +1424,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
   grid_dependency_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_SCAN);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
-  const int p = (int)((d.ctl->tick + local) & 1);
+  const int p = (int)((d.tick0 + local) & 1);
   const int lane = threadIdx.x & 31;
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
 
   if ((int)blockIdx.x < qblocks) {
     // ---- the candidate lists: one warp per unit, a lane per candidate --------------------------
@@ -1512,7 +1515,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
           if (!have) {
             // a full list gives up one of its rows: every listed untouched row is <= m, the new floor, and a
             // listed touched row is checked again when k_apply writes its new weight
-            const int slot = (n < CAND_CAP) ? n : (int)((d.ctl->tick + local + (unsigned)cu) % CAND_CAP);
+            const int slot = (n < CAND_CAP) ? n : (int)((d.tick0 + local + (unsigned)cu) % CAND_CAP);
             d.cand_rows[(size_t)cu * CAND_CAP + slot] = row;
             d.cand_n[cu] = (n < CAND_CAP) ? n + 1 : CAND_CAP;
           } else {
@@ -1626,7 +1629,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
 __global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, int rebuild) {
   grid_dependency_wait();
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;
-  const int p = (int)((d.ctl->tick + local) & 1);
+  const int p = (int)((d.tick0 + local) & 1);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned long long* sArg = reinterpret_cast<unsigned long long*>(smem_raw);  // [Kp] CTA maxima with their rows
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) sArg[mu] = 0ull;
@@ -1692,7 +1695,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_colscan(Dev d, int local, i
       if (!have) {
         // a full list gives up one of its rows: every listed untouched row is <= m, the new floor, and a
         // listed touched row is checked again when k_apply writes its new weight
-        const int slot = (n < CAND_CAP) ? n : (int)((d.ctl->tick + local + (unsigned)mu) % CAND_CAP);
+        const int slot = (n < CAND_CAP) ? n : (int)((d.tick0 + local + (unsigned)mu) % CAND_CAP);
         d.cand_rows[(size_t)mu * CAND_CAP + slot] = row;
         d.cand_n[mu] = (n < CAND_CAP) ? n + 1 : CAND_CAP;
       } else {
@@ -1773,7 +1776,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   uint32_t* sFloor = reinterpret_cast<uint32_t*>(sN + d.Kp);  // the units' candidate floors as this kernel found them
   __shared__ float sRed[8];
   __shared__ float sScale;
-  const int p = (int)((d.ctl->tick + local) & 1);
+  const int p = (int)((d.tick0 + local) & 1);
   const double* __restrict__ alpha = d.alpha + p * d.Kp;
   double* __restrict__ alpha_next = d.alpha + (p ^ 1) * d.Kp;
 
@@ -1792,7 +1795,7 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   __shared__ int sFail;
   if (threadIdx.x == 0) sFail = 0;
   __syncthreads();
-  const unsigned seq = (unsigned)(d.ctl->tick + local + 1);
+  const unsigned seq = (unsigned)(d.tick0 + local + 1);
   __shared__ uint32_t sWord[MAX_RANKS];
   __shared__ uint32_t sCount[MAX_RANKS];
   if (d.shard && threadIdx.x < d.G) {
@@ -1974,9 +1977,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
   grid_dependency_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_SCAN);
   if (d.ctl->error & FV_DEVERR_TIMEOUT) return;  // a peer never answered: the step loop is void
-  const int p = (int)((d.ctl->tick + local) & 1);
+  const int p = (int)((d.tick0 + local) & 1);
   const int lane = threadIdx.x & 31;
-  const uint32_t seq = (uint32_t)(d.ctl->tick + local + 1);
+  const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
 
@@ -1990,11 +1993,13 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
   int* sN = reinterpret_cast<int*>(sXm + d.Kp);                    // active ranks
   uint32_t* sBad = reinterpret_cast<uint32_t*>(sN + d.Kp);         // ranks whose windows must leave the counts
   uint32_t* sFloor = sBad + d.Kp;                                  // the units' candidate floors
+  double* sAl = reinterpret_cast<double*>(sFloor + d.Kp);          // the units' scales (Kp is a multiple of 4: aligned)
   const bool query_cta = (int)blockIdx.x < qblocks;
   const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
   const int nthreads = (gridDim.x - qblocks) * blockDim.x;
   const int e0 = ((int)blockIdx.x - qblocks) * (int)blockDim.x + (int)threadIdx.x;
   const float delta = d.ctl->delta;
+  const float eps = d.ctl->eps;
 
   if (query_cta) {
     constexpr int QW = SCAN_THREADS / 32;
@@ -2068,7 +2073,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
           bool have = false;
           for (int j = 0; j < n; ++j) have |= (d.cand_rows[(size_t)cu * CAND_CAP + j] == row);
           if (!have) {
-            const int slot = (n < CAND_CAP) ? n : (int)((d.ctl->tick + local + (unsigned)cu) % CAND_CAP);
+            const int slot = (n < CAND_CAP) ? n : (int)((d.tick0 + local + (unsigned)cu) % CAND_CAP);
             d.cand_rows[(size_t)cu * CAND_CAP + slot] = row;
             d.cand_n[cu] = (n < CAND_CAP) ? n + 1 : CAND_CAP;
           } else {
@@ -2098,7 +2103,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
       double X = 0.0;
       int n = 0;
       if (mu < d.K) unit_stats(d, p, seq, mu, &X, &n);
-      sC[mu] = X * alpha[mu];
+      const double al = alpha[mu];
+      sAl[mu] = al;
+      sC[mu] = X * al;
       sXm[mu] = X;
       sN[mu] = n;
       const uint32_t bad = (mu < d.K && n > 0) ? unit_cancelled(d, p, mu) : 0u;
@@ -2152,24 +2159,32 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(&d.ctl->update_arrivals, 1ull);
+    // (the failure flag of another wait is looked at every 64th poll only: one load per poll keeps the
+    // meeting point's latency at one L2 round trip)
     unsigned polls = 0;
     while (*reinterpret_cast<volatile unsigned long long*>(&d.ctl->update_arrivals) < target) {
-      if (wait_expired(d, polls)) {
-        s_fail = 1;
-        break;
+      if ((++polls & 63u) == 0u) {
+        if (polls > d.spin_limit || (*reinterpret_cast<volatile uint32_t*>(&d.ctl->error) & FV_DEVERR_TIMEOUT)) {
+          atomicOr(&d.ctl->error, FV_DEVERR_TIMEOUT);
+          s_fail = 1;
+          break;
+        }
+        if (polls > 4096u) __nanosleep(128);
       }
     }
     __threadfence();
+    if ((int)blockIdx.x == qblocks) phase_mark(d.ctl, PH_APPLY);  // the clock's "apply" is the second half as this CTA sees it
   }
   __syncthreads();
   if (s_fail || query_cta) return;
 
   // ---- second half: normaliser, step size, the records come back with their scatter term ------------
-  const double* __restrict__ alpha = d.alpha + p * d.Kp;
   double* __restrict__ alpha_next = d.alpha + (p ^ 1) * d.Kp;
   __shared__ float sRed[SCAN_THREADS / 32];
   __shared__ float sScale;
   const bool first = (int)blockIdx.x == qblocks;  // the CTA that writes what there is one of
+  // everything the second half reads from memory leaves together: the maxima, the floors, the records' maximum
+  const uint32_t ncb_bits = (threadIdx.x == 0) ? __ldcg(&d.ncb[p]) : 0u;
   float dense = 0.f;
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     sFloor[mu] = __ldcg(d.cand_floor + mu);
@@ -2179,9 +2194,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
   if (lane == 0) sRed[threadIdx.x >> 5] = dense;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float nc = __uint_as_float(__ldcg(&d.ncb[p]));
+    float nc = __uint_as_float(ncb_bits);
     for (int w = 0; w < SCAN_THREADS / 32; ++w) nc = fmaxf(nc, sRed[w]);
-    const float eps = d.ctl->eps;
     const float s = (d.prec > nc) ? eps / d.prec : eps / nc;  // cuda_funcs.cu:1797-1799
     sScale = s;
     if (first) {
@@ -2193,7 +2207,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
   const float s = sScale;
   for (int mu = threadIdx.x; mu < d.Kp; mu += blockDim.x) {
     const int n = sN[mu];
-    double a = alpha[mu];
+    double a = sAl[mu];
     double coef = 0.0;
     if (n > 0) {
       a = a * (1.0 - (double)s * sXm[mu]);
@@ -2270,7 +2284,7 @@ __global__ void __launch_bounds__(256) k_fold(Dev d, int local) {
   grid_dependency_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) phase_mark(d.ctl, PH_FOLD);
   // `local` = steps already launched in this call: the buffer the next step would read
-  const double* __restrict__ alpha = d.alpha + ((d.ctl->tick + local) & 1) * d.Kp;
+  const double* __restrict__ alpha = d.alpha + ((d.tick0 + local) & 1) * d.Kp;
   const size_t total = (size_t)d.N * d.Kq;
   float vmax = 0.f;
   for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (size_t)gridDim.x * blockDim.x) {
@@ -2652,7 +2666,7 @@ void forward_occupancy(int* fwd, size_t fwd_smem, cudaError_t* err) {
   }
 
 // Multiplies alpha into wt and resets alpha.  `local` = steps already launched
-// since ctl->tick was last advanced.
+// since the running call began (tr->d.tick0).
 int fold_weights(fv_trainer* tr, int local) {
   if (tr->steps_since_fold == 0) return FV_OK;
   k_fold<<<tr->num_sms * 4, 256, 0, tr->stream>>>(tr->d, local);
@@ -2823,6 +2837,7 @@ int loop_begin(fv_trainer* tr, StepLoop& L) {
   for (int b = 0; b < 2 && L.gather_ids; ++b)
     if (!tr->d_idx_local[b]) FV_TRY(dev_alloc(&tr->d_idx_local[b], L.own_ids * STAGE_STEPS));
   tr->d.idx_rstride = (int)L.own_ids;
+  tr->d.tick0 = tr->ticks;
   L.chunk_rstride = (int)L.own_ids;
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, L.first_step, L.eps, tr->delta_now);
   L.launches = 1;
@@ -3176,7 +3191,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   }
   {
     // k_update's CTAs meet inside the kernel, so the whole grid must be resident
-    tr->update_smem = (size_t)d.Kp * (2 * sizeof(double) + sizeof(int) + 2 * sizeof(uint32_t));
+    tr->update_smem = (size_t)d.Kp * (3 * sizeof(double) + sizeof(int) + 2 * sizeof(uint32_t));
     int bps = 0;
     FV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, k_update, SCAN_THREADS, tr->update_smem));
     if (bps > 2) bps = 2;
@@ -3455,6 +3470,7 @@ int fv_trainer_get_weights(fv_trainer* tr, float* w_kn) {
   fv::DeviceGuard guard(tr->device);
   FV_REQUIRE(guard.ok, FV_ERR_CUDA, "cannot select device %d", tr->device);
   const Dev& d = tr->d;
+  tr->d.tick0 = tr->ticks;  // the scales of the step that would come next
   FV_TRY(fold_weights(tr, 0));
   float* tmp = nullptr;
   FV_TRY(dev_alloc(&tmp, (size_t)d.K * d.N));
@@ -3594,6 +3610,7 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
   const Dev& d = tr->d;
   const size_t step_ids = (size_t)d.G * d.B * d.W;
   if (!tr->d_idx_stage[0]) FV_TRY(dev_alloc(&tr->d_idx_stage[0], step_ids * STAGE_STEPS));
+  tr->d.tick0 = tr->ticks;
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, step, 0.f, tr->delta_now);
   k_build_idx_block<<<tr->num_sms * 4, 256, 0, tr->stream>>>(d, step, 1, tr->d_idx_stage[0]);
   // the kernel only writes winners and adds to the xx accumulators, so it can be repeated on the same
