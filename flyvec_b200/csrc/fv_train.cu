@@ -982,10 +982,33 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
         key[u] = (cidx < tot) ? s_ckey[cidx] : 0u;
         cur[u] = key[u] ? __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + (key[u] - 1u)) : 0u;
       }
+      // the claims of a thread leave together: a claim is one compare-and-swap whose answer is either the
+      // expected weight (this record owns the position) or the tag of the record that got there first
+      uint32_t prev[UN];
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
         const uint32_t cidx = (uint32_t)(u * XX_THREADS + threadIdx.x);
-        if (key[u]) claim_position(d, key[u] - 1u, cur[u], s_gbase + cidx, s_cmult[cidx], (uint32_t)EV);
+        prev[u] = cur[u];
+        if (key[u] && (cur[u] & ABS_MASK) <= TAG_BASE)
+          prev[u] = atomicCAS(reinterpret_cast<uint32_t*>(d.wt) + (key[u] - 1u), cur[u], TAG_BASE | (s_gbase + cidx + 1u));
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (!key[u]) continue;
+        const uint32_t cidx = (uint32_t)(u * XX_THREADS + threadIdx.x);
+        const uint32_t pos = key[u] - 1u, mult = s_cmult[cidx];
+        if (prev[u] == cur[u] && (cur[u] & ABS_MASK) <= TAG_BASE) {
+          const int irow = (int)fdiv(pos, d.mKp, d.sKp);
+          d.rec[s_gbase + cidx] = make_uint4(pos, cur[u], __float_as_uint(__ldg(d.f + (irow >= d.V ? irow - d.V : irow))), mult);
+        } else {
+          const uint32_t owner = (prev[u] & 0x007fffffu) - 1u;
+          if ((prev[u] & ABS_MASK) <= TAG_BASE || (prev[u] >> 31) || owner >= (uint32_t)EV) {
+            atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);  // neither the expected weight nor a tag
+          } else {
+            if (mult & 0xffffu) atomicAdd(&d.cnt[owner], (int)(mult & 0xffffu));
+            if (mult >> 16) atomicAdd(&d.cntn[owner], (int)(mult >> 16));
+          }
+        }
       }
     }
     __syncthreads();  // the tables are reused by the next round
