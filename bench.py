@@ -441,7 +441,7 @@ def bench_update_emulated(args):
                       "config": {"workload": f"config 1 shapes, {G} x {B} windows per step"}}))
 
 
-def hash_numbers(args, windows: bool, state: dict | None = None) -> dict:
+def hash_numbers(args, windows: bool, state: dict | None = None, device: int = 0, shard: tuple[int, int] = (0, 1)) -> dict:
     """Device-resident and end-to-end throughput of the token / window hasher.  End to end = the host-buffer
     entry point (fv_hash_tokens / fv_hash_windows) on page-locked ids and codes: upload, kernel and download
     of the whole batch inside the timed call.  `state` carries the inputs from one hash length to the next."""
@@ -453,26 +453,26 @@ def hash_numbers(args, windows: bool, state: dict | None = None) -> dict:
     peak, peak_src = measured_peaks()
     code_b = (K + 7) // 8
     if "h" not in state:
-        state["h"] = engine.Hasher(synth.make_weights(K, 2 * V, seed=WEIGHT_SEED), normalize=True)
+        state["h"] = engine.Hasher(synth.make_weights(K, 2 * V, seed=WEIGHT_SEED), normalize=True, device=device)
         if windows:
-            n = args.items or 16_000_000
+            n = (args.items or 16_000_000) // shard[1]  # this rank's share: the items are independent, nothing is exchanged
             enc, off = synth.make_corpus(max(n // 2, 1_000_000), V, seed=104)
             starts = engine.enumerate_windows(off, W)
-            sel = np.random.default_rng(204).integers(0, len(starts), n)
+            sel = np.random.default_rng(204 + shard[0]).integers(0, len(starts), n)
             ids = _lib.pinned_empty((n, W), np.int32)
             ids[...] = build_idx_host(enc, starts, sel, W, V)
             state["inv_f"] = engine.inverse_frequency(enc, V)
             state["h"].set_inverse_frequency(state["inv_f"])
         else:
-            n = args.items or 1_000_000
+            n = (args.items or 1_000_000) // shard[1]
             ids = _lib.pinned_empty((n,), np.int32)
-            ids[...] = synth.make_hash_ids(n, V, seed=100)
+            ids[...] = synth.make_hash_ids(n, V, seed=100 + shard[0])
             state["inv_f"] = None
         state["ids"], state["n"] = ids, n
         state["codes"] = _lib.pinned_empty((n, code_b), np.uint8)
-        state["d_in"] = engine.DeviceBuffer(ids.nbytes)
+        state["d_in"] = engine.DeviceBuffer(ids.nbytes, device)
         state["d_in"].upload(ids)
-        state["d_out"] = engine.DeviceBuffer(n * code_b)
+        state["d_out"] = engine.DeviceBuffer(n * code_b, device)
     h, ids, n, inv_f, d_in, d_out = state["h"], state["ids"], state["n"], state["inv_f"], state["d_in"], state["d_out"]
     if windows:
         per_item = W * K * 4 + W * 4 + code_b
@@ -485,7 +485,7 @@ def hash_numbers(args, windows: bool, state: dict | None = None) -> dict:
         run()
     times = []
     for _ in range(max(args.steps, 1)):
-        engine.flush_l2(0)
+        engine.flush_l2(device)
         times.append(run())
     t = float(np.mean(times))
     e2e = None
@@ -520,7 +520,29 @@ def hash_numbers(args, windows: bool, state: dict | None = None) -> dict:
 
 
 def bench_hash(args, windows: bool):
-    print(json.dumps(hash_numbers(args, windows)))
+    """One GPU, or `--gpus N` under torch.distributed.run: every rank hashes its own N-th of the items on its
+    own GPU (the items are independent; there is no exchange), the line carries the sum over the ranks."""
+    rank, world, local = dist_env()
+    if world == 1:
+        print(json.dumps(hash_numbers(args, windows)))
+        return
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    dist = Dist(world)
+    args.no_cpu_baseline = True
+    dist.barrier()
+    out = hash_numbers(args, windows, device=local, shard=(rank, world))
+    n_local = out["config"]["items"]
+    t = dist.max(out["ms_per_step"])
+    e2e_t = dist.max(n_local / out["e2e"]["value"])
+    dist.barrier()
+    if rank == 0:
+        out.update(value=world * n_local / (t * 1e-3), ms_per_step=t, n_gpus=world, scaling="weak")
+        out["config"].update(items=world * n_local, parallelism=f"{world} independent shards, no exchange")
+        out["e2e"].update(value=world * n_local / e2e_t, h2d_bytes_per_step=out["e2e"]["h2d_bytes_per_step"] * world,
+                          d2h_bytes_per_step=out["e2e"]["d2h_bytes_per_step"] * world)
+        out["roofline"]["note"] = "per GPU (rank 0)"
+        print(json.dumps(out))
+    dist.close()
 
 
 def cpu_hash_baseline(syn, V, ids, hl, windows, h_f, seconds_limit: float = 15.0):
