@@ -25,11 +25,15 @@
 //                     eight more CTAs copy this rank's winners into the peers' mailboxes, and every
 //                     consumer of a peer's word checks the sequence number the word carries
 //                     (or, without peer access: k_xx, then one NCCL all-gather of the packets)
-//   k_scan       T11  nc = max|D|: exact D at touched positions, column max of |wt|
-//                     over untouched ones (tags read as 0)     (cu_special_reduction.cu:26-99)
-//   k_apply      T12-13 s = eps/max(prec,nc); alpha *= 1 - s*X; touched weights restored
-//                     plus their scatter term                  (cuda_funcs.cu:1797-1799,
+//   k_update     T11  nc = max|D|: exact D at touched positions; the largest |wt| over untouched ones
+//                     from per-unit candidate rows kept from step to step, no pass over the matrix
+//                                                              (cu_special_reduction.cu:26-99)
+//                T12-13 s = eps/max(prec,nc); alpha *= 1 - s*X; touched weights restored plus their
+//                     scatter term                             (cuda_funcs.cu:1797-1799,
 //                                                               cu_special_reduction.cu:316-354)
+//                     (= k_eval + k_apply in one launch; the step after new weights or a fold runs them
+//                     apart with k_colscan and k_collect, which rebuild the candidate rows, in between;
+//                     k_scan is the every-step matrix pass the candidate rows replace)
 #include <dlfcn.h>
 
 #include <algorithm>
@@ -2700,11 +2704,12 @@ int fold_weights(fv_trainer* tr, int local) {
   return FV_OK;
 }
 
-// One global step on tr->stream is four phases, each a kernel (or a short run of kernels):
+// One global step on tr->stream is five phases, each a kernel (or a short run of kernels):
 //   0  forward pass (with NCCL exchange: + k_xx + the all-gather; with emulated ranks: every rank's block in turn)
-//   1  tagging (+ xx_finish and the winner push in its first CTAs)
-//   2  scan
-//   3  apply
+//   1  exchange kernel (only where several ranks share one stream; otherwise part of phase 2)
+//   2  tagging (+ xx_finish and the winner push in its first CTAs)
+//   3  evaluation of the normaliser (k_update does this and phase 4 in one launch)
+//   4  apply
 // `idx` holds this step's input ids (all ranks' windows).  Adds the kernels launched to *launches.
 constexpr int STEP_PHASES = 5;
 int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint64_t* launches) {
