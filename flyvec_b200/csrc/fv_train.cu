@@ -874,19 +874,29 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       const uint32_t pos = (uint32_t)((size_t)(go0 ? i0 : 0) * d.Kp + (go0 ? mu0 : 0));
       uint32_t c0 = 0u;
       if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos);
-      const unsigned live = __ballot_sync(FULL, go0);
-      if (lane == 0) s_scan[wic] = (uint32_t)__popc(live);
-      __syncthreads();
-      uint32_t before = 0u, tot = 0u;
+      if (!d.shard) {
+        // The record of a slot is the slot itself: no numbering, hence no counter to bump and no block barrier
+        // in this kernel's chain of dependent accesses.  Slots that own no position stay holes, of which the
+        // later kernels skip a few more than a compact list would hold (duplicates inside one step of one
+        // rank are rare).  The list is then as long as the step has slots.
+        if (blk == 0 && threadIdx.x == 0) d.ctl->list_count[parity] = (uint32_t)EV;
+        if (go0) claim_position(d, pos, c0, (uint32_t)ev, ev >= E ? 0x10000u : 1u, (uint32_t)EV);
+      } else {
+        // sharded update: the list is sent to the peers, so it is kept compact
+        const unsigned live = __ballot_sync(FULL, go0);
+        if (lane == 0) s_scan[wic] = (uint32_t)__popc(live);
+        __syncthreads();
+        uint32_t before = 0u, tot = 0u;
 #pragma unroll
-      for (int w = 0; w < XX_WARPS; ++w) {
-        const uint32_t c = s_scan[w];
-        before += (w < wic) ? c : 0u;
-        tot += c;
+        for (int w = 0; w < XX_WARPS; ++w) {
+          const uint32_t c = s_scan[w];
+          before += (w < wic) ? c : 0u;
+          tot += c;
+        }
+        if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
+        __syncthreads();
+        if (go0) claim_position(d, pos, c0, s_gbase + before + (uint32_t)__popc(live & ((1u << lane) - 1u)), ev >= E ? 0x10000u : 1u, (uint32_t)EV);
       }
-      if (threadIdx.x == 0) s_gbase = tot ? atomicAdd(&d.ctl->list_count[parity], tot) : 0u;
-      __syncthreads();
-      if (go0) claim_position(d, pos, c0, s_gbase + before + (uint32_t)__popc(live & ((1u << lane) - 1u)), ev >= E ? 0x10000u : 1u, (uint32_t)EV);
     } else {
       constexpr int TAG_TABLE = 2 * TAG_BLOCK;
       constexpr int TAG_TABLE_LOG2 = (UN == 2) ? 11 : 12;
