@@ -455,7 +455,12 @@ __device__ __forceinline__ float weighted_activation(const Dev& d, const double*
 // warp idles while others still have a queue; outputs are keyed by window index, so
 // the schedule does not influence any result.
 //   * rows are gathered four at a time (16 independent 128-bit loads per lane) and
-//     added in position order with packed float adds; padding positions gather an
+//     added in position order with packed float adds (measured inside the step loop at
+//     K=400, w=11: four rows, 128 registers, 16 warps per SM: 24.5 us; six rows, 166
+//     registers, 12 warps: 25.6 us; the whole window, 221 registers, 8 warps: 28.3 us;
+//     three rows, 96 registers, 20 warps: 26.4 us; two rows, 80 registers, 24 warps: 25.7 us;
+//     requesting the next window's first rows ahead of the arg-max: 30.6 us with 168
+//     registers, 31.6 us held to 128 with spills -- warps, not depth, hide the tail); padding positions gather an
 //     all-zero row behind the matrix; lanes past the end of a row re-read its last
 //     16 bytes instead of being predicated off.
 //   * the float arg-max is certified when no other unit comes within theta of the
