@@ -543,8 +543,10 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
     d.xx_wins[mu] = 1u;  // "won a window": the same value from everybody, a plain store will do
   };
 
-  // winners go into this rank's packet as flagged words; the tagging kernel forwards them to the peers
-  // (remote stores issued here would have to drain before this kernel can end)
+  // winners go into this rank's packet as flagged words; the tagging kernel forwards them to the peers.
+  // (Storing them into the peers' memory from here, window by window, was measured on two GPUs: the
+  // remote stores have to drain before this kernel can end -- 29.4 instead of 25.5 us -- and the tagging
+  // kernel only gets 2.4 us shorter.)
   const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   unsigned long long* win_out = (lane == 0) ? packet(d, par, d.rank) : nullptr;
   const int zrow = d.N;  // the all-zero row
