@@ -454,7 +454,7 @@ __device__ __forceinline__ float weighted_activation(const Dev& d, const double*
 // handed out through a counter in the control word, one window per request, so no
 // warp idles while others still have a queue; outputs are keyed by window index, so
 // the schedule does not influence any result.
-//   * rows are gathered four at a time (16 independent 128-bit loads per lane) and
+//   * rows are gathered four at a time (two at a time for K > 640: 16 independent 128-bit loads per lane) and
 //     added in position order with packed float adds (measured inside the step loop at
 //     K=400, w=11: four rows, 128 registers, 16 warps per SM: 24.5 us; six rows, 166
 //     registers, 12 warps: 25.6 us; the whole window, 221 registers, 8 warps: 28.3 us;
@@ -550,7 +550,10 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
   const uint32_t seq = (uint32_t)(d.tick0 + local + 1);
   unsigned long long* win_out = (lane == 0) ? packet(d, par, d.rank) : nullptr;
   const int zrow = d.N;  // the all-zero row
-  const int nbatch = (d.W + 3) >> 2;
+  // rows whose loads are in flight together: 16 x 128-bit loads per lane whatever the width of a row
+  // (K = 1000, w = 15: four rows, 250 registers, 8 warps per SM 94.5 us; two rows, 168 registers, 12 warps 83.7 us)
+  constexpr int RB = (NT >= 6) ? 2 : 4;
+  const int nbatch = (d.W + RB - 1) / RB;
   int qc[NT];
   bool live[NT];  // does this lane own real columns in group t?
 #pragma unroll
@@ -576,15 +579,15 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
 #pragma unroll
       for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = 0ull;
       for (int b = 0; b < nbatch; ++b) {
-        const ulonglong2* __restrict__ r[4];
+        const ulonglong2* __restrict__ r[RB];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int id = __shfl_sync(FULL, row_id, (4 * b + u) & 31);
+        for (int u = 0; u < RB; ++u) {
+          const int id = __shfl_sync(FULL, row_id, (RB * b + u) & 31);
           r[u] = reinterpret_cast<const ulonglong2*>(d.wt + (size_t)id * d.Kp);
         }
-        ulonglong2 v[4][NT];
+        ulonglong2 v[RB][NT];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < RB; ++u)
 #pragma unroll
           for (int t = 0; t < NT; ++t) v[u][t] = __ldg(r[u] + qc[t]);
         if (b == 0) {
@@ -593,7 +596,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
           if (jn < d.B && lane < d.W) n_my = idx_own[(size_t)jn * d.W + lane];
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)  // position order, as the reference adds
+        for (int u = 0; u < RB; ++u)  // position order, as the reference adds
 #pragma unroll
           for (int t = 0; t < NT; ++t) {
             add2(acc[t][0], v[u][t].x);
