@@ -209,6 +209,11 @@ def make_or_load_corpus(ntok: int, rank: int, dist: Dist):
     dist.barrier()
     enc = np.load(base / "enc.npy", mmap_mode="r")
     off = np.load(base / "off.npy", mmap_mode="r")
+    dist.barrier()  # every rank has the files mapped: the names can go, the pages stay until the last unmap
+    if rank == 0:
+        import shutil
+
+        shutil.rmtree(base, ignore_errors=True)
     return enc, off
 
 
