@@ -71,6 +71,38 @@ def test_config1_shapes_free_running_300_steps(built_lib):
     assert_weights_close(Wgpu, Wref)
 
 
+def test_config1_one_whole_epoch(built_lib):
+    """The parity target as stated: config 1 in full -- a 50 M-token corpus, 30 M windows, 3001 minibatches of
+    10000 (the last one partial), one `fv_trainer_run_epoch` with the window order shuffled on the GPU --
+    and the synapses after the epoch within 1e-4 relative of the oracle's, element by element.  The scales
+    are folded 23 times on the way; the oracle needs about 40 s of host time for its 3001 dense steps."""
+    K, V, W, B = 400, 20000, 11, 10000
+    enc, off = synth.make_corpus(50_000_000, V, s=1.0, mean_len=25.0, min_len=W, seed=101)
+    tr = Trainer(hid=K, vocab=V, window=W, batch=B, lr0=2e-4)
+    ns = tr.set_corpus(enc, off)
+    W0 = synth.make_weights(K, 2 * V, seed=1)
+    tr.set_weights(W0)
+    tr.shuffle(201)
+    perm, starts, f = tr.get_permutation(), tr.window_starts(), tr.inverse_frequency()
+    st = tr.run_epoch(0, 1)  # eps = lr0 * (1 - 0/1)
+    Wgpu = tr.get_weights()
+    tr.close()
+    steps = (ns + B - 1) // B
+    assert st["windows"] == ns and steps > 3000
+    runner = c_oracle.StepRunner(K, 2 * V, V, W, B, 1)
+    Wref = W0.copy()
+    for t in range(steps):
+        sel = perm[t * B:(t + 1) * B]
+        idx = orc.build_idx(enc, starts, sel, W, V)
+        if len(sel) < B:
+            idx = np.concatenate([idx, np.full((B - len(sel), W), -1, np.int32)])
+        runner.step(Wref, idx[None], [len(sel)], f, np.float32(2e-4))
+    assert not np.array_equal(Wref, W0)
+    assert_weights_close(Wgpu, Wref)
+    big = np.abs(Wref) > 1e-2  # away from zero the bound is purely relative
+    assert (np.abs(Wgpu[big].astype(np.float64) - Wref[big]) / np.abs(Wref[big])).max() < 1e-4
+
+
 @pytest.mark.parametrize("world,variant", [(4, 0), (8, 0), (8, 3), (16, 0)])
 def test_config2_shapes_emulated_ranks(built_lib, world, variant):
     """Config 2's global step (world x 10000 windows): every rank's block on one GPU, which makes
