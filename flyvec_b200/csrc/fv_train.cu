@@ -82,6 +82,9 @@ struct StepCtl {
 enum Phase { PH_OTHER = 0, PH_FORWARD = 1, PH_XX = 2, PH_WAIT = 3, PH_TAG = 4, PH_SCAN = 5, PH_APPLY = 6, PH_FOLD = 7 };
 
 // Everything a kernel needs, passed by value.
+constexpr int HOT_TOKENS = 32;            // most frequent tokens whose two rows (context, target) are hot
+constexpr int HOT_ROWS = 2 * HOT_TOKENS;
+
 struct Dev {
   int K, Kp, Kq, V, N, W, B, G, rank, P, XO;  // P = packet words, XO = offset of xx inside a packet
   // Steps this trainer had executed when the running call began.  A kernel's step number is tick0 + local:
@@ -116,7 +119,17 @@ struct Dev {
   float fmax;      // upper bound of the inverse frequencies (scales the fixed-point unit)
   int32_t* cnt;    // per record: later comers that add +f_i (first winner's row)
   int32_t* cntn;   // per record: later comers that add -delta*f_i (second winner's row); null without delta
-  uint4* rec;      // [G*B*w] touched-position records {position, parked weight bits, 1/count bits, 0}
+  uint4* rec;      // [rec_cap] touched-position records {position, parked weight bits, 1/count bits, multiplicities}
+  int rec_cap;     // records the list can hold: every (window, position) of a step plus one per hot pair
+  // Hot rows: the rows of the most frequent tokens.  A (hot row, unit) pair is asked for by hundreds of windows
+  // of a step; claimed one by one, those requests queue at one L2 address.  Instead k_forward counts them per
+  // pair as it finds the winners (fire-and-forget reductions spread over the whole pass) and the tagging kernel
+  // claims every non-empty pair once, with its count.  Which rows are "hot" never changes a result.
+  int nhot;                  // hot rows in use by the running step loop (0: off)
+  const int8_t* hotidx;      // [N+1] hot-row number of a matrix row, or -1
+  const int32_t* hot_rows;   // [nhot] matrix row of a hot-row number
+  uint32_t* hot_cnt;         // [HOT_ROWS][Kp] windows that want +f_i at (hot row, unit); zero between steps
+  uint32_t* hot_cntn;        // the same for the second winner's -delta*f_i; null without delta
   uint32_t* colmax;
   uint32_t* ncb;
   // Candidate rows of the column maxima (see k_eval): per unit up to CAND_CAP rows and a floor that bounds
@@ -583,6 +596,8 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
     int winner = -1;
     float awv = 0.f;
     int n_my = -1;
+    // hot-row number of this lane's input row; used once the winner is known
+    const int hrow = (d.nhot && my >= 0) ? (int)__ldg(d.hotidx + my) : -1;
     if (__shfl_sync(FULL, my, 0) != -2) {  // -2 marks a window past the end of the order
       const int row_id = (my < 0) ? zrow : my;  // lanes >= W hold -1
       unsigned long long acc[NT][2];
@@ -684,6 +699,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
         }
         const float aw2 = weighted_activation(d, alpha, my, second, lane);
         if (win_out) win_out[d.MO + j] = pk_word((uint32_t)second, seq);
+        if (hrow >= 0 && second >= 0) atomicAdd(d.hot_cntn + (size_t)hrow * d.Kp + second, 1u);
         if (lane == 0 && second >= 0) xx_add(second, -d.ctl->delta * aw2, j);  // cuda_funcs.cu:726-735
       }
     } else {
@@ -699,6 +715,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(Dev d, int local, const
       if (d.has_delta && winner < 0) win_out[d.MO + j] = pk_word((uint32_t)-1, seq);
     }
     if (lane == 0 && winner >= 0) xx_add(winner, awv, j);
+    if (hrow >= 0 && winner >= 0) atomicAdd(d.hot_cnt + (size_t)hrow * d.Kp + winner, 1u);
     j = jn;
     my = n_my;
   }
@@ -837,6 +854,44 @@ __device__ __forceinline__ void claim_position(const Dev& d, uint32_t pos, uint3
     c = prev;
   }
 }
+// Hot pair v = (hot row, unit): takes what k_forward counted for it (and clears the counters for the next step)
+// and claims the position once.  The claimant's record says "one request of each kind present"; the rest of the
+// count goes into the counters that later comers use, so that no multiplicity field can overflow.
+__device__ __forceinline__ void claim_hot_pair(const Dev& d, int v, uint32_t slot, uint32_t EVX) {
+  uint32_t c1 = __ldcg(d.hot_cnt + v);
+  uint32_t c2 = d.has_delta ? __ldcg(d.hot_cntn + v) : 0u;
+  if (!(c1 | c2)) return;
+  if (c1) d.hot_cnt[v] = 0u;
+  if (c2) d.hot_cntn[v] = 0u;
+  const int h = (int)fdiv((uint32_t)v, d.mKp, d.sKp);
+  const int mu = v - h * d.Kp;
+  const uint32_t pos = (uint32_t)((size_t)__ldg(d.hot_rows + h) * d.Kp + mu);
+  uint32_t* addr = reinterpret_cast<uint32_t*>(d.wt) + pos;
+  uint32_t c = __ldcg(addr);
+  uint32_t owner = slot;
+  for (;;) {
+    if ((c & ABS_MASK) > TAG_BASE) {
+      owner = (c & 0x007fffffu) - 1u;
+      if ((c >> 31) || owner >= EVX) {
+        atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);
+        return;
+      }
+      break;
+    }
+    const uint32_t prev = atomicCAS(addr, c, TAG_BASE | (slot + 1u));
+    if (prev == c) {
+      const int irow = __ldg(d.hot_rows + h);
+      const uint32_t mult = (c1 ? 1u : 0u) | (c2 ? 0x10000u : 0u);
+      d.rec[slot] = make_uint4(pos, c, __float_as_uint(__ldg(d.f + (irow >= d.V ? irow - d.V : irow))), mult);
+      c1 -= c1 ? 1u : 0u;
+      c2 -= c2 ? 1u : 0u;
+      break;
+    }
+    c = prev;
+  }
+  if (c1) atomicAdd(&d.cnt[owner], (int)c1);
+  if (c2) atomicAdd(&d.cntn[owner], (int)c2);
+}
 template <int UN>  // slots per thread and block round: a CTA deduplicates UN * XX_THREADS slots together
 __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const int32_t* __restrict__ idx, int xx_ctas, int push_ctas) {
   grid_dependency_wait();
@@ -867,8 +922,10 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
   const int E = d.G * d.B * d.W;
   const int EV = E * (1 + d.has_delta);
   constexpr int TAG_BLOCK = UN * XX_THREADS;
-  const int nblocks = (EV + TAG_BLOCK - 1) / TAG_BLOCK;
+  const int nblocks = (EV + (UN == 1 ? d.nhot * d.Kp : 0) + TAG_BLOCK - 1) / TAG_BLOCK;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  const bool emulate = (d.flags & FV_FLAG_EMULATE_RANKS) != 0;
+  auto slot_rank = [&](int e) -> int { return (int)fdiv(fdiv((uint32_t)e, d.mW, d.sW), d.mB, d.sB); };
   // packet word with the winner of virtual slot ev (which must be < EV)
   auto winner_word = [&](int ev) -> const unsigned long long* {
     const int kind = (ev >= E) ? 1 : 0;
@@ -891,12 +948,16 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       // the CTA with a ballot/prefix (one counter bump per CTA round) and claim directly
       // the winner's address does not depend on the id: both loads leave together
       const int ev = blk * TAG_BLOCK + threadIdx.x;
+      // behind the slots, one thread per hot pair: what k_forward counted for it is claimed once, with the count
+      if (ev >= EV && ev < EV + d.nhot * d.Kp) claim_hot_pair(d, ev - EV, (uint32_t)ev, (uint32_t)(EV + d.nhot * d.Kp));
       const int i0 = (ev < EV) ? step_id(d, idx, ev >= E ? ev - E : ev) : -1;
       const unsigned long long* ww = winner_word(ev < EV ? ev : 0);
       const unsigned long long w0 = load_relaxed_sys64(ww);
       const int mu0 = (ev < EV) ? winner_from(ww, w0) : -1;
-      const bool go0 = i0 >= 0 && mu0 >= 0 &&
-                       !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
+      bool go0 = i0 >= 0 && mu0 >= 0 &&
+                 !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
+      // a hot row's slot of a window k_forward ran here is in the pair's count already
+      if (go0 && d.nhot && __ldg(d.hotidx + i0) >= 0 && (emulate || slot_rank(ev >= E ? ev - E : ev) == d.rank)) go0 = false;
       const uint32_t pos = (uint32_t)((size_t)(go0 ? i0 : 0) * d.Kp + (go0 ? mu0 : 0));
       uint32_t c0 = 0u;
       if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos);
@@ -905,8 +966,8 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
         // in this kernel's chain of dependent accesses.  Slots that own no position stay holes, of which the
         // later kernels skip a few more than a compact list would hold (duplicates inside one step of one
         // rank are rare).  The list is then as long as the step has slots.
-        if (blk == 0 && threadIdx.x == 0) d.ctl->list_count[parity] = (uint32_t)EV;
-        if (go0) claim_position(d, pos, c0, (uint32_t)ev, ev >= E ? 0x10000u : 1u, (uint32_t)EV);
+        if (blk == 0 && threadIdx.x == 0) d.ctl->list_count[parity] = (uint32_t)(EV + d.nhot * d.Kp);
+        if (go0) claim_position(d, pos, c0, (uint32_t)ev, ev >= E ? 0x10000u : 1u, (uint32_t)(EV + d.nhot * d.Kp));
       } else {
         // sharded update: the list is sent to the peers, so it is kept compact
         const unsigned live = __ballot_sync(FULL, go0);
@@ -1051,7 +1112,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
         }
       }
     }
-    __syncthreads();  // the tables are reused by the next round
+    if (UN != 1 || d.shard) __syncthreads();  // the tables are reused by the next round
   }
 }
 
@@ -1286,7 +1347,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_scan(Dev d, int local, cons
     if (bad) s_any_bad = 1;
   }
   __syncthreads();
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)d.rec_cap);
   const int nthreads = gridDim.x * blockDim.x;
   const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
   if (s_any_bad) {
@@ -1472,7 +1533,7 @@ __device__ __forceinline__ void publish_partial(const Dev& d, int local, int p) 
   __syncthreads();
   if (threadIdx.x < d.G) {
     const unsigned long long seq = (unsigned)(d.tick0 + local + 1);
-    const unsigned nrec = min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+    const unsigned nrec = min(d.ctl->list_count[p], (uint32_t)d.rec_cap);
     unsigned long long* words = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_NC);
     store_relaxed_sys64(words + p * MAX_RANKS + d.rank, (seq << 32) | __float_as_uint(s_pub[0]));
     unsigned long long* outw = reinterpret_cast<unsigned long long*>(d.peers[threadIdx.x] + WORD_OUT);
@@ -1597,7 +1658,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_eval(Dev d, int local, cons
   uint32_t* sBad = reinterpret_cast<uint32_t*>(sN + d.Kp) + d.Kp;  // same layout as k_scan (its column maxima lie between)
   const double* __restrict__ alpha = d.alpha + p * d.Kp;
   __shared__ int s_any_bad;
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)d.rec_cap);
   const int nthreads = (gridDim.x - qblocks) * blockDim.x;
   const int e0 = (blockIdx.x - qblocks) * blockDim.x + threadIdx.x;
   constexpr int TS = 4;
@@ -1909,9 +1970,8 @@ __global__ void __launch_bounds__(256) k_apply(Dev d, int local, const int32_t* 
   if (blockIdx.x == 0 && threadIdx.x == 0) d.ncb[p ^ 1] = 0u;
   __syncthreads();
 
-  const int E = d.G * d.B * d.W;
   uint32_t vmax = 0u;
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(E * (1 + d.has_delta)));
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)d.rec_cap);
   const float delta = d.ctl->delta;
   if (blockIdx.x == 0 && threadIdx.x == 0) d.ctl->list_count[p ^ 1] = 0u;  // the next step counts from zero
   const int nthreads = gridDim.x * blockDim.x;
@@ -2058,7 +2118,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) k_update(Dev d, int local, co
   uint32_t* sFloor = sBad + d.Kp;                                  // the units' candidate floors
   double* sAl = reinterpret_cast<double*>(sFloor + d.Kp);          // the units' scales (Kp is a multiple of 4: aligned)
   const bool query_cta = (int)blockIdx.x < qblocks;
-  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)(d.G * d.B * d.W * (1 + d.has_delta)));
+  const int nrec = (int)min(d.ctl->list_count[p], (uint32_t)d.rec_cap);
   const int nthreads = (gridDim.x - qblocks) * blockDim.x;
   const int e0 = ((int)blockIdx.x - qblocks) * (int)blockDim.x + (int)threadIdx.x;
   const float delta = d.ctl->delta;
@@ -2550,6 +2610,47 @@ __global__ void __launch_bounds__(512) k_count_tokens(const int32_t* __restrict_
       if (s_bins[v]) atomicAdd(&counts[v], (unsigned long long)s_bins[v]);
   }
 }
+// The HOT_TOKENS most frequent tokens (smallest positive 1/count; ties by id) and the hot-row numbers of their
+// context row (token) and target row (V + token).  One CTA; `picked` receives the number of hot rows.
+__global__ void __launch_bounds__(1024) k_pick_hot(const float* __restrict__ f, int V, int8_t* __restrict__ hotidx,
+                                                   int32_t* __restrict__ hot_rows, int* __restrict__ picked) {
+  __shared__ unsigned long long s_best[32];
+  __shared__ unsigned long long s_last;
+  const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_last = 0ull;
+  __syncthreads();
+  int n = 0;
+  for (int h = 0; h < HOT_TOKENS; ++h) {
+    const unsigned long long last = s_last;
+    unsigned long long best = ~0ull;  // key = (bits of 1/count, id): the smallest key above the last pick
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      const float x = f[v];
+      if (!(x > 0.f)) continue;
+      const unsigned long long key = ((unsigned long long)__float_as_uint(x) << 32) | (unsigned)(v + 1);
+      if (key > last && key < best) best = key;
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (lane == 0) s_best[wic] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w) best = min(best, s_best[w]);
+      if (best != ~0ull) {
+        const int tok = (int)(unsigned)(best & 0xffffffffull) - 1;
+        hotidx[tok] = (int8_t)h;
+        hotidx[V + tok] = (int8_t)(HOT_TOKENS + h);
+        hot_rows[h] = tok;
+        hot_rows[HOT_TOKENS + h] = V + tok;
+      }
+      s_last = best;
+    }
+    __syncthreads();
+    if (s_last == ~0ull) break;
+    ++n;
+  }
+  // fewer tokens than HOT_TOKENS: the unused hot-row numbers point at rows whose counters nobody bumps
+  if (threadIdx.x == 0) *picked = n;
+}
 __global__ void k_inverse_counts(const unsigned long long* __restrict__ counts, int V, int saturate, float* __restrict__ f) {
   for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x) {
     unsigned long long c = counts[v];
@@ -2637,6 +2738,14 @@ struct fv_trainer {
   int32_t* d_cnt = nullptr;
   int32_t* d_cntn = nullptr;
   uint4* d_rec = nullptr;
+  int8_t* d_hotidx = nullptr;
+  int32_t* d_hot_rows = nullptr;
+  uint32_t* d_hot_cnt = nullptr;
+  uint32_t* d_hot_cntn = nullptr;
+  int hot_rows_picked = 0;       // hot rows the corpus provided (<= HOT_ROWS)
+  bool hot_pairs = true;         // option "hot_pairs"
+  bool hot_fits = false;         // the step's slots and the hot pairs fit one round of k_tag<1>
+  int tag_hot_grid = 0;
   uint32_t* d_colmax = nullptr;
   uint32_t* d_ncb = nullptr;
   double* d_stat_x = nullptr;
@@ -2801,7 +2910,7 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     if (tr->tag_un == 2 && !own) {
       launch_pdl(k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx, xx_ctas, push_ctas);
     } else if (u == 1) {
-      launch_pdl(k_tag<1>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
+      launch_pdl(k_tag<1>, (d.nhot ? tr->tag_hot_grid + xx_ctas + push_ctas : grid), XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
     } else {
 #define FV_TAG_BATCH(U_)                                                                                                      \
   (own ? launch_pdl(k_tag_batch<U_, true>, grid, XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas)   \
@@ -2902,6 +3011,7 @@ int loop_begin(fv_trainer* tr, StepLoop& L) {
     if (!tr->d_idx_local[b]) FV_TRY(dev_alloc(&tr->d_idx_local[b], L.own_ids * STAGE_STEPS));
   tr->d.idx_rstride = (int)L.own_ids;
   tr->d.tick0 = tr->ticks;
+  tr->d.nhot = (tr->hot_pairs && tr->hot_fits && !tr->d.shard) ? tr->hot_rows_picked : 0;
   L.chunk_rstride = (int)L.own_ids;
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, L.first_step, L.eps, tr->delta_now);
   L.launches = 1;
@@ -3070,7 +3180,7 @@ void free_all(fv_trainer* tr) {
     if (tr->peer_mail[r] && r != tr->d.rank) cudaIpcCloseMemHandle(tr->peer_mail[r]);
   if (tr->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(tr->comm);
   void* bufs[] = {tr->d_wt,  tr->d_alpha, tr->d_tokens, tr->d_wstart, tr->d_perm,   tr->d_f,
-                  tr->d_mail, tr->d_peer_table, tr->d_xx_acc, tr->d_xx_wins, tr->d_cnt, tr->d_cntn, tr->d_rec,  tr->d_colmax, tr->d_ncb, tr->d_stat_x, tr->d_stat_n, tr->d_cand_rows, tr->d_cand_n, tr->d_cand_floor, tr->d_cand_unc, tr->d_colarg, tr->d_ctl,
+                  tr->d_mail, tr->d_peer_table, tr->d_xx_acc, tr->d_xx_wins, tr->d_cnt, tr->d_cntn, tr->d_rec, tr->d_hotidx, tr->d_hot_rows, tr->d_hot_cnt, tr->d_hot_cntn, tr->d_colmax, tr->d_ncb, tr->d_stat_x, tr->d_stat_n, tr->d_cand_rows, tr->d_cand_n, tr->d_cand_floor, tr->d_cand_unc, tr->d_colarg, tr->d_ctl,
                   tr->d_log, tr->d_idx_stage[0], tr->d_idx_stage[1], tr->d_idx_local[0], tr->d_idx_local[1]};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -3110,6 +3220,10 @@ void choose_tag_variant(fv_trainer* tr, int force_un) {
   if (force_un == 1) u = 1;
   tr->tag_batch_u = u;
   tr->tag_batch_grid = grid_for(E, XX_THREADS * u, (int)resident);
+  // hot pairs ride behind the slots of the one-slot-per-thread kernel while one round still covers them all
+  const size_t with_hot = E + (size_t)HOT_ROWS * d.Kp;
+  tr->hot_fits = tr->tag_un == 1 && u == 1 && (with_hot + XX_THREADS - 1) / XX_THREADS <= resident;
+  tr->tag_hot_grid = grid_for(with_hot, XX_THREADS, (int)resident);
 }
 
 int create_impl(const fv_config* cfg, fv_trainer* tr) {
@@ -3162,7 +3276,7 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.flags = cfg->flags;
   tr->NT = (d.Kq + 31) / 32;
 
-  const size_t E = (size_t)d.G * d.B * d.W * (1 + (cfg->delta != 0.0f ? 1 : 0));  // virtual slots: both kinds with delta
+  size_t E = (size_t)d.G * d.B * d.W * (1 + (cfg->delta != 0.0f ? 1 : 0));  // virtual slots: both kinds with delta
   FV_TRY(dev_alloc(&tr->d_wt, ((size_t)d.N + 1) * d.Kp));  // one extra all-zero row for padding positions
   FV_TRY(dev_alloc(&tr->d_alpha, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_f, (size_t)d.V));
@@ -3170,12 +3284,28 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.inbox_cap = (d.G > 1 && !d.has_delta) ? (size_t)d.G * d.B * d.W : 0;  // a sender's list can hold every slot of a step
   tr->mail_words = d.inbox_off + 2 * (size_t)d.G * d.inbox_cap;
   FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
+  const size_t hot_pairs = (size_t)HOT_ROWS * d.Kp;
+  E += hot_pairs;  // records: one per slot, one per hot pair
+  d.rec_cap = (int)E;
   FV_TRY(dev_alloc(&tr->d_cnt, E));
   if (cfg->delta != 0.0f) {
     FV_TRY(dev_alloc(&tr->d_cntn, E));
     FV_CUDA(cudaMemsetAsync(tr->d_cntn, 0, E * sizeof(int32_t), tr->stream));
+    FV_TRY(dev_alloc(&tr->d_hot_cntn, hot_pairs));
+    FV_CUDA(cudaMemsetAsync(tr->d_hot_cntn, 0, hot_pairs * sizeof(uint32_t), tr->stream));
   }
   FV_TRY(dev_alloc(&tr->d_rec, E));
+  FV_TRY(dev_alloc(&tr->d_hotidx, (size_t)d.N + 1));
+  FV_TRY(dev_alloc(&tr->d_hot_rows, (size_t)HOT_ROWS));
+  FV_TRY(dev_alloc(&tr->d_hot_cnt, hot_pairs));
+  FV_CUDA(cudaMemsetAsync(tr->d_hotidx, 0xff, (size_t)d.N + 1, tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_hot_rows, 0, HOT_ROWS * sizeof(int32_t), tr->stream));
+  FV_CUDA(cudaMemsetAsync(tr->d_hot_cnt, 0, hot_pairs * sizeof(uint32_t), tr->stream));
+  d.hotidx = tr->d_hotidx;
+  d.hot_rows = tr->d_hot_rows;
+  d.hot_cnt = tr->d_hot_cnt;
+  d.hot_cntn = tr->d_hot_cntn;
+  d.nhot = 0;
   FV_TRY(dev_alloc(&tr->d_colmax, 2 * (size_t)d.Kp));
   FV_TRY(dev_alloc(&tr->d_ncb, 2));
   FV_TRY(dev_alloc(&tr->d_cand_rows, (size_t)d.Kp * CAND_CAP));
@@ -3263,6 +3393,8 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
     tr->update_grid = (bps >= 1 && tr->num_sms * bps > qblocks + tr->num_sms / 2) ? tr->num_sms * bps : 0;
     const char* e = getenv("FV_FUSED_UPDATE");
     tr->fused_update = e ? atoi(e) != 0 : true;
+    const char* hp = getenv("FV_HOT_PAIRS");
+    tr->hot_pairs = hp ? atoi(hp) != 0 : true;
   }
   FV_TRY(dev_alloc(&tr->d_xx_acc, 2 * (size_t)XX_SLOTS * d.Kp));
   FV_TRY(dev_alloc(&tr->d_xx_wins, (size_t)d.Kp));
@@ -3332,6 +3464,7 @@ int fv_trainer_destroy(fv_trainer* tr) {
 }
 
 // Tokens and chunk boundaries go up once; window table and 1/count are made on the GPU.
+static int pick_hot_rows(fv_trainer* tr);
 static int prepare_corpus_on_device(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
                                     uint64_t noffsets) {
   Dev& d = tr->d;
@@ -3414,6 +3547,25 @@ static int prepare_corpus_on_device(fv_trainer* tr, const int32_t* enc, uint64_t
   d.Ns = ns;
   d.ntok = ntok;
   tr->have_corpus = true;
+  return pick_hot_rows(tr);
+}
+
+// Chooses the hot rows from the inverse frequencies now on the device.
+static int pick_hot_rows(fv_trainer* tr) {
+  const Dev& d = tr->d;
+  int* d_n = nullptr;
+  FV_CUDA(cudaMalloc((void**)&d_n, sizeof(int)));
+  cudaMemsetAsync(tr->d_hotidx, 0xff, (size_t)d.N + 1, tr->stream);
+  cudaMemsetAsync(tr->d_hot_rows, 0, HOT_ROWS * sizeof(int32_t), tr->stream);
+  k_pick_hot<<<1, 1024, 0, tr->stream>>>(tr->d_f, d.V, tr->d_hotidx, tr->d_hot_rows, d_n);
+  int n = 0;
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&n, d_n, sizeof(int), cudaMemcpyDeviceToHost, tr->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(tr->stream);
+  cudaFree(d_n);
+  FV_CUDA(e);
+  // hot-row numbers are h (context row) and HOT_TOKENS + h (target row): the whole range is in use as soon as one token is
+  tr->hot_rows_picked = n > 0 ? HOT_ROWS : 0;
   return FV_OK;
 }
 
@@ -3443,7 +3595,7 @@ static int upload_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, cons
   d.Ns = ns;
   d.ntok = ntok;
   tr->have_corpus = true;
-  return FV_OK;
+  return pick_hot_rows(tr);
 }
 
 int fv_trainer_set_corpus(fv_trainer* tr, const int32_t* enc, uint64_t ntok, const uint64_t* offsets,
@@ -3682,6 +3834,7 @@ int fv_trainer_time_forward(fv_trainer* tr, uint64_t step, uint32_t reps, double
   // keep their winners to this rank: a peer must not find words of a step that never ran.
   uint32_t* const* const peers = tr->d.peers;
   tr->d.peers = nullptr;
+  tr->d.nhot = 0;  // nobody would collect the counts; the next step loop sets it again
   for (uint32_t r = 0; r < 3; ++r) FV_DISPATCH_NT(tr->NT, launch_forward, tr, (int)(r & 1), tr->d_idx_stage[0]);
   FV_CUDA(cudaEventRecord(tr->ev_begin, tr->stream));
   for (uint32_t r = 0; r < reps; ++r) FV_DISPATCH_NT(tr->NT, launch_forward, tr, (int)((r + 1) & 1), tr->d_idx_stage[0]);
@@ -3831,12 +3984,18 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
       const size_t E = (size_t)tr->d.G * tr->d.B * tr->d.W * (1 + tr->d.has_delta);
       tr->tag_batch_u = (int)value;
       tr->tag_batch_grid = grid_for(E, XX_THREADS * tr->tag_batch_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
+      if (tr->tag_batch_u != 1) tr->hot_fits = false;  // hot pairs are claimed by the one-slot-per-thread kernel only
     }
     return FV_OK;
   }
   if (strcmp(key, "fused_update") == 0) {
     FV_REQUIRE(value == 0.0 || value == 1.0, FV_ERR_INVALID, "fused_update must be 0 or 1, got %g", value);
     tr->fused_update = value != 0.0;
+    return FV_OK;
+  }
+  if (strcmp(key, "hot_pairs") == 0) {
+    FV_REQUIRE(value == 0.0 || value == 1.0, FV_ERR_INVALID, "hot_pairs must be 0 or 1, got %g", value);
+    tr->hot_pairs = value != 0.0;
     return FV_OK;
   }
   if (strcmp(key, "colmax_lists") == 0) {
