@@ -204,8 +204,9 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *                  (FV_FUSED_UPDATE=0 in the environment selects the same);
  *   "hot_pairs"    1 (default): requests for a (row of one of the 32 most frequent tokens, unit) pair are counted
  *                  by the forward pass and claimed once per pair by the tagging kernel, instead of queueing one by
- *                  one at the pair's address; used while a step's slots fit one round of the one-slot-per-thread
- *                  tagging kernel (one GPU at the benchmark's shapes); 0: every request claims for itself
+ *                  one at the pair's address; used where a step's slots fit one round of the one-slot-per-thread
+ *                  tagging kernel (one or two GPUs at the benchmark's shapes; a rank counts the windows of its
+ *                  own forward pass); 0: every request claims for itself
  *                  (FV_HOT_PAIRS=0 in the environment selects the same);
  *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
  *   "loopback_peers" 1: test aid -- every peer's mailbox is mapped onto this rank's own, so a peer's

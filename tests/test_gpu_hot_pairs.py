@@ -85,3 +85,26 @@ def test_config1_shapes_200_steps(built_lib):
     Wb, ncb, sb = run_single(p, B, steps, False, lr0=2e-4)
     np.testing.assert_array_equal(nca, ncb)
     np.testing.assert_array_equal(Wa, Wb)
+
+
+def test_two_ranks_of_config1_take_a_second_round_for_the_pairs(built_lib):
+    """Two ranks of 10000 windows fill the resident threads of the tagging kernel with slots alone; the hot
+    pairs then cost some CTAs a second block round.  Same bits as claiming one by one."""
+    K, V, W, B, steps = 400, 20000, 11, 10000, 12
+    p = skewed_problem(K, V, W, 1_500_000, 57, 1.0)
+    assert len(p["starts"]) >= steps * B * 2
+    out = []
+    for hot in (1, 0):
+        g = TrainerGroup([0, 0], hid=K, vocab=V, window=W, batch=B, lr0=2e-4, shard=False)
+        for t in g.ranks:
+            t.set_option("hot_pairs", hot)
+        g.set_corpus(p["enc"], p["off"])
+        g.set_weights(p["W0"])
+        g.set_permutation(p["perm"])
+        st = g.run_steps(0, steps, np.float32(2e-4), want_log=True)
+        W0, W1 = g.get_weights(0), g.get_weights(1)
+        np.testing.assert_array_equal(W0, W1)
+        out.append((W0, st[0]["nc"]))
+        g.close()
+    np.testing.assert_array_equal(out[0][1], out[1][1])
+    np.testing.assert_array_equal(out[0][0], out[1][0])
