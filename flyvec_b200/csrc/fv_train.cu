@@ -130,6 +130,10 @@ struct Dev {
   const int32_t* hot_rows;   // [nhot] matrix row of a hot-row number
   uint32_t* hot_cnt;         // [HOT_ROWS][Kp] windows that want +f_i at (hot row, unit); zero between steps
   uint32_t* hot_cntn;        // the same for the second winner's -delta*f_i; null without delta
+  int hot_x;                 // several ranks with peer mailboxes: the counts of all ranks travel (hotbox), so that
+                             // every hot-row slot of every rank is skipped; else a rank counts what its own forward pass saw
+  size_t hot_off;            // word offset of the hotbox inside the mailbox: u64 [2][G][HC] flagged count words
+  int HC;                    // count words per rank and step: HOT_ROWS * Kp, twice that with delta
   uint32_t* colmax;
   uint32_t* ncb;
   // Candidate rows of the column maxima (see k_eval): per unit up to CAND_CAP rows and a floor that bounds
@@ -185,6 +189,10 @@ constexpr uint32_t ENTRY_VALID = 0x80000000u;
 constexpr uint32_t ENTRY_HOLE = 0xffffffffu;
 __device__ __forceinline__ unsigned long long* inbox(const Dev& d, const uint32_t* mail, int sender) {
   return reinterpret_cast<unsigned long long*>(const_cast<uint32_t*>(mail) + d.inbox_off) + (size_t)sender * d.inbox_cap;
+}
+// Hot-pair counts of `sender` for the step of the given parity inside mailbox `mail`: HC flagged words.
+__device__ __forceinline__ unsigned long long* hotbox(const Dev& d, const uint32_t* mail, int parity, int sender) {
+  return reinterpret_cast<unsigned long long*>(const_cast<uint32_t*>(mail) + d.hot_off) + ((size_t)parity * d.G + sender) * d.HC;
 }
 __device__ __forceinline__ uint32_t fdiv(uint32_t n, uint32_t m, uint32_t s) {
   return (uint32_t)(((unsigned long long)n * m) >> s);
@@ -798,6 +806,24 @@ __device__ __forceinline__ void push_winners(const Dev& d, int parity, int cta, 
     }
   }
 }
+// The same CTAs then send what this rank's forward pass counted for the hot pairs: every count (zero or not)
+// as a flagged word into every rank's hotbox, this rank's own included, and the counters start the next
+// step at zero.
+__device__ __forceinline__ void push_hot(const Dev& d, int parity, uint32_t seq, int cta, int nctas) {
+  const int n = d.nhot * d.Kp;  // pairs per kind
+  const int n2 = d.HC >> 1;     // two words at a time
+  const int per = (n2 + nctas - 1) / nctas;
+  const int hi = min((cta + 1) * per, n2);
+  for (int i = cta * per + threadIdx.x; i < hi; i += XX_THREADS) {
+    const int v = 2 * i;  // n is even (Kp is a multiple of 4), so a pair of words never straddles the kinds
+    uint32_t* src = (v < n) ? d.hot_cnt + v : d.hot_cntn + (v - n);
+    const uint2 c = *reinterpret_cast<const uint2*>(src);
+    if (c.x | c.y) *reinterpret_cast<uint2*>(src) = make_uint2(0u, 0u);
+    const ulonglong2 w = make_ulonglong2(pk_word(c.x, seq), pk_word(c.y, seq));
+    for (int r = 0; r < d.G; ++r)
+      *reinterpret_cast<ulonglong2*>(hotbox(d, r == d.rank ? d.mail : d.peers[r], parity, d.rank) + v) = w;
+  }
+}
 // CTA 0 finishes xx; further CTAs (when launched) push this rank's winners to the peers.  The tagging
 // kernel does both in its first CTAs; this kernel does them alone where xx must be complete before an
 // all-gather, and where several ranks share one stream, so that every rank's words are out before any
@@ -810,6 +836,7 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
     xx_finish(d, local);
   } else {
     push_winners(d, (int)((d.tick0 + local) & 1), blockIdx.x - 1, gridDim.x - 1);
+    if (d.hot_x) push_hot(d, (int)((d.tick0 + local) & 1), (uint32_t)(d.tick0 + local + 1), blockIdx.x - 1, gridDim.x - 1);
   }
 }
 
@@ -857,12 +884,41 @@ __device__ __forceinline__ void claim_position(const Dev& d, uint32_t pos, uint3
 // Hot pair v = (hot row, unit): takes what k_forward counted for it (and clears the counters for the next step)
 // and claims the position once.  The claimant's record says "one request of each kind present"; the rest of the
 // count goes into the counters that later comers use, so that no multiplicity field can overflow.
-__device__ __forceinline__ void claim_hot_pair(const Dev& d, int v, uint32_t slot, uint32_t EVX) {
-  uint32_t c1 = __ldcg(d.hot_cnt + v);
-  uint32_t c2 = d.has_delta ? __ldcg(d.hot_cntn + v) : 0u;
+// What the forward passes counted for hot pair v: this trainer's own counters (cleared here), or, with the
+// exchange, the sum of every rank's flagged word (bounded wait for a word that is still on its way).
+__device__ __forceinline__ void hot_pair_counts(const Dev& d, int parity, uint32_t seq, int v, uint32_t* c1, uint32_t* c2) {
+  if (!d.hot_x) {
+    *c1 = __ldcg(d.hot_cnt + v);
+    *c2 = d.has_delta ? __ldcg(d.hot_cntn + v) : 0u;
+    if (*c1) d.hot_cnt[v] = 0u;
+    if (*c2) d.hot_cntn[v] = 0u;
+    return;
+  }
+  const int n = d.nhot * d.Kp;
+  uint32_t a = 0u, b = 0u;
+  constexpr int RB = 8;  // ranks whose words are fetched together
+  for (int r0 = 0; r0 < d.G; r0 += RB) {
+    unsigned long long w1[RB], w2[RB];
+#pragma unroll
+    for (int u = 0; u < RB; ++u) {
+      if (r0 + u >= d.G) continue;
+      const unsigned long long* box = hotbox(d, d.mail, parity, r0 + u);
+      w1[u] = load_relaxed_sys64(box + v);
+      w2[u] = d.has_delta ? load_relaxed_sys64(box + n + v) : 0ull;
+    }
+#pragma unroll
+    for (int u = 0; u < RB; ++u) {
+      if (r0 + u >= d.G) continue;
+      const unsigned long long* box = hotbox(d, d.mail, parity, r0 + u);
+      a += ((uint32_t)(w1[u] >> 32) == seq) ? (uint32_t)w1[u] : pk_read(d, box + v, seq, 0u);
+      if (d.has_delta) b += ((uint32_t)(w2[u] >> 32) == seq) ? (uint32_t)w2[u] : pk_read(d, box + n + v, seq, 0u);
+    }
+  }
+  *c1 = a;
+  *c2 = b;
+}
+__device__ __forceinline__ void claim_hot_pair(const Dev& d, int v, uint32_t slot, uint32_t EVX, uint32_t c1, uint32_t c2) {
   if (!(c1 | c2)) return;
-  if (c1) d.hot_cnt[v] = 0u;
-  if (c2) d.hot_cntn[v] = 0u;
   const int h = (int)fdiv((uint32_t)v, d.mKp, d.sKp);
   const int mu = v - h * d.Kp;
   const uint32_t pos = (uint32_t)((size_t)__ldg(d.hot_rows + h) * d.Kp + mu);
@@ -904,6 +960,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
   const int svc = xx_ctas + push_ctas;  // CTAs that serve the exchange instead of tagging
   if ((int)blockIdx.x < svc) {
     push_winners(d, parity, blockIdx.x - xx_ctas, push_ctas);
+    if (d.hot_x) push_hot(d, parity, (uint32_t)(d.tick0 + local + 1), blockIdx.x - xx_ctas, push_ctas);
     return;
   }
   if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
@@ -949,7 +1006,11 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       // the winner's address does not depend on the id: both loads leave together
       const int ev = blk * TAG_BLOCK + threadIdx.x;
       // behind the slots, one thread per hot pair: what k_forward counted for it is claimed once, with the count
-      if (ev >= EV && ev < EV + d.nhot * d.Kp) claim_hot_pair(d, ev - EV, (uint32_t)ev, (uint32_t)(EV + d.nhot * d.Kp));
+      if (ev >= EV && ev < EV + d.nhot * d.Kp) {
+        uint32_t c1, c2;
+        hot_pair_counts(d, parity, seq, ev - EV, &c1, &c2);
+        claim_hot_pair(d, ev - EV, (uint32_t)ev, (uint32_t)(EV + d.nhot * d.Kp), c1, c2);
+      }
       const int i0 = (ev < EV) ? step_id(d, idx, ev >= E ? ev - E : ev) : -1;
       const unsigned long long* ww = winner_word(ev < EV ? ev : 0);
       const unsigned long long w0 = load_relaxed_sys64(ww);
@@ -957,7 +1018,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
       bool go0 = i0 >= 0 && mu0 >= 0 &&
                  !(d.shard && (int)((uint32_t)i0 - fdiv((uint32_t)i0, d.mG, d.sG) * (uint32_t)d.G) != d.rank);
       // a hot row's slot of a window k_forward ran here is in the pair's count already
-      if (go0 && d.nhot && __ldg(d.hotidx + i0) >= 0 && (emulate || slot_rank(ev >= E ? ev - E : ev) == d.rank)) go0 = false;
+      if (go0 && d.nhot && __ldg(d.hotidx + i0) >= 0 && (emulate || d.hot_x || slot_rank(ev >= E ? ev - E : ev) == d.rank)) go0 = false;
       const uint32_t pos = (uint32_t)((size_t)(go0 ? i0 : 0) * d.Kp + (go0 ? mu0 : 0));
       uint32_t c0 = 0u;
       if (go0) c0 = __ldcg(reinterpret_cast<const uint32_t*>(d.wt) + pos);
@@ -1135,6 +1196,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
   const int svc = xx_ctas + push_ctas;  // CTAs that serve the exchange instead of tagging
   if ((int)blockIdx.x < svc) {
     push_winners(d, parity, blockIdx.x - xx_ctas, push_ctas);
+    if (d.hot_x) push_hot(d, parity, (uint32_t)(d.tick0 + local + 1), blockIdx.x - xx_ctas, push_ctas);
     return;
   }
   if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
@@ -1148,6 +1210,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
   constexpr int TAG_BLOCK = U * XX_THREADS;
   const int nblocks = (EV + TAG_BLOCK - 1) / TAG_BLOCK;
   const int lane = threadIdx.x & 31, wic = threadIdx.x >> 5;
+  const bool emulate = (d.flags & FV_FLAG_EMULATE_RANKS) != 0;
   uint32_t* __restrict__ wbits = reinterpret_cast<uint32_t*>(d.wt);
   // every rank begins with the blocks of its own windows, whose winners are here already
   const int first_blk = (int)(((long long)nblocks * d.rank) / d.G);
@@ -1166,10 +1229,12 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
       const int ev = blk * TAG_BLOCK + u * XX_THREADS + threadIdx.x;
       bool mine = i[u] >= 0;
       if (OWN) mine = mine && (int)((uint32_t)i[u] - fdiv((uint32_t)i[u], d.mG, d.sG) * (uint32_t)d.G) == d.rank;
-      if (!mine) i[u] = -1;
       const int kind = (mine && ev >= E) ? 1 : 0;
       const uint32_t q = fdiv((uint32_t)(mine ? ev - kind * E : 0), d.mW, d.sW);  // window of the global step
       const uint32_t r = fdiv(q, d.mB, d.sB);                                    // its rank
+      // a hot row's slot of a window k_forward ran here is in the pair's count already
+      if (!OWN && mine && d.nhot && __ldg(d.hotidx + i[u]) >= 0 && (emulate || d.hot_x || (int)r == d.rank)) mine = false;
+      if (!mine) i[u] = -1;
       ww[u] = packet(d, parity, (int)r) + kind * d.MO + (int)(q - r * (uint32_t)d.B);
       w0[u] = mine ? load_relaxed_sys64(ww[u]) : 0ull;
     }
@@ -1226,7 +1291,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
         d.rec[slot[u]] = make_uint4(pos[u], c0[u], __float_as_uint(__ldg(d.f + (irow >= d.V ? irow - d.V : irow))), mult);
       } else {
         const uint32_t owner = (prev[u] & 0x007fffffu) - 1u;
-        if ((prev[u] & ABS_MASK) <= TAG_BASE || (prev[u] >> 31) || owner >= (uint32_t)EV) {
+        if ((prev[u] & ABS_MASK) <= TAG_BASE || (prev[u] >> 31) || owner >= (uint32_t)d.rec_cap) {
           atomicOr(&d.ctl->error, FV_DEVERR_NAN_WEIGHT);  // neither the expected weight nor a tag
         } else {
           if (mult & 0xffffu) atomicAdd(&d.cnt[owner], 1);
@@ -1235,6 +1300,23 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
       }
     }
     __syncthreads();  // s_scan and s_gbase are reused by the next round
+  }
+  if (!OWN && d.nhot) {
+    // behind the slots, the hot pairs: one thread per pair claims what k_forward counted for it; the non-empty
+    // pairs of a warp take their record numbers together
+    const int npairs = d.nhot * d.Kp;
+    const int stride = (gridDim.x - svc) * XX_THREADS;
+    for (int v0 = (blockIdx.x - svc) * XX_THREADS + threadIdx.x; v0 - lane < npairs; v0 += stride) {
+      uint32_t c1 = 0u, c2 = 0u;
+      if (v0 < npairs) hot_pair_counts(d, parity, seq, v0, &c1, &c2);
+      const bool has = (c1 | c2) != 0u;
+      const unsigned live = __ballot_sync(FULL, has);
+      if (!live) continue;
+      uint32_t base = 0u;
+      if (lane == 0) base = atomicAdd(&d.ctl->list_count[parity], (uint32_t)__popc(live));
+      base = __shfl_sync(FULL, base, 0);
+      if (has) claim_hot_pair(d, v0, base + (uint32_t)__popc(live & ((1u << lane) - 1u)), (uint32_t)d.rec_cap, c1, c2);
+    }
   }
 }
 
@@ -2744,7 +2826,9 @@ struct fv_trainer {
   uint32_t* d_hot_cntn = nullptr;
   int hot_rows_picked = 0;       // hot rows the corpus provided (<= HOT_ROWS)
   bool hot_pairs = true;         // option "hot_pairs"
-  bool hot_fits = false;         // the step's slots and the hot pairs fit one round of k_tag<1>
+  bool hot_fits = false;
+  int tag_forced = 0;            // the "tag_variant" option as given (0: by size)
+  bool tag_dedupe_now = false;   // the running call tags with the shared-memory dedupe kernel
   int tag_hot_grid = 0;
   uint32_t* d_colmax = nullptr;
   uint32_t* d_ncb = nullptr;
@@ -2907,7 +2991,7 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     const int own = d.shard ? 1 : 0;
     const int u = tr->tag_batch_u;
     const int grid = tr->tag_batch_grid + xx_ctas + push_ctas;
-    if (tr->tag_un == 2 && !own) {
+    if (tr->tag_dedupe_now && !own) {
       launch_pdl(k_tag<2>, tr->tag_grid + xx_ctas + push_ctas, XX_THREADS, table_smem, tr->stream, d, local, idx, xx_ctas, push_ctas);
     } else if (u == 1) {
       launch_pdl(k_tag<1>, (d.nhot ? tr->tag_hot_grid + xx_ctas + push_ctas : grid), XX_THREADS, (size_t)0, tr->stream, d, local, idx, xx_ctas, push_ctas);
@@ -3011,7 +3095,21 @@ int loop_begin(fv_trainer* tr, StepLoop& L) {
     if (!tr->d_idx_local[b]) FV_TRY(dev_alloc(&tr->d_idx_local[b], L.own_ids * STAGE_STEPS));
   tr->d.idx_rstride = (int)L.own_ids;
   tr->d.tick0 = tr->ticks;
-  tr->d.nhot = (tr->hot_pairs && tr->hot_fits && !tr->d.shard) ? tr->hot_rows_picked : 0;
+  {
+    // Hot pairs: with one rank, emulated ranks, or ranks that exchange their counts through peer mailboxes every
+    // hot-row slot is counted by some forward pass, and large steps need no dedupe any more (several slots per
+    // thread, batched claims).  Ranks that cannot exchange the counts (NCCL mode) count their own windows only;
+    // their large steps keep the dedupe kernel, which does not claim hot pairs.
+    Dev& dd = tr->d;
+    const bool emu = (dd.flags & FV_FLAG_EMULATE_RANKS) != 0;
+    const bool can_x = dd.G > 1 && !emu && tr->comm_mode == 2;
+    const bool all_counted = dd.G == 1 || emu || can_x;
+    const bool want_hot = tr->hot_pairs && tr->hot_fits && !dd.shard && tr->hot_rows_picked > 0;
+    const bool big = tr->tag_un == 2;  // a step larger than one round of k_tag<1>
+    tr->tag_dedupe_now = big && !dd.shard && (tr->tag_forced == 2 || !(want_hot && all_counted));
+    dd.nhot = (want_hot && !tr->tag_dedupe_now) ? tr->hot_rows_picked : 0;
+    dd.hot_x = (dd.nhot && can_x) ? 1 : 0;
+  }
   L.chunk_rstride = (int)L.own_ids;
   k_set_ctl<<<1, 1, 0, tr->stream>>>(tr->d_ctl, L.first_step, L.eps, tr->delta_now);
   L.launches = 1;
@@ -3224,7 +3322,8 @@ void choose_tag_variant(fv_trainer* tr, int force_un) {
   // threads (two ranks of 10000 windows), a tenth of the CTAs takes a second block round for them, which still
   // pays: on two GPUs the tagging kernel went from 13.7 to 12.0 us with each rank counting its own windows
   const size_t with_hot = E + (size_t)HOT_ROWS * d.Kp;
-  tr->hot_fits = tr->tag_un == 1 && u == 1;
+  tr->tag_forced = force_un;
+  tr->hot_fits = true;  // k_tag<1> and k_tag_batch claim hot pairs; whether the dedupe kernel is used instead is decided per call
   tr->tag_hot_grid = grid_for(with_hot, XX_THREADS, (int)resident);
 }
 
@@ -3285,6 +3384,10 @@ int create_impl(const fv_config* cfg, fv_trainer* tr) {
   d.inbox_off = (MAIL_HDR + 2 * 2 * (size_t)d.G * d.P + 3) & ~(size_t)3;
   d.inbox_cap = (d.G > 1 && !d.has_delta) ? (size_t)d.G * d.B * d.W : 0;  // a sender's list can hold every slot of a step
   tr->mail_words = d.inbox_off + 2 * (size_t)d.G * d.inbox_cap;
+  d.HC = HOT_ROWS * d.Kp * (1 + d.has_delta);
+  d.hot_off = (tr->mail_words + 3) & ~(size_t)3;
+  d.hot_x = 0;
+  if (d.G > 1) tr->mail_words = d.hot_off + 2 * 2 * (size_t)d.G * d.HC;  // u64 [2][G][HC]
   FV_TRY(dev_alloc(&tr->d_mail, tr->mail_words));
   const size_t hot_pairs = (size_t)HOT_ROWS * d.Kp;
   E += hot_pairs;  // records: one per slot, one per hot pair
@@ -3986,7 +4089,6 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
       const size_t E = (size_t)tr->d.G * tr->d.B * tr->d.W * (1 + tr->d.has_delta);
       tr->tag_batch_u = (int)value;
       tr->tag_batch_grid = grid_for(E, XX_THREADS * tr->tag_batch_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
-      if (tr->tag_batch_u != 1) tr->hot_fits = false;  // hot pairs are claimed by the one-slot-per-thread kernel only
     }
     return FV_OK;
   }
