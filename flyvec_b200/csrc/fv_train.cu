@@ -786,6 +786,7 @@ __device__ __forceinline__ void xx_finish(const Dev& d, int local) {
 // slice of the flagged words into every peer's copy of this rank's packet: plain 8-byte stores over
 // NVLink, no fence and no separate flag -- every word announces itself.
 constexpr int PUSH_CTAS = 8;
+constexpr int HOT_PUSH_CTAS = 16;  // further CTAs that send the hot-pair counts while the first eight send the winners
 __device__ __forceinline__ void push_winners(const Dev& d, int parity, int cta, int nctas) {
   const ulonglong2* __restrict__ src2 = reinterpret_cast<const ulonglong2*>(packet(d, parity, d.rank));
   const int n2 = d.XO >> 1;  // first and (with delta) second winners, two words at a time
@@ -824,6 +825,18 @@ __device__ __forceinline__ void push_hot(const Dev& d, int parity, uint32_t seq,
       *reinterpret_cast<ulonglong2*>(hotbox(d, r == d.rank ? d.mail : d.peers[r], parity, d.rank) + v) = w;
   }
 }
+// Push CTA `cta` of `nctas`: the first PUSH_CTAS send the winners, the others (launched when the hot-pair
+// counts travel) the counts, side by side.
+__device__ __forceinline__ void serve_exchange(const Dev& d, int parity, uint32_t seq, int cta, int nctas) {
+  if (!d.hot_x || nctas <= PUSH_CTAS) {
+    push_winners(d, parity, cta, nctas);
+    if (d.hot_x) push_hot(d, parity, seq, cta, nctas);
+  } else if (cta < PUSH_CTAS) {
+    push_winners(d, parity, cta, PUSH_CTAS);
+  } else {
+    push_hot(d, parity, seq, cta - PUSH_CTAS, nctas - PUSH_CTAS);
+  }
+}
 // CTA 0 finishes xx; further CTAs (when launched) push this rank's winners to the peers.  The tagging
 // kernel does both in its first CTAs; this kernel does them alone where xx must be complete before an
 // all-gather, and where several ranks share one stream, so that every rank's words are out before any
@@ -835,8 +848,7 @@ __global__ void __launch_bounds__(XX_THREADS) k_xx(Dev d, int local) {
   if (blockIdx.x == 0) {
     xx_finish(d, local);
   } else {
-    push_winners(d, (int)((d.tick0 + local) & 1), blockIdx.x - 1, gridDim.x - 1);
-    if (d.hot_x) push_hot(d, (int)((d.tick0 + local) & 1), (uint32_t)(d.tick0 + local + 1), blockIdx.x - 1, gridDim.x - 1);
+    serve_exchange(d, (int)((d.tick0 + local) & 1), (uint32_t)(d.tick0 + local + 1), blockIdx.x - 1, gridDim.x - 1);
   }
 }
 
@@ -959,8 +971,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag(Dev d, int local, const i
   }
   const int svc = xx_ctas + push_ctas;  // CTAs that serve the exchange instead of tagging
   if ((int)blockIdx.x < svc) {
-    push_winners(d, parity, blockIdx.x - xx_ctas, push_ctas);
-    if (d.hot_x) push_hot(d, parity, (uint32_t)(d.tick0 + local + 1), blockIdx.x - xx_ctas, push_ctas);
+    serve_exchange(d, parity, (uint32_t)(d.tick0 + local + 1), blockIdx.x - xx_ctas, push_ctas);
     return;
   }
   if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
@@ -1195,8 +1206,7 @@ __global__ void __launch_bounds__(XX_THREADS, 3) k_tag_batch(Dev d, int local, c
   }
   const int svc = xx_ctas + push_ctas;  // CTAs that serve the exchange instead of tagging
   if ((int)blockIdx.x < svc) {
-    push_winners(d, parity, blockIdx.x - xx_ctas, push_ctas);
-    if (d.hot_x) push_hot(d, parity, (uint32_t)(d.tick0 + local + 1), blockIdx.x - xx_ctas, push_ctas);
+    serve_exchange(d, parity, (uint32_t)(d.tick0 + local + 1), blockIdx.x - xx_ctas, push_ctas);
     return;
   }
   if ((int)blockIdx.x == svc && threadIdx.x == 0) phase_mark(d.ctl, PH_TAG);
@@ -2950,7 +2960,7 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
   const bool split_exchange = tr->lockstep && tr->comm_mode == 2 && !emulate && !single;
   if (phase == 1) {
     if (split_exchange) {
-      launch_pdl(k_xx, 1 + PUSH_CTAS, XX_THREADS, (size_t)0, tr->stream, d, local);
+      launch_pdl(k_xx, 1 + PUSH_CTAS + (d.hot_x ? HOT_PUSH_CTAS : 0), XX_THREADS, (size_t)0, tr->stream, d, local);
       *launches += 1;
     }
     return FV_OK;
@@ -2985,7 +2995,7 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     // (and, with mailboxes, push winners first and xx last); otherwise xx is complete already.
     const bool fused = single || (tr->comm_mode == 2 && !emulate && !split_exchange);
     const size_t table_smem = tag_table_bytes(tr->tag_un);
-    const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS : 0;
+    const int xx_ctas = fused ? 1 : 0, push_ctas = (fused && !single) ? PUSH_CTAS + (d.hot_x ? HOT_PUSH_CTAS : 0) : 0;
     // 1: one slot per thread (a step fits one round of the resident threads); 2: dedupe in shared memory;
     // 3: U slots per thread with batched claims (what large steps use)
     const int own = d.shard ? 1 : 0;
@@ -3306,7 +3316,7 @@ int default_shard(const fv_trainer* tr) {
 void choose_tag_variant(fv_trainer* tr, int force_un) {
   const Dev& d = tr->d;
   const size_t E = (size_t)d.G * d.B * d.W * (1 + d.has_delta);
-  const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS;
+  const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS - HOT_PUSH_CTAS;
   // replicated update: large steps deduplicate in shared memory (measured at 8 ranks' slots: 46.6 us for the
   // three update kernels against 55.4 us with four batched slots per thread -- hot (unit, token) pairs meet at
   // one L2 address); force_un = 3 selects the batched kernel all the same
@@ -4088,7 +4098,7 @@ int fv_trainer_set_option(fv_trainer* tr, const char* key, double value) {
     if (value != 0.0) {
       const size_t E = (size_t)tr->d.G * tr->d.B * tr->d.W * (1 + tr->d.has_delta);
       tr->tag_batch_u = (int)value;
-      tr->tag_batch_grid = grid_for(E, XX_THREADS * tr->tag_batch_u, tr->num_sms * 3 - 1 - PUSH_CTAS);
+      tr->tag_batch_grid = grid_for(E, XX_THREADS * tr->tag_batch_u, tr->num_sms * 3 - 1 - PUSH_CTAS - HOT_PUSH_CTAS);
     }
     return FV_OK;
   }

@@ -2,8 +2,8 @@
 claimed once by the tagging kernel (the default where a step fits one round of the one-slot-per-thread
 kernel), or claimed one by one like every other request (`"hot_pairs" = 0`).  The counts are integers, so
 whole runs must agree bit for bit: weights, per-step normalisers and step sizes, with one rank, emulated
-ranks, linked ranks (each counts its own windows only), the anti-Hebbian term, and a corpus in which a
-handful of tokens make up almost everything."""
+ranks, linked ranks (each counts its own windows and sends the counts to the others), the anti-Hebbian term,
+and a corpus in which a handful of tokens make up almost everything."""
 import numpy as np
 import pytest
 
@@ -55,7 +55,7 @@ def test_counted_and_one_by_one_agree_bit_for_bit(built_lib, K, V, W, B, steps, 
 
 
 @pytest.mark.parametrize("world", [2, 3])
-def test_linked_ranks_count_their_own_windows(built_lib, world):
+def test_linked_ranks_exchange_their_counts(built_lib, world):
     p = small_problem(K=64, V=300, W=11, ntok=200000, seed=53)
     B, steps = 150, 40
     out = []
@@ -87,9 +87,9 @@ def test_config1_shapes_200_steps(built_lib):
     np.testing.assert_array_equal(Wa, Wb)
 
 
-def test_two_ranks_of_config1_take_a_second_round_for_the_pairs(built_lib):
-    """Two ranks of 10000 windows fill the resident threads of the tagging kernel with slots alone; the hot
-    pairs then cost some CTAs a second block round.  Same bits as claiming one by one."""
+def test_two_linked_ranks_at_config1_shapes_exchange_their_counts(built_lib):
+    """Two ranks of 10000 windows each: a step of 220000 slots goes through the batched tagging kernel, every
+    hot-row slot is skipped and the ranks' counts meet in the hotboxes.  Same bits as claiming one by one."""
     K, V, W, B, steps = 400, 20000, 11, 10000, 12
     p = skewed_problem(K, V, W, 1_500_000, 57, 1.0)
     assert len(p["starts"]) >= steps * B * 2
