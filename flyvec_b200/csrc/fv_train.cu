@@ -786,7 +786,8 @@ __device__ __forceinline__ void xx_finish(const Dev& d, int local) {
 // slice of the flagged words into every peer's copy of this rank's packet: plain 8-byte stores over
 // NVLink, no fence and no separate flag -- every word announces itself.
 constexpr int PUSH_CTAS = 8;
-constexpr int HOT_PUSH_CTAS = 16;  // further CTAs that send the hot-pair counts while the first eight send the winners
+constexpr int HOT_PUSH_CTAS = 0;  // further CTAs that would send the hot-pair counts beside the winners: measured no gain on two GPUs,
+                                  // and every CTA taken from the tagging pushes large steps towards more slots per thread
 __device__ __forceinline__ void push_winners(const Dev& d, int parity, int cta, int nctas) {
   const ulonglong2* __restrict__ src2 = reinterpret_cast<const ulonglong2*>(packet(d, parity, d.rank));
   const int n2 = d.XO >> 1;  // first and (with delta) second winners, two words at a time
