@@ -193,7 +193,7 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *   "tag_variant"  the scatter bookkeeping of a step: 1: one slot per thread and block round; 2: 1024 slots
  *                  deduplicated in shared memory before they are claimed; 3: several slots per thread, their
  *                  loads and claims issued together; 0 (default): 1 while a step fits the resident threads, else
- *                  2 for the replicated and 3 for the sharded update;
+ *                  3, or 2 where hot pairs are off or not every rank's windows are counted (see "hot_pairs");
  *   "tag_slots"    the slots per thread of the default variant: 1, 2, 4, 8, or 0 for the size-based choice;
  *   "colmax_lists" 1 (default): the largest untouched weight of every unit comes from a short list of
  *                  candidate rows kept from step to step (a unit whose list cannot certify its maximum
@@ -204,9 +204,8 @@ int fv_trainer_init_comm(fv_trainer* tr, const uint8_t id[128]);
  *                  (FV_FUSED_UPDATE=0 in the environment selects the same);
  *   "hot_pairs"    1 (default): requests for a (row of one of the 32 most frequent tokens, unit) pair are counted
  *                  by the forward pass and claimed once per pair by the tagging kernel, instead of queueing one by
- *                  one at the pair's address; used where a step's slots fit one round of the one-slot-per-thread
- *                  tagging kernel (one or two GPUs at the benchmark's shapes; a rank counts the windows of its
- *                  own forward pass); 0: every request claims for itself
+ *                  one at the pair's address; ranks with peer mailboxes send one another their counts, ranks
+ *                  that exchange through NCCL count their own windows only; 0: every request claims for itself
  *                  (FV_HOT_PAIRS=0 in the environment selects the same);
  *   "shard"        1 / 0: sharded or replicated update (peer mailboxes only; see fv_trainer_comm_mode);
  *   "loopback_peers" 1: test aid -- every peer's mailbox is mapped onto this rank's own, so a peer's
