@@ -2856,6 +2856,7 @@ struct fv_trainer {
   unsigned long long column_rescans = 0;  // single units whose column was read because their candidates were all touched
   bool fused_update = true;      // ordinary steps run evaluation and apply as one kernel (k_update)
   bool fused_this_step = false;
+  bool no_grid_meeting = false;  // the running call has collectives of another library in flight beside the step loop
   int update_grid = 0;           // CTAs of k_update: all resident at once
   size_t update_smem = 0;
   unsigned long long update_launches = 0;
@@ -3018,7 +3019,7 @@ int enqueue_phase(fv_trainer* tr, int phase, int local, const int32_t* idx, uint
     *launches += 1;
   } else if (phase == 2) {
     tr->fused_this_step = false;
-    if (d.use_cand && !tr->cand_dirty && !d.shard && tr->fused_update && tr->update_grid > 0) {
+    if (d.use_cand && !tr->cand_dirty && !d.shard && tr->fused_update && tr->update_grid > 0 && !tr->no_grid_meeting) {
       // an ordinary step: evaluation and apply in one kernel
       const int qblocks = (d.K + SCAN_THREADS / 32 - 1) / (SCAN_THREADS / 32);
       tr->update_launches += 1;
@@ -3099,6 +3100,13 @@ int loop_begin(fv_trainer* tr, StepLoop& L) {
   for (int b = 0; b < 2; ++b)
     if (!tr->d_idx_stage[b]) FV_TRY(dev_alloc(&tr->d_idx_stage[b], L.step_ids * STAGE_STEPS));
   L.gather_ids = L.idx_host && L.idx_local && d.G > 1 && !(d.flags & FV_FLAG_EMULATE_RANKS);
+  // The ranks' ids meet through NCCL all-gathers on the second stream while the step loop runs.  A kernel whose own
+  // CTAs wait for one another (k_update's meeting point) needs its whole grid resident; beside an NCCL kernel it
+  // may not get that until the collective ends, and the collective may be waiting for a rank whose GPU is filled
+  // by a tagging kernel that waits for this rank's next packet: the ring closes (seen on 8 GPUs as FV_ERR_TIMEOUT
+  // at the first block boundary).  Such calls evaluate and apply in two kernels, which wait for nobody on the
+  // same GPU.
+  tr->no_grid_meeting = L.gather_ids;
   if (L.idx_host && L.idx_local && d.G > 1 && !L.gather_ids)
     return fv::fail(FV_ERR_INVALID, "rank-local ids need real ranks: with FV_FLAG_EMULATE_RANKS pass all ranks' ids");
   if (L.gather_ids) FV_REQUIRE(tr->comm != nullptr, FV_ERR_STATE, "rank-local ids travel through the NCCL communicator: call fv_trainer_init_comm");
