@@ -2837,7 +2837,6 @@ struct fv_trainer {
   uint32_t* d_hot_cntn = nullptr;
   int hot_rows_picked = 0;       // hot rows the corpus provided (<= HOT_ROWS)
   bool hot_pairs = true;         // option "hot_pairs"
-  bool hot_fits = false;
   int tag_forced = 0;            // the "tag_variant" option as given (0: by size)
   bool tag_dedupe_now = false;   // the running call tags with the shared-memory dedupe kernel
   int tag_hot_grid = 0;
@@ -3123,7 +3122,7 @@ int loop_begin(fv_trainer* tr, StepLoop& L) {
     const bool emu = (dd.flags & FV_FLAG_EMULATE_RANKS) != 0;
     const bool can_x = dd.G > 1 && !emu && tr->comm_mode == 2;
     const bool all_counted = dd.G == 1 || emu || can_x;
-    const bool want_hot = tr->hot_pairs && tr->hot_fits && !dd.shard && tr->hot_rows_picked > 0;
+    const bool want_hot = tr->hot_pairs && !dd.shard && tr->hot_rows_picked > 0;
     const bool big = tr->tag_un == 2;  // a step larger than one round of k_tag<1>
     tr->tag_dedupe_now = big && !dd.shard && (tr->tag_forced == 2 || !(want_hot && all_counted));
     dd.nhot = (want_hot && !tr->tag_dedupe_now) ? tr->hot_rows_picked : 0;
@@ -3326,9 +3325,11 @@ void choose_tag_variant(fv_trainer* tr, int force_un) {
   const Dev& d = tr->d;
   const size_t E = (size_t)d.G * d.B * d.W * (1 + d.has_delta);
   const size_t resident = (size_t)tr->num_sms * 3 - 1 - PUSH_CTAS - HOT_PUSH_CTAS;
-  // replicated update: large steps deduplicate in shared memory (measured at 8 ranks' slots: 46.6 us for the
-  // three update kernels against 55.4 us with four batched slots per thread -- hot (unit, token) pairs meet at
-  // one L2 address); force_un = 3 selects the batched kernel all the same
+  // tag_un = 2: the step is larger than one round of the one-slot-per-thread kernel.  Such a step takes several
+  // slots per thread with batched claims when every hot-row slot is counted (see loop_begin), else it deduplicates
+  // in shared memory: measured at 8 ranks' slots with every request claiming for itself, 46.6 us for the three
+  // update kernels with the dedupe against 55.4 us with four batched slots per thread -- hot (unit, token) pairs
+  // meet at one L2 address -- and 29 us with the batched kernel once the hot pairs are counted
   tr->tag_un = (force_un == 2 || (force_un == 0 && (E + XX_THREADS - 1) / XX_THREADS > resident)) ? 2 : 1;
   tr->tag_grid = grid_for(E, XX_THREADS * tr->tag_un, (int)resident);
   // slots per thread so that one block round covers the step
@@ -3338,11 +3339,9 @@ void choose_tag_variant(fv_trainer* tr, int force_un) {
   tr->tag_batch_u = u;
   tr->tag_batch_grid = grid_for(E, XX_THREADS * u, (int)resident);
   // hot pairs ride behind the slots of the one-slot-per-thread kernel; where the slots alone fill the resident
-  // threads (two ranks of 10000 windows), a tenth of the CTAs takes a second block round for them, which still
-  // pays: on two GPUs the tagging kernel went from 13.7 to 12.0 us with each rank counting its own windows
+  // threads (two ranks of 10000 windows), a tenth of the CTAs takes a second block round for them
   const size_t with_hot = E + (size_t)HOT_ROWS * d.Kp;
   tr->tag_forced = force_un;
-  tr->hot_fits = true;  // k_tag<1> and k_tag_batch claim hot pairs; whether the dedupe kernel is used instead is decided per call
   tr->tag_hot_grid = grid_for(with_hot, XX_THREADS, (int)resident);
 }
 
