@@ -11,8 +11,10 @@
 //   idx     int  [32][G*B][w] input ids of the next steps (all ranks' windows), two staging buffers.
 //   mailbox                 per rank and step parity a packet of 64-bit words {payload, step sequence
 //                           number}: B winners, (with delta) B second winners, Kp floats of xx.
-//   xx_hi/lo  u64 [8][Kp]   fixed-point accumulators of xx; rec/cnt [G*B*w] scatter bookkeeping: one
+//   xx_hi/lo  u64 [8][Kp]   fixed-point accumulators of xx; rec/cnt [G*B*w + 64*Kp] scatter bookkeeping: one
 //                           record per distinct touched position.
+//   hot_cnt u32 [64][Kp]    requests per (row of one of the 32 most frequent tokens, unit) pair, counted by
+//                           k_forward; with several ranks the counts travel in a "hotbox" beside the packets.
 //
 // One global step (reference: run_epoch, flyvec/src/cuda_funcs.cu:1662-1812):
 //   (k_build_idx_block, on a side stream: T4, ids of the next 32 steps   (cuda_funcs.cu:915-936))
@@ -20,7 +22,9 @@
 //                T8   every window adds its term of xx[mu] as a fixed-point number: the sum does not
 //                     depend on the order of arrival          (cuda_funcs.cu:722-744)
 //   k_tag        T10  each touched (mu,i) gets one owner record; its weight is parked there and
-//                     replaced by a tagged NaN                 (cuda_funcs.cu:657-672);
+//                     replaced by a tagged NaN                 (cuda_funcs.cu:657-672); requests for hot
+//                     pairs are not claimed one by one: one thread per pair claims the counted total
+//                     (k_tag_batch: the same with several slots per thread, for steps of several ranks);
 //                     its first CTA turns the xx sums into floats (xx_finish); with several ranks
 //                     eight more CTAs copy this rank's winners into the peers' mailboxes, and every
 //                     consumer of a peer's word checks the sequence number the word carries
