@@ -295,9 +295,14 @@ def bench_train(args):
     tr.run_steps_host_local(pinned[:min(8, e2e_steps)], min(8, e2e_steps), eps)  # warm the staging buffers
     dist.barrier()
     t0 = time.perf_counter()
-    tr.run_steps_host_local(pinned, e2e_steps, eps, nc_out=nc_host)
+    e2e_error = None
+    try:
+        tr.run_steps_host_local(pinned, e2e_steps, eps, nc_out=nc_host)
+    except _lib.FlyvecError as exc:  # the line still carries the device-timed value; the failure is reported, not hidden
+        e2e_error = str(exc)
     e2e_wall = dist.max(time.perf_counter() - t0)
-    e2e_value = e2e_steps * world * B / e2e_wall
+    e2e_error = next((e for e in dist.gather_obj(e2e_error) if e), None)
+    e2e_value = None if e2e_error else e2e_steps * world * B / e2e_wall
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- roofline of the dominant kernel ---------------------------------------
@@ -306,7 +311,10 @@ def bench_train(args):
     # latency that the pipelined loop hides).
     peak, peak_src = measured_peaks()
     fwd_bytes = B * W * K * 4 + B * (8 + 4 * W) + B * 8  # gathered rows + order entry and ids + winner and activation out
-    fwd_avg = dist.max(tr.time_forward(warmup + steps, reps=50))
+    if e2e_error is None:
+        fwd_avg = dist.max(tr.time_forward(warmup + steps, reps=50))
+    else:  # the trainers are void after a failed call: take the kernel's time inside the timed step loop instead
+        fwd_avg = fwd_s / steps
     achieved = fwd_bytes / fwd_avg / 1e9
     step_bytes = B * W * K * 4 + 3 * K * 2 * V * 4 + B * (8 + 4 * W) + B * 2 + K * 4  # the reference schedule's figure
     # The synapse matrix (64 MB) lives in the L2, so the forward kernel's real ceiling is what the L2 gives
@@ -340,7 +348,7 @@ def bench_train(args):
         "wall_ms_per_step": wall / steps * 1e3,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "windows/s", "h2d_bytes_per_step": world * B * W * 4,
-                "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                "d2h_bytes_per_step": 4, "steps": e2e_steps, **({"error": e2e_error} if e2e_error else {}),
                 "what": "fv_trainer_run_steps_host_local: every rank uploads the input ids of its own windows from pinned host "
                         "memory inside the call (all-gathered over NVLink when there are several ranks), per-step "
                         "normaliser copied back"},
